@@ -1,0 +1,344 @@
+"""Fused-graph IR: the 6-tuple of dict lists that the reference's tracer hands to its code generators.
+
+The reference's ``trace_graph`` (trace/graph_trace.py:32-328) returns
+``(inputs, outputs, selector_register, map_operations, reducer_operations, aggregator_operations)``;
+every emitter downstream (codegen/merged_gen_core.py, codegen/merged_gen_gpu.py,
+codegen/merged_gen_binding.py) consumes only those lists.  ``easier`` (the package that produces the
+FX graph) is a third-party dependency, so this module builds the same lists by hand for the graphs
+the benchmark configurations need and for the unit-test graphs.  Dict keys follow
+trace/graph_trace.py:133-157 (inputs), :179-205 (selector_register), :279-286 (map operations).
+
+Two optional keys are an extension understood only by this package's CUDA emitter (the reference
+emitters ignore unknown keys):
+
+``row_identity`` (selector_register entry, selector == 1)
+    the selector's index array equals the row id of every edge (``idx[e] == row(e)``), so the CUDA
+    kernel derives it from the merge path instead of streaming the index array from HBM.  The array
+    is still part of the operator signature.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Sequence, Tuple
+
+
+class NodeRef:
+    """Stand-in for a torch.fx Node: the binding generators only read ``args[0].name`` of a selector
+    input (codegen/merged_gen_binding.py:46-48, codegen/merged_gen_binding_cpu.py:46-48)."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __repr__(self) -> str:  # printed by the emitters when they str() an argument
+        return self.name
+
+
+@dataclass
+class GraphIR:
+    """One fused sub-graph in the reference's IR.  ``value_dtype`` is 'float32' | 'float64' | 'int64'
+    for the instance that gets compiled (the reference dispatches float/double(/long) at run time,
+    cuda_template/merged_binding_template.cu:55-69)."""
+
+    name: str
+    inputs: List[Dict[str, Any]]
+    outputs: List[Dict[str, Any]]
+    selector_register: List[Dict[str, Any]]
+    map_operations: List[Dict[str, Any]]
+    reducer_operations: List[Dict[str, Any]]
+    aggregator_operations: List[Dict[str, Any]]
+    doc: str = ""
+
+    def as_tuple(self):
+        return (self.inputs, self.outputs, self.selector_register, self.map_operations,
+                self.reducer_operations, self.aggregator_operations)
+
+    @property
+    def has_reducer(self) -> bool:
+        return len(self.reducer_operations) > 0
+
+    def digest(self) -> str:
+        def norm(o):
+            if isinstance(o, dict):
+                return {k: norm(v) for k, v in sorted(o.items()) if k != "dtype_data"}
+            if isinstance(o, (list, tuple)):
+                return [norm(v) for v in o]
+            if isinstance(o, NodeRef):
+                return o.name
+            if isinstance(o, (int, float, str)) or o is None:
+                return o
+            return str(o)
+        blob = json.dumps([norm(x) for x in self.as_tuple()], sort_keys=True)
+        return hashlib.sha1(blob.encode()).hexdigest()[:12]
+
+
+# ----------------------------------------------------------------------------------------------
+# small helpers that produce dicts exactly in the tracer's shape
+# ----------------------------------------------------------------------------------------------
+
+def dim_of(shape: Sequence[int]) -> int:
+    """Flattened per-element width (codegen/utils.py:5-12)."""
+    d = 1
+    for s in shape:
+        d *= int(s)
+    return d
+
+
+def placeholder(name: str, shape: Tuple[int, ...]) -> Dict[str, Any]:
+    return {"name": name, "target": name, "dtype": "scalar_t", "shape": tuple(shape),
+            "op": "placeholder", "args": (), "dtype_data": None}
+
+
+def selector_input(name: str, gather_src: str, shape: Tuple[int, ...]) -> Dict[str, Any]:
+    """A Selector module call; ``target`` names the index array, args[0] is the gathered tensor."""
+    return {"name": name, "target": name, "dtype": "int", "shape": tuple(shape),
+            "op": "call_module", "args": (NodeRef(gather_src),), "dtype_data": None}
+
+
+def edge_register(name: str, shape: Tuple[int, ...]) -> Dict[str, Any]:
+    return {"name": name, "target": name, "dtype": "TensorT", "selector": 0,
+            "selector_name": name, "shape": tuple(shape), "dtype_data": None}
+
+
+def gather_register(name: str, gather_src: str, shape: Tuple[int, ...], row_identity: bool = False) -> Dict[str, Any]:
+    d = {"name": name, "target": gather_src, "dtype": "TensorKeyT", "selector": 1,
+         "selector_name": name, "shape": tuple(shape), "dtype_data": None}
+    if row_identity:
+        d["row_identity"] = True
+    return d
+
+
+def mop(name: str, op: str, shape: Tuple[int, ...], *args) -> Dict[str, Any]:
+    return {"name": name, "target": op, "op": op, "shape": tuple(shape), "dtype_data": None,
+            "args": list(args)}
+
+
+def out(name: str, target: Any, shape: Tuple[int, ...], args=()) -> Dict[str, Any]:
+    return {"op": "call_module" if target == "reducer" else "call_function", "name": name,
+            "target": target, "dtype": "ValueT", "shape": tuple(shape), "args": args,
+            "dtype_data": None}
+
+
+def _finish(name, inputs, outputs, selreg, mapops, doc="") -> GraphIR:
+    reducers = [{k: v for k, v in m.items() if k != "target"} for m in mapops if m["op"] == "reducer"]
+    aggs = [{k: v for k, v in m.items() if k != "target"} for m in mapops if m["op"] == "sum"]
+    return GraphIR(name, inputs, outputs, selreg, mapops, reducers, aggs, doc)
+
+
+# ----------------------------------------------------------------------------------------------
+# the graphs
+# ----------------------------------------------------------------------------------------------
+
+def spmv_graph() -> GraphIR:
+    """Plain y = A.x: ``mul(vals, x[col])`` then a dim-1 reducer.
+    Operator: merged_spmv_launch(vals, x, selector_idx, row_end_offsets, num_rows, num_cols) -> (y,)"""
+    inputs = [placeholder("vals", (1,)), placeholder("x", (1,)), selector_input("selector", "x", (1,))]
+    selreg = [edge_register("vals", (1,)), gather_register("selector", "x", (1,))]
+    mapops = [mop("mul", "mul", (1,), "vals", "selector"), mop("reducer", "reducer", (1,), "mul")]
+    outputs = [out("reducer", "reducer", (1,))]
+    return _finish("spmv", inputs, outputs, selreg, mapops, spmv_graph.__doc__)
+
+
+def spring_mass_graph() -> GraphIR:
+    """Spring-mass force: f = k (|d| - L) d/|d| with d = p[dst] - p[src], summed per source vertex.
+    Operator: merged_spmv_launch(L, k, p, sel_src_idx, sel_dst_idx, row_end_offsets, N, N) -> (f,)
+    ``sel_src`` is the row id of every edge (edges are stored CSR-by-source)."""
+    inputs = [placeholder("L", (1,)), placeholder("k", (1,)), placeholder("p", (2,)),
+              selector_input("sel_src", "p", (2,)), selector_input("sel_dst", "p", (2,))]
+    selreg = [edge_register("L", (1,)), edge_register("k", (1,)),
+              gather_register("sel_src", "p", (2,), row_identity=True),
+              gather_register("sel_dst", "p", (2,))]
+    mapops = [
+        mop("d", "sub", (2,), "sel_dst", "sel_src"),
+        mop("n", "norm", (1,), "d"),
+        mop("s", "sub", (1,), "n", "L"),
+        mop("ks", "mul", (1,), "k", "s"),
+        mop("kd", "mul", (2,), "ks", "d"),
+        mop("f", "truediv", (2,), "kd", "n"),
+        mop("red", "reducer", (2,), "f"),
+    ]
+    outputs = [out("red", "reducer", (2,))]
+    return _finish("spring_mass", inputs, outputs, selreg, mapops, spring_mass_graph.__doc__)
+
+
+def rusanov_graph() -> GraphIR:
+    """Shallow-water Rusanov / local Lax-Friedrichs face flux, g = 9.81, summed per cell.
+    Per edge (cell i -> neighbour j) with face data (nx, ny, len) and state U = (h, hu, hv):
+      un = (hu nx + hv ny)/h ;  F.n = (h un, hu un + g h^2 nx / 2, hv un + g h^2 ny / 2)
+      lam = max(|un_i| + sqrt(g h_i), |un_j| + sqrt(g h_j))
+      flux = (0.5 (F_i.n + F_j.n) - 0.5 lam (U_j - U_i)) len
+    Written only with ops of the reference vocabulary (no sqrt/max: pow 0.5 and where(gt)); the three
+    components are three dim-1 reducers because the vocabulary has no concat.
+    Operator: merged_spmv_launch(face, U, sel_self_idx, sel_nbr_idx, row_end_offsets, n, n)
+              -> (flux_h, flux_hu, flux_hv)"""
+    S1 = (1,)
+    inputs = [placeholder("face", (3,)), placeholder("U", (3,)),
+              selector_input("sel_self", "U", (3,)), selector_input("sel_nbr", "U", (3,))]
+    selreg = [edge_register("face", (3,)),
+              gather_register("sel_self", "U", (3,), row_identity=True),
+              gather_register("sel_nbr", "U", (3,))]
+    m: List[Dict[str, Any]] = []
+
+    def op(name, kind, *args):
+        m.append(mop(name, kind, S1, *args))
+        return name
+
+    nx = op("nx", "getitem", "face", (None, 0))
+    ny = op("ny", "getitem", "face", (None, 1))
+    ln = op("ln", "getitem", "face", (None, 2))
+    side = {}
+    for s, sel in (("i", "sel_self"), ("j", "sel_nbr")):
+        h = op(f"h{s}", "getitem", sel, (None, 0))
+        hu = op(f"hu{s}", "getitem", sel, (None, 1))
+        hv = op(f"hv{s}", "getitem", sel, (None, 2))
+        a1 = op(f"a1{s}", "mul", hu, nx)
+        a2 = op(f"a2{s}", "mul", hv, ny)
+        a3 = op(f"a3{s}", "add", a1, a2)
+        un = op(f"un{s}", "truediv", a3, h)
+        h2 = op(f"h2{s}", "mul", h, h)
+        p = op(f"p{s}", "mul", h2, 4.905)
+        f0 = op(f"f0{s}", "mul", h, un)
+        t1 = op(f"t1{s}", "mul", hu, un)
+        t2 = op(f"t2{s}", "mul", p, nx)
+        f1 = op(f"f1{s}", "add", t1, t2)
+        t3 = op(f"t3{s}", "mul", hv, un)
+        t4 = op(f"t4{s}", "mul", p, ny)
+        f2 = op(f"f2{s}", "add", t3, t4)
+        gh = op(f"gh{s}", "mul", h, 9.81)
+        c = op(f"c{s}", "pow", gh, 0.5)
+        au = op(f"au{s}", "abs", un)
+        sp = op(f"sp{s}", "add", au, c)
+        side[s] = dict(h=h, hu=hu, hv=hv, f=(f0, f1, f2), sp=sp)
+    g = op("spgt", "gt", side["i"]["sp"], side["j"]["sp"])
+    lam = op("lam", "where", g, side["i"]["sp"], side["j"]["sp"])
+    hl = op("hl", "mul", lam, 0.5)
+    reds = []
+    for k, comp in enumerate(("h", "hu", "hv")):
+        fs = op(f"fs{k}", "add", side["i"]["f"][k], side["j"]["f"][k])
+        fa = op(f"fa{k}", "mul", fs, 0.5)
+        du = op(f"du{k}", "sub", side["j"][comp], side["i"][comp])
+        ds = op(f"ds{k}", "mul", hl, du)
+        fx = op(f"fx{k}", "sub", fa, ds)
+        fl = op(f"fl{k}", "mul", fx, ln)
+        reds.append(op(f"flux_{comp}", "reducer", fl))
+    outputs = [out(r, "reducer", S1) for r in reds]
+    return _finish("rusanov", inputs, outputs, selreg, m, rusanov_graph.__doc__)
+
+
+def mixed_dims_graph() -> GraphIR:
+    """Unit-test graph shaped like the reference's demo model (easier_spmv.py:17-69, generated
+    instance include/merged_agent_spmv.cuh:124-149): two selectors on one dim-2 vertex tensor, edge
+    tensors of dim 2 and 6, modulo broadcasting 2 -> 6, a dim-2 and a dim-6 reducer, one per-edge
+    map output.  Exercises empty rows, multi-reducer accumulation and mixed widths."""
+    inputs = [placeholder("ea", (2,)), placeholder("eb", (6,)), placeholder("vx", (2,)),
+              selector_input("s0", "vx", (2,)), selector_input("s1", "vx", (2,))]
+    selreg = [edge_register("ea", (2,)), edge_register("eb", (6,)),
+              gather_register("s0", "vx", (2,)), gather_register("s1", "vx", (2,))]
+    m = [
+        mop("t0", "add", (2,), "s0", "s1"),
+        mop("t1", "mul", (2,), "t0", "ea"),
+        mop("t2", "mul", (6,), "eb", "t1"),          # 6 x 2 modulo broadcast
+        mop("t3", "sub", (6,), "t2", 0.25),
+        mop("t4", "neg", (2,), "t1"),
+        mop("r2", "reducer", (2,), "t4"),
+        mop("r6", "reducer", (6,), "t3"),
+    ]
+    outputs = [out("r2", "reducer", (2,)), out("r6", "reducer", (6,)), out("t1", "mul", (2,))]
+    return _finish("mixed_dims", inputs, outputs, selreg, m, mixed_dims_graph.__doc__)
+
+
+def ops_zoo_graph() -> GraphIR:
+    """Unit-test graph touching the rest of the map vocabulary (trace/graph_trace.py:229-276):
+    truediv with a zero divisor (guarded: result 0, data_struct_shared.cuh:194-200), scalar / tensor,
+    pow, exp, abs, sign, lt, gt, where, getitem, clone, norm."""
+    inputs = [placeholder("w", (2,)), placeholder("v", (2,)), selector_input("sel", "v", (2,))]
+    selreg = [edge_register("w", (2,)), gather_register("sel", "v", (2,))]
+    m = [
+        mop("q", "truediv", (2,), "w", "sel"),       # same dims: guarded divide
+        mop("iq", "truediv", (2,), 1.5, "sel"),      # scalar / tensor: guarded
+        mop("aw", "abs", (2,), "w"),
+        mop("pw", "pow", (2,), "aw", 1.5),
+        mop("sw", "mul", (2,), "w", -0.125),
+        mop("ex", "exp", (2,), "sw"),
+        mop("sg", "sign", (2,), "w"),
+        mop("lt0", "lt", (2,), "w", 0.25),
+        mop("g0", "gt", (2,), "sel", "w"),
+        mop("wh", "where", (2,), "lt0", "pw", "ex"),
+        mop("w0", "getitem", (1,), "w", (None, 0)),
+        mop("cl", "clone", (2,), "sg"),
+        mop("nn", "norm", (1,), "sel"),
+        mop("a0", "add", (2,), "q", "iq"),
+        mop("a1", "add", (2,), "a0", "wh"),
+        mop("a2", "mul", (2,), "a1", "w0"),          # 2 x 1 broadcast
+        mop("a3", "add", (2,), "a2", "cl"),
+        mop("a4", "add", (2,), "a3", "g0"),
+        mop("a5", "truediv", (2,), "a4", "nn"),      # tensor / scalar: unguarded
+        mop("red", "reducer", (2,), "a5"),
+    ]
+    outputs = [out("red", "reducer", (2,))]
+    return _finish("ops_zoo", inputs, outputs, selreg, m, ops_zoo_graph.__doc__)
+
+
+def edge_sum_graph() -> GraphIR:
+    """Aggregator flavour (no reducer, cuda_template/aggregator/*): per-edge product stored as a map
+    output plus a global ``sum`` of it.  Operator:
+    merged_spmv_launch(ew, vx, sel_idx, row_end_offsets(dummy), num_rows, num_cols) -> (prod, total)"""
+    inputs = [placeholder("ew", (2,)), placeholder("vx", (2,)), selector_input("sel", "vx", (2,))]
+    selreg = [edge_register("ew", (2,)), gather_register("sel", "vx", (2,))]
+    m = [mop("prod", "mul", (2,), "ew", "sel"), mop("total", "sum", (2,), "prod")]
+    outputs = [out("prod", "mul", (2,)), out("total", "sum", (2,))]
+    return _finish("edge_sum", inputs, outputs, selreg, m, edge_sum_graph.__doc__)
+
+
+def edge_copy_graph() -> GraphIR:
+    """Map-only flavour with in-place writes, the shape of the reference's checked-in CPU instance
+    (merged_spmv.h:92-151: getitem / clone / copy_ on boundary points): gathers a vertex tensor and
+    writes it through an input pointer (copy_), no allocated output.  Valid for integer ValueT."""
+    inputs = [placeholder("dst", (2,)), placeholder("src", (2,)), selector_input("sel", "src", (2,))]
+    selreg = [edge_register("dst", (2,)), gather_register("sel", "src", (2,))]
+    m = [mop("c", "clone", (2,), "sel"), mop("cp", "copy_", (2,), "dst", "c")]
+    return _finish("edge_copy", inputs, [], selreg, m, edge_copy_graph.__doc__)
+
+
+ALL_GRAPHS = {
+    "spmv": spmv_graph,
+    "spring_mass": spring_mass_graph,
+    "rusanov": rusanov_graph,
+    "mixed_dims": mixed_dims_graph,
+    "ops_zoo": ops_zoo_graph,
+    "edge_sum": edge_sum_graph,
+    "edge_copy": edge_copy_graph,
+}
+
+# value types each graph is compiled for (one C-ABI symbol per pair)
+GRAPH_DTYPES = {
+    "spmv": ("float32", "float64", "int64"),
+    "spring_mass": ("float32", "float64"),
+    "rusanov": ("float64", "float32"),
+    "mixed_dims": ("float32", "float64", "int64"),
+    "ops_zoo": ("float32", "float64"),
+    "edge_sum": ("float32", "float64", "int64"),
+    "edge_copy": ("float32", "float64", "int64"),
+}
+
+
+def operator_signature(ir: GraphIR):
+    """Positional argument order of the operator, as the reference's binding generator derives it
+    (codegen/merged_gen_binding.py:27-78): non-gather value inputs, gather value inputs (first-use
+    order, de-duplicated), one index tensor per distinct selector target, then row_end_offsets,
+    num_rows, num_cols.  Returns (value_names, gather_names, index_names)."""
+    gather_targets = {s["target"] for s in ir.selector_register if s.get("selector") == 1}
+    value_inputs = [i for i in ir.inputs if i["dtype"] != "int"]
+    seen, sel_inputs = set(), []
+    for i in ir.inputs:
+        if i["dtype"] == "int" and i["target"] not in seen:
+            sel_inputs.append(i)
+            seen.add(i["target"])
+    non_gather = [i["name"] for i in value_inputs if i["name"] not in gather_targets]
+    gathers, seen_g = [], set()
+    for i in ir.inputs:
+        if i["op"] == "call_module" and i["args"][0].name in gather_targets and i["args"][0].name not in seen_g:
+            gathers.append(i["args"][0].name)
+            seen_g.add(i["args"][0].name)
+    return non_gather, gathers, [s["target"] for s in sel_inputs]

@@ -1,0 +1,270 @@
+"""Seeded synthetic problems for the five benchmark configurations and for the unit tests.
+
+The reference measures on no public data set: its harnesses draw a seeded random CSR problem
+(src/flex_spmv_full_red.cu:391-427, main.cpp:126-176).  The generators here produce the matrices,
+meshes and states the benchmark configurations describe; every one takes its size as a parameter so
+the same code feeds small parity cases and the full-size benchmark.  All host generators use
+``numpy.random.default_rng(seed)`` and return plain numpy arrays (identical arrays go to the CPU
+oracle and to the GPU).  ``*_device`` variants build the two largest problems directly in GPU memory
+with torch (same distributions, torch's generator) because shipping 2-15 GB from the host would
+dominate a benchmark run.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import numpy as np
+
+
+@dataclass
+class Problem:
+    """Inputs of one operator call, in the reference IR's naming.
+
+    ``values``  name -> array (num_edges, dim) or (num_vertices, dim) (dim==1 arrays are 1-D)
+    ``indices`` selector target name -> int32 (num_edges,)
+    ``row_offsets`` CSR offsets with the leading 0 (length num_rows+1), int32 or int64
+    """
+    graph: str
+    values: Dict[str, np.ndarray]
+    indices: Dict[str, np.ndarray]
+    row_offsets: Optional[np.ndarray]
+    num_rows: int
+    num_cols: int
+    meta: Dict[str, object] = field(default_factory=dict)
+
+    @property
+    def nnz(self) -> int:
+        return int(next(iter(self.indices.values())).shape[0])
+
+
+# ----------------------------------------------------------------------------------------------
+# config 0 / config 4: Poisson stencils
+# ----------------------------------------------------------------------------------------------
+
+def poisson2d(n: int = 512, seed: int = 0, dtype=np.float64) -> Problem:
+    """5-point Laplacian on an n x n grid, Dirichlet (out-of-grid neighbours dropped), CSR sorted,
+    4.0 on the diagonal and -1.0 off it; x ~ U(-1,1)."""
+    idx = np.arange(n * n, dtype=np.int64)
+    i, j = idx // n, idx % n
+    cand_col = np.stack([idx - n, idx - 1, idx, idx + 1, idx + n], axis=1)
+    valid = np.stack([i > 0, j > 0, np.ones_like(i, bool), j < n - 1, i < n - 1], axis=1)
+    cand_val = np.broadcast_to(np.array([-1.0, -1.0, 4.0, -1.0, -1.0]), cand_col.shape)
+    counts = valid.sum(axis=1)
+    ro = np.zeros(n * n + 1, dtype=np.int32)
+    np.cumsum(counts, out=ro[1:])
+    cols = cand_col[valid].astype(np.int32)
+    vals = cand_val[valid].astype(dtype)
+    x = np.random.default_rng(seed).uniform(-1.0, 1.0, n * n).astype(dtype)
+    return Problem("spmv", {"vals": vals, "x": x}, {"selector": cols}, ro, n * n, n * n,
+                   {"config": 0, "grid": n})
+
+
+def poisson3d(n: int = 512, seed: int = 4, dtype=np.float64, offset_dtype=np.int64,
+              z_begin: int = 0, z_end: Optional[int] = None) -> Problem:
+    """7-point Laplacian on an n^3 grid (x fastest), Dirichlet, 6.0 / -1.0, rows of z-planes
+    [z_begin, z_end); column indices are global.  x ~ U(-1,1) over the whole grid."""
+    z_end = n if z_end is None else z_end
+    n2 = n * n
+    idx = np.arange(z_begin * n2, z_end * n2, dtype=np.int64)
+    k, r = idx // n2, idx % n2
+    j, i = r // n, r % n
+    cand_col = np.stack([idx - n2, idx - n, idx - 1, idx, idx + 1, idx + n, idx + n2], axis=1)
+    valid = np.stack([k > 0, j > 0, i > 0, np.ones_like(i, bool), i < n - 1, j < n - 1, k < n - 1], axis=1)
+    cand_val = np.broadcast_to(np.array([-1.0, -1.0, -1.0, 6.0, -1.0, -1.0, -1.0]), cand_col.shape)
+    ro = np.zeros(idx.shape[0] + 1, dtype=offset_dtype)
+    np.cumsum(valid.sum(axis=1), out=ro[1:])
+    cols = cand_col[valid].astype(np.int32)
+    vals = cand_val[valid].astype(dtype)
+    x = np.random.default_rng(seed).uniform(-1.0, 1.0, n ** 3).astype(dtype)
+    return Problem("spmv", {"vals": vals, "x": x}, {"selector": cols}, ro, idx.shape[0], n ** 3,
+                   {"config": 4, "grid": n, "z_begin": z_begin, "z_end": z_end})
+
+
+# ----------------------------------------------------------------------------------------------
+# config 1: spring-mass lattice
+# ----------------------------------------------------------------------------------------------
+
+def spring_mass(n: int = 1024, seed: int = 1, dtype=np.float32) -> Problem:
+    """n x n particle lattice, 8-neighbour directed edges stored CSR by source vertex.
+    p = grid*h + U(-0.2h, 0.2h), h = 1/n; L_e = |p_i - p_j| * U(0.9, 1.1); k_e ~ U(0.5, 2.0)
+    (rng draw order: jitter, L factors, k)."""
+    rng = np.random.default_rng(seed)
+    h = 1.0 / n
+    idx = np.arange(n * n, dtype=np.int64)
+    i, j = idx // n, idx % n
+    p = np.stack([j * h, i * h], axis=1) + rng.uniform(-0.2 * h, 0.2 * h, (n * n, 2))
+    p = p.astype(dtype)
+    offs = [(-1, -1), (-1, 0), (-1, 1), (0, -1), (0, 1), (1, -1), (1, 0), (1, 1)]
+    cand = np.stack([(i + di) * n + (j + dj) for di, dj in offs], axis=1)
+    valid = np.stack([((i + di) >= 0) & ((i + di) < n) & ((j + dj) >= 0) & ((j + dj) < n) for di, dj in offs], axis=1)
+    ro = np.zeros(n * n + 1, dtype=np.int32)
+    np.cumsum(valid.sum(axis=1), out=ro[1:])
+    dst = cand[valid].astype(np.int32)
+    src = np.repeat(idx, valid.sum(axis=1)).astype(np.int32)
+    d0 = p[dst].astype(np.float64) - p[src].astype(np.float64)
+    L = (np.sqrt((d0 * d0).sum(axis=1)) * rng.uniform(0.9, 1.1, dst.shape[0])).astype(dtype)
+    k = rng.uniform(0.5, 2.0, dst.shape[0]).astype(dtype)
+    return Problem("spring_mass", {"L": L, "k": k, "p": p}, {"sel_src": src, "sel_dst": dst}, ro,
+                   n * n, n * n, {"config": 1, "grid": n})
+
+
+# ----------------------------------------------------------------------------------------------
+# config 2: shallow water on a triangulated square
+# ----------------------------------------------------------------------------------------------
+
+def shallow_water(n: int = 1024, dtype=np.float64) -> Problem:
+    """n x n unit squares each split along the (0,0)-(1,1) diagonal into a lower (L: corners
+    (0,0),(1,0),(1,1)) and an upper (U: (0,0),(1,1),(0,1)) triangle -> 2 n^2 cells, 3 faces per cell.
+    Cell id = 2*(iy*n+ix) + {0: L, 1: U}.  Boundary faces are kept as self-edges (neighbour = the
+    cell itself), which for the zero-velocity initial state gives the reflective-wall flux.
+    State U = (h, hu, hv), h = 1 + 0.1 exp(-((x-.5)^2 + (y-.5)^2)/0.01) at centroids, hu = hv = 0.
+    Face data per edge: outward unit normal (nx, ny) and face length.  Deterministic (no rng)."""
+    hs = 1.0 / n
+    sq = np.arange(n * n, dtype=np.int64)
+    iy, ix = sq // n, sq % n
+    cl, cu = 2 * sq, 2 * sq + 1
+    r2 = np.sqrt(0.5)
+    # lower triangle faces: bottom (normal 0,-1) -> U of square below; right (1,0) -> U of square to
+    # the right; diagonal (normal (-1,1)/sqrt2) -> U of same square
+    nb_l = np.stack([np.where(iy > 0, 2 * (sq - n) + 1, cl), np.where(ix < n - 1, 2 * (sq + 1) + 1, cl), cu], axis=1)
+    # upper triangle faces: diagonal (normal (1,-1)/sqrt2) -> L of same square; top (0,1) -> L of the
+    # square above; left (-1,0) -> L of square to the left
+    nb_u = np.stack([cl, np.where(iy < n - 1, 2 * (sq + n), cu), np.where(ix > 0, 2 * (sq - 1), cu)], axis=1)
+    nbr = np.empty((2 * n * n, 3), dtype=np.int64)
+    nbr[0::2], nbr[1::2] = nb_l, nb_u
+    face_l = np.array([[0.0, -1.0, hs], [1.0, 0.0, hs], [-r2, r2, hs * np.sqrt(2.0)]])
+    face_u = np.array([[r2, -r2, hs * np.sqrt(2.0)], [0.0, 1.0, hs], [-1.0, 0.0, hs]])
+    face = np.empty((2 * n * n, 3, 3))
+    face[0::2], face[1::2] = face_l, face_u
+    cx = np.empty(2 * n * n)
+    cy = np.empty(2 * n * n)
+    cx[0::2], cy[0::2] = (ix + 2.0 / 3.0) * hs, (iy + 1.0 / 3.0) * hs
+    cx[1::2], cy[1::2] = (ix + 1.0 / 3.0) * hs, (iy + 2.0 / 3.0) * hs
+    hgt = 1.0 + 0.1 * np.exp(-((cx - 0.5) ** 2 + (cy - 0.5) ** 2) / 0.01)
+    U = np.stack([hgt, np.zeros_like(hgt), np.zeros_like(hgt)], axis=1).astype(dtype)
+    cells = 2 * n * n
+    ro = (3 * np.arange(cells + 1, dtype=np.int64)).astype(np.int32)
+    self_idx = np.repeat(np.arange(cells, dtype=np.int32), 3)
+    return Problem("rusanov", {"face": face.reshape(-1, 3).astype(dtype), "U": U},
+                   {"sel_self": self_idx, "sel_nbr": nbr.reshape(-1).astype(np.int32)}, ro, cells, cells,
+                   {"config": 2, "grid": n})
+
+
+# ----------------------------------------------------------------------------------------------
+# config 3: power-law CSR
+# ----------------------------------------------------------------------------------------------
+
+def powerlaw_row_lengths(n: int, rng, mean_len: float = 16.0, cap: int = 100_000) -> np.ndarray:
+    """raw = min(floor(1/(1-u)), cap), u ~ U[0,1)  (discrete power law, exponent 2, min 1);
+    len = clip(round(raw * mean_len / mean(raw)), 1, cap)."""
+    u = rng.random(n)
+    raw = np.minimum(np.floor(1.0 / (1.0 - u)), cap)
+    ln = np.clip(np.rint(raw * (mean_len / raw.mean())), 1, cap).astype(np.int64)
+    return ln
+
+
+def powerlaw(n: int = 1 << 24, seed: int = 3, dtype=np.float32, mean_len: float = 16.0,
+             cap: int = 100_000) -> Problem:
+    """n x n CSR, power-law row lengths, uniform random columns sorted within each row, values
+    N(0,1), x ~ U(-1,1) (rng draw order: lengths, columns, values, x)."""
+    rng = np.random.default_rng(seed)
+    ln = powerlaw_row_lengths(n, rng, mean_len, min(cap, n))
+    ro = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(ln, out=ro[1:])
+    m = int(ro[-1])
+    cols = rng.integers(0, n, m, dtype=np.int64)
+    rows = np.repeat(np.arange(n, dtype=np.int64), ln)
+    key = np.sort((rows << 32) | cols)
+    cols = (key & 0xFFFFFFFF).astype(np.int32)
+    vals = rng.standard_normal(m).astype(dtype)
+    x = rng.uniform(-1.0, 1.0, n).astype(dtype)
+    assert m < 2 ** 31
+    return Problem("spmv", {"vals": vals, "x": x}, {"selector": cols}, ro.astype(np.int32), n, n,
+                   {"config": 3})
+
+
+# ----------------------------------------------------------------------------------------------
+# the reference harness' random problem (unit tests)
+# ----------------------------------------------------------------------------------------------
+
+def random_cut_csr(num_rows: int, nnz: int, rng) -> np.ndarray:
+    """Row offsets = sorted random cut points, so empty rows and long rows both occur
+    (the idea of src/flex_spmv_full_red.cu:391-427)."""
+    cuts = np.sort(rng.integers(0, nnz + 1, max(num_rows - 1, 0)))
+    ro = np.concatenate([[0], cuts, [nnz]]).astype(np.int32)
+    return ro[: num_rows + 1] if num_rows > 0 else np.array([0], np.int32)
+
+
+def random_problem(graph_ir, num_rows: int, num_vertices: int, nnz: int, seed: int, dtype,
+                   integer_range: int = 7) -> Problem:
+    """Random inputs for any graph IR: vertex tensors (num_vertices, dim), edge tensors (nnz, dim),
+    selector indices uniform in [0, num_vertices), random cut-point CSR.  Row-identity selectors get
+    the expanded row ids (and num_vertices is then forced to num_rows)."""
+    from .graphs import dim_of
+    rng = np.random.default_rng(seed)
+    ro = random_cut_csr(num_rows, nnz, rng)
+    is_int = np.issubdtype(np.dtype(dtype), np.integer)
+    gather_src = {s["target"] for s in graph_ir.selector_register if s.get("selector") == 1}
+    values, indices = {}, {}
+
+    def draw(shape):
+        if is_int:
+            return rng.integers(-integer_range, integer_range + 1, shape).astype(dtype)
+        a = rng.uniform(-1.0, 1.0, shape)
+        a[rng.random(shape) < 0.02] = 0.0   # exact zeros exercise the guarded divide
+        return a.astype(dtype)
+
+    for inp in graph_ir.inputs:
+        if inp["dtype"] == "int":
+            continue
+        d = dim_of(inp["shape"])
+        rows = num_vertices if inp["name"] in gather_src else nnz
+        a = draw((rows, d))
+        values[inp["name"]] = a[:, 0].copy() if d == 1 else a
+    for s in graph_ir.selector_register:
+        if s.get("selector") != 1 or s["selector_name"] in indices:
+            continue
+        if s.get("row_identity"):
+            assert num_vertices == num_rows
+            indices[s["selector_name"]] = np.repeat(np.arange(num_rows, dtype=np.int32), np.diff(ro))
+        else:
+            indices[s["selector_name"]] = rng.integers(0, num_vertices, nnz).astype(np.int32)
+    return Problem(graph_ir.name, values, indices, ro if graph_ir.has_reducer else None, num_rows,
+                   num_vertices, {"seed": seed})
+
+
+# ----------------------------------------------------------------------------------------------
+# algorithmic bytes
+# ----------------------------------------------------------------------------------------------
+
+def algorithmic_bytes(graph_ir, num_rows: int, nnz: int, num_vertices: int, value_bytes: int,
+                      offset_bytes: int = 4) -> int:
+    """Every compulsory array counted once (the reference's effective-bandwidth formula,
+    src/flex_spmv_full_red.cu:347-359):  nnz*(4 per streamed index + V*sum(edge dims)) +
+    (rows+1)*R + sum over gather sources V*dim*vertices + rows*V*sum(reducer dims) +
+    nnz*V*dim per stored per-edge output.  A row-identity selector is derivable from the row
+    offsets and is not counted."""
+    from .graphs import dim_of
+    b = 0
+    seen_idx = set()
+    for s in graph_ir.selector_register:
+        if s.get("selector") == 1:
+            if not s.get("row_identity") and s["selector_name"] not in seen_idx:
+                b += 4 * nnz
+                seen_idx.add(s["selector_name"])
+        else:
+            b += value_bytes * dim_of(s["shape"]) * nnz
+    for src in {s["target"]: s for s in graph_ir.selector_register if s.get("selector") == 1}.values():
+        b += value_bytes * dim_of(src["shape"]) * num_vertices
+    if graph_ir.has_reducer:
+        b += (num_rows + 1) * offset_bytes
+    for o in graph_ir.outputs:
+        d = dim_of(o["shape"])
+        if str(o["target"]) == "reducer":
+            b += value_bytes * d * num_rows
+        elif "sum" in str(o["target"]):
+            b += value_bytes * d
+        else:
+            b += value_bytes * d * nnz
+    return b

@@ -1,0 +1,170 @@
+/*
+ * CPU ORACLE -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * Plain-C restatement of the reference's CPU algorithm for the fused gather-map-reduce path, used
+ * only as the checker in tests, in the smoke check and as the timed "port" CPU baseline.  The
+ * product (the CUDA library) never links, loads or calls anything in this file.
+ *
+ * What is restated, with the reference location each function follows:
+ *   merge_path_search_*   MergePathSearch          cpu_template/merged_spmv_template_reducer.h:27-51
+ *                                                  (same arithmetic as include/merged_spmv_kernels.cuh:19-50)
+ *   omp_merge_reduce_*    OmpMergeSystem (reducer) cpu_template/merged_spmv_template_reducer.h:92-169
+ *                         + ApplyCarryOutFixup     cpu_template/merged_spmv_template_reducer.h:56-70
+ *   omp_merge_sum_*       OmpMergeSystem (aggregator) cpu_template/merged_spmv_template_aggregator.h:92-136
+ *                         + ApplyCarryOutFixup     cpu_template/merged_spmv_template_aggregator.h:75-87
+ *   tile_coordinates_*    SpmvSearchKernel         include/merged_spmv_kernels.cuh:60-99
+ *   nnz_balanced_row_blocks  (no reference counterpart: multi-GPU row split, lower_bound on offsets)
+ *
+ * The per-edge map itself (Tensor arithmetic, data_struct_shared.cuh) is restated in ir_eval.py;
+ * the functions here take the already-mapped per-edge values (num_edges x dim, row-major) and
+ * reproduce the reference's summation ORDER: `num_threads` equal merge-path spans, every whole row
+ * summed left to right from zero and ASSIGNED, the trailing partial row of each span carried out
+ * and added afterwards in thread order.  "Threads" are iterated sequentially here; the result is
+ * identical to the OpenMP run because spans do not interact before the fix-up.
+ *
+ * Parity pin: checked against the reference's own generated code compiled from its sources
+ * (oracle/_ref, see ref_build.py) in tests/test_oracle_vs_ref.py and against tests/golden/.
+ */
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ---- MergePathSearch: a = row END offsets (leading 0 already skipped), b = 0,1,2,... ---------- */
+void merge_path_search_i32(int32_t diagonal, const int32_t *a, int32_t a_len, int32_t b_len,
+                           int32_t *out_x, int32_t *out_y) {
+  int32_t x_min = diagonal - b_len > 0 ? diagonal - b_len : 0;
+  int32_t x_max = diagonal < a_len ? diagonal : a_len;
+  while (x_min < x_max) {
+    int32_t pivot = (x_min + x_max) >> 1;
+    if (a[pivot] <= diagonal - pivot - 1) x_min = pivot + 1;
+    else x_max = pivot;
+  }
+  *out_x = x_min < a_len ? x_min : a_len;
+  *out_y = diagonal - x_min;
+}
+
+/* 64-bit flavour (the reference is int-only; needed for int64 row offsets / rows+nnz >= 2^31). */
+void merge_path_search_i64(int64_t diagonal, const int64_t *a, int64_t a_len, int64_t b_len,
+                           int64_t *out_x, int64_t *out_y) {
+  int64_t x_min = diagonal - b_len > 0 ? diagonal - b_len : 0;
+  int64_t x_max = diagonal < a_len ? diagonal : a_len;
+  while (x_min < x_max) {
+    int64_t pivot = (x_min + x_max) >> 1;
+    if (a[pivot] <= diagonal - pivot - 1) x_min = pivot + 1;
+    else x_max = pivot;
+  }
+  *out_x = x_min < a_len ? x_min : a_len;
+  *out_y = diagonal - x_min;
+}
+
+/* tile_idx -> coordinate of diagonal tile_idx*tile_items, for tile_idx in [0, num_tiles]
+ * (SpmvSearchKernel).  row_offsets has the leading 0; coords is (num_tiles+1) x 2 (row, nz). */
+void tile_coordinates_i32(const int32_t *row_offsets, int32_t num_rows, int32_t nnz,
+                          int32_t tile_items, int32_t num_tiles, int32_t *coords) {
+  for (int32_t t = 0; t <= num_tiles; ++t) {
+    int64_t d = (int64_t)t * tile_items;
+    int64_t total = (int64_t)num_rows + nnz;
+    if (d > total) d = total;
+    merge_path_search_i32((int32_t)d, row_offsets + 1, num_rows, nnz, &coords[2 * t], &coords[2 * t + 1]);
+  }
+}
+
+void tile_coordinates_i64(const int64_t *row_offsets, int64_t num_rows, int64_t nnz,
+                          int64_t tile_items, int64_t num_tiles, int64_t *coords) {
+  for (int64_t t = 0; t <= num_tiles; ++t) {
+    int64_t d = t * tile_items;
+    if (d > num_rows + nnz) d = num_rows + nnz;
+    merge_path_search_i64(d, row_offsets + 1, num_rows, nnz, &coords[2 * t], &coords[2 * t + 1]);
+  }
+}
+
+/* nnz-balanced contiguous row blocks: first_row[k] = lower_bound(row_offsets, k*nnz/parts),
+ * rounded up to a multiple of `snap` rows (snap=1: none). first_row has parts+1 entries. */
+void nnz_balanced_row_blocks(const int64_t *row_offsets, int64_t num_rows, int32_t parts,
+                             int64_t snap, int64_t *first_row) {
+  int64_t nnz = row_offsets[num_rows];
+  first_row[0] = 0;
+  for (int32_t k = 1; k < parts; ++k) {
+    int64_t target = (int64_t)(((__int128)nnz * k) / parts);
+    int64_t lo = 0, hi = num_rows;
+    while (lo < hi) {
+      int64_t mid = (lo + hi) >> 1;
+      if (row_offsets[mid] < target) lo = mid + 1; else hi = mid;
+    }
+    if (snap > 1) lo = ((lo + snap / 2) / snap) * snap;
+    if (lo > num_rows) lo = num_rows;
+    if (lo < first_row[k - 1]) lo = first_row[k - 1];
+    first_row[k] = lo;
+  }
+  first_row[parts] = num_rows;
+}
+
+/* ---- OmpMergeSystem, reducer flavour ----------------------------------------------------------- */
+#define DEFINE_REDUCE(NAME, T)                                                                      \
+  void NAME(int num_threads, const int32_t *row_offsets, const T *edge_vals, int dim, int num_rows, \
+            int nnz, T *y) {                                                                        \
+    const int32_t *row_end = row_offsets + 1;                                                       \
+    int32_t *carry_row = (int32_t *)malloc(sizeof(int32_t) * (size_t)num_threads);                  \
+    T *carry_val = (T *)calloc((size_t)num_threads * (size_t)dim, sizeof(T));                       \
+    T *total = (T *)malloc(sizeof(T) * (size_t)dim);                                                \
+    int32_t items = num_rows + nnz;                                                                 \
+    int32_t per = (items + num_threads - 1) / num_threads;                                          \
+    for (int tid = 0; tid < num_threads; ++tid) {                                                   \
+      int32_t d0 = per * tid < items ? per * tid : items;                                           \
+      int32_t d1 = d0 + per < items ? d0 + per : items;                                             \
+      int32_t x, yy, xe, ye;                                                                        \
+      merge_path_search_i32(d0, row_end, num_rows, nnz, &x, &yy);                                   \
+      merge_path_search_i32(d1, row_end, num_rows, nnz, &xe, &ye);                                  \
+      for (; x < xe; ++x) {                                                                         \
+        for (int i = 0; i < dim; ++i) total[i] = 0;                                                 \
+        for (; yy < row_end[x]; ++yy)                                                               \
+          for (int i = 0; i < dim; ++i) total[i] += edge_vals[(size_t)yy * dim + i];                \
+        for (int i = 0; i < dim; ++i) y[(size_t)x * dim + i] = total[i];                            \
+      }                                                                                             \
+      for (int i = 0; i < dim; ++i) total[i] = 0;                                                   \
+      for (; yy < ye; ++yy)                                                                         \
+        for (int i = 0; i < dim; ++i) total[i] += edge_vals[(size_t)yy * dim + i];                  \
+      carry_row[tid] = xe;                                                                          \
+      for (int i = 0; i < dim; ++i) carry_val[(size_t)tid * dim + i] = total[i];                    \
+    }                                                                                               \
+    for (int tid = 0; tid < num_threads - 1; ++tid)                                                 \
+      if (carry_row[tid] < num_rows)                                                                \
+        for (int i = 0; i < dim; ++i)                                                               \
+          y[(size_t)carry_row[tid] * dim + i] += carry_val[(size_t)tid * dim + i];                  \
+    free(carry_row); free(carry_val); free(total);                                                  \
+  }
+
+DEFINE_REDUCE(omp_merge_reduce_f32, float)
+DEFINE_REDUCE(omp_merge_reduce_f64, double)
+DEFINE_REDUCE(omp_merge_reduce_i64, int64_t)
+
+/* ---- OmpMergeSystem, aggregator flavour: edges split by ceil((rows+nnz)/T) per thread ---------- */
+#define DEFINE_SUM(NAME, T)                                                                         \
+  void NAME(int num_threads, const T *edge_vals, int dim, int num_rows, int nnz, T *out) {          \
+    T *part = (T *)calloc((size_t)num_threads * (size_t)dim, sizeof(T));                            \
+    int32_t items = num_rows + nnz;                                                                 \
+    int32_t per = (items + num_threads - 1) / num_threads;                                          \
+    for (int tid = 0; tid < num_threads; ++tid) {                                                   \
+      int64_t e0 = (int64_t)tid * per;                                                              \
+      int64_t e1 = e0 + per < nnz ? e0 + per : nnz;                                                 \
+      for (int64_t e = e0; e < e1; ++e)                                                             \
+        for (int i = 0; i < dim; ++i) part[(size_t)tid * dim + i] += edge_vals[(size_t)e * dim + i];\
+    }                                                                                               \
+    for (int i = 0; i < dim; ++i) out[i] = 0;                                                       \
+    for (int tid = 0; tid < num_threads; ++tid)                                                     \
+      for (int i = 0; i < dim; ++i) out[i] += part[(size_t)tid * dim + i];                          \
+    free(part);                                                                                     \
+  }
+
+DEFINE_SUM(omp_merge_sum_f32, float)
+DEFINE_SUM(omp_merge_sum_f64, double)
+DEFINE_SUM(omp_merge_sum_i64, int64_t)
+
+/* sum_j |term_ij| per row in double, the normaliser of the per-row parity tolerance */
+void row_abs_sum_f64(const int32_t *row_offsets, const double *abs_terms, int dim, int num_rows, double *out) {
+  for (int r = 0; r < num_rows; ++r) {
+    for (int i = 0; i < dim; ++i) out[(size_t)r * dim + i] = 0.0;
+    for (int32_t e = row_offsets[r]; e < row_offsets[r + 1]; ++e)
+      for (int i = 0; i < dim; ++i) out[(size_t)r * dim + i] += abs_terms[(size_t)e * dim + i];
+  }
+}
