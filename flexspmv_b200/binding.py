@@ -1,0 +1,239 @@
+"""The operator the reference's runtime wrapper calls: ``ext.merged_spmv_launch(*args)``.
+
+The reference JIT-builds one pybind11 torch extension per fused graph whose single function
+``merged_spmv_launch`` (cuda_template/merged_binding_template.cu:73-80) takes, positionally
+(codegen/merged_gen_binding.py:65-78): the non-gather value inputs, the gather value inputs, one int32
+index tensor per selector target, ``row_end_offsets`` (leading 0 included), ``num_rows``,
+``num_cols`` -- and returns a tuple of freshly allocated outputs (or None when the graph has none).
+``GraphExtension`` is that object for this library: same function name, argument order, keyword
+names, checks and return convention; behind it a ctypes call into the C ABI of
+libflexspmv_b200.so (include/flexspmv.h) on torch's current CUDA stream.  PyTorch provides device
+memory and the stream, nothing else.
+
+Differences from the reference binding, all on the host side of the same contract:
+  * outputs are ``torch.empty`` (the kernels write every element; the reference needs torch::zeros
+    because it accumulates with atomicAdd), scratch comes from torch's caching allocator instead of a
+    per-call cudaMalloc/cudaFree (cuda_template/merged_binding_template.cu:42-49);
+  * the merge-path partition is planned once per (row_end_offsets tensor, version) and cached;
+  * int64 ``row_end_offsets`` are accepted as they are (the reference casts to int32);
+  * an unsupported dtype raises (the reference prints to stderr and falls off the end of a non-void
+    function, cuda_template/merged_binding_template.cu:65-68).
+
+There is no CPU path: a missing library or a CPU tensor is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from collections import OrderedDict
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .graphs import GraphIR, dim_of, operator_signature
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+DEFAULT_LIB = os.path.join(_PKG, "lib", "libflexspmv_b200.so")
+
+_SFX = {torch.float32: "f32", torch.float64: "f64", torch.int64: "i64"}
+
+
+class Desc(ctypes.Structure):
+    _fields_ = [("num_rows", ctypes.c_int64), ("num_edges", ctypes.c_int64), ("num_vertices", ctypes.c_int64),
+                ("offset_bits", ctypes.c_int32), ("tile_items", ctypes.c_int32), ("max_ctas", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
+
+
+class GraphInfo(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("num_values", "num_indices", "num_outputs", "has_reducer", "value_bytes", "default_tile_items",
+                 "block_threads", "items_per_thread", "stages", "smem_bytes", "acc_dim", "reserved")]
+
+
+class FlexSpmvError(RuntimeError):
+    pass
+
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+
+def load_library(path: Optional[str] = None) -> ctypes.CDLL:
+    """dlopen the C-ABI library; raises when it is missing (no fallback of any kind)."""
+    path = os.path.abspath(path or os.environ.get("FLEXSPMV_LIB", DEFAULT_LIB))
+    if path not in _libs:
+        if not os.path.exists(path):
+            raise FlexSpmvError(f"{path} not found: build it with `python -m flexspmv_b200.build` "
+                                "(there is no CPU or eager fallback)")
+        lib = ctypes.CDLL(path)
+        lib.flexspmv_error_string.restype = ctypes.c_char_p
+        lib.flexspmv_error_string.argtypes = [ctypes.c_int]
+        _libs[path] = lib
+    return _libs[path]
+
+
+def check(lib, status: int, what: str):
+    if status != 0:
+        raise FlexSpmvError(f"{what} failed: {lib.flexspmv_error_string(status).decode()} (status {status})")
+
+
+def _stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _Symbols:
+    def __init__(self, lib, sym: str):
+        def fn(name):
+            try:
+                f = getattr(lib, f"flexspmv_{sym}_{name}")
+            except AttributeError as e:
+                raise FlexSpmvError(f"library has no graph '{sym}' (symbol flexspmv_{sym}_{name})") from e
+            f.restype = ctypes.c_int
+            return f
+        self.info, self.workspace_bytes, self.plan = fn("info"), fn("workspace_bytes"), fn("plan")
+        self.launch, self.device_status = fn("launch"), fn("device_status")
+        gi = GraphInfo()
+        check(lib, self.info(ctypes.byref(gi)), f"{sym}_info")
+        self.graph_info = gi
+
+
+class GraphExtension:
+    """Drop-in for the module object ``torch.utils.cpp_extension.load`` returns in the reference flow
+    (test_full/easier_full.py:359-373): exposes ``merged_spmv_launch``."""
+
+    PLAN_CACHE_ENTRIES = 8
+
+    def __init__(self, ir: GraphIR, lib_path: Optional[str] = None, symbol_prefix: Optional[str] = None,
+                 tile_items: int = 0, max_ctas: int = 0):
+        self.ir = ir
+        self.lib = load_library(lib_path)
+        self.prefix = symbol_prefix or ir.name
+        self.tile_items, self.max_ctas = int(tile_items), int(max_ctas)
+        self.non_gather, self.gathers, self.index_names = operator_signature(ir)
+        self.value_names = self.non_gather + self.gathers
+        self.arg_names = self.value_names + [n + "_idx" for n in self.index_names] + \
+            ["row_end_offsets", "num_rows", "num_cols"]
+        self._syms: Dict[str, _Symbols] = {}
+        self._plans: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self.launches = 0    # kernels this object enqueued (plan kernels included)
+
+    # -- helpers ----------------------------------------------------------------------------------
+    def symbols(self, dtype: torch.dtype) -> _Symbols:
+        if dtype not in _SFX:
+            raise FlexSpmvError(f"Unsupported dtype for ValueT: {dtype}. Use float32, float64 or int64.")
+        sfx = _SFX[dtype]
+        if sfx not in self._syms:
+            self._syms[sfx] = _Symbols(self.lib, f"{self.prefix}_{sfx}")
+        return self._syms[sfx]
+
+    def _bind(self, args, kwargs) -> list:
+        if len(args) > len(self.arg_names):
+            raise TypeError(f"merged_spmv_launch() takes {len(self.arg_names)} arguments ({len(args)} given)")
+        vals = list(args)
+        for n in self.arg_names[len(args):]:
+            if n not in kwargs:
+                raise TypeError(f"merged_spmv_launch() missing argument '{n}'")
+            vals.append(kwargs[n])
+        extra = set(kwargs) - set(self.arg_names[len(args):])
+        if extra:
+            raise TypeError(f"merged_spmv_launch() got unexpected keyword arguments {sorted(extra)}")
+        return vals
+
+    def _workspace(self, syms: _Symbols, desc: Desc, ro: Optional[torch.Tensor], device) -> Tuple[torch.Tensor, int]:
+        key = (id(syms), desc.num_rows, desc.num_edges, desc.offset_bits, desc.tile_items, desc.max_ctas,
+               (ro.data_ptr(), ro._version) if ro is not None else None, device.index)
+        hit = self._plans.get(key)
+        if hit is not None:
+            self._plans.move_to_end(key)
+            return hit[0], hit[1]
+        nbytes = ctypes.c_size_t()
+        check(self.lib, syms.workspace_bytes(ctypes.byref(desc), ctypes.byref(nbytes)), "workspace_bytes")
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=device)
+        check(self.lib, syms.plan(ctypes.byref(desc), ctypes.c_void_p(ro.data_ptr() if ro is not None else 0),
+                                  ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(nbytes.value), _stream_ptr()),
+              "plan")
+        self.launches += 2 if ro is not None else 1
+        # keep the row-offset tensor alive so its address cannot be recycled under a cached plan
+        self._plans[key] = (ws, nbytes.value, ro)
+        while len(self._plans) > self.PLAN_CACHE_ENTRIES:
+            self._plans.popitem(last=False)
+        return ws, nbytes.value
+
+    # -- the operator --------------------------------------------------------------------------------
+    def merged_spmv_launch(self, *args, **kwargs):
+        a = self._bind(args, kwargs)
+        nv, ni = len(self.value_names), len(self.index_names)
+        values: List[torch.Tensor] = a[:nv]
+        indices: List[torch.Tensor] = a[nv:nv + ni]
+        row_end_offsets, num_rows, num_cols = a[nv + ni], int(a[nv + ni + 1]), int(a[nv + ni + 2])
+        for n, t in zip(self.arg_names, values + indices + [row_end_offsets]):
+            if not isinstance(t, torch.Tensor):
+                raise TypeError(f"{n} must be a torch.Tensor")
+            if not t.is_cuda:
+                raise FlexSpmvError(f"{n} must be a CUDA tensor")
+            if not t.is_contiguous():
+                raise FlexSpmvError(f"{n} must be contiguous")
+        dispatch = values[0]
+        dt = dispatch.dtype
+        syms = self.symbols(dt)
+        for n, t in zip(self.value_names, values):
+            if t.dtype != dt:
+                raise FlexSpmvError(f"{n} dtype mismatch")
+        for n, t in zip(self.index_names, indices):
+            if t.dtype != torch.int32:
+                raise FlexSpmvError(f"{n}_idx dtype mismatch")
+        ne = int(indices[0].numel()) if indices else num_cols
+        if ne <= 0:
+            raise FlexSpmvError("selector index must be non-empty")
+        has_red = self.ir.has_reducer
+        if has_red:
+            if row_end_offsets.dtype not in (torch.int32, torch.int64):
+                raise FlexSpmvError("row_end_offsets dtype mismatch")
+            if row_end_offsets.numel() != num_rows + 1:
+                raise FlexSpmvError("row_end_offsets must have length num_rows + 1")
+        device = dispatch.device
+        desc = Desc(num_rows if has_red else 0, ne, num_cols,
+                    64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
+                    self.tile_items, self.max_ctas, 0)
+        outputs: List[torch.Tensor] = []
+        for o in self.ir.outputs:
+            d = dim_of(o["shape"])
+            tgt = str(o["target"])
+            if tgt == "reducer":
+                shape = (num_rows,) if d == 1 else (num_rows, d)
+            elif "sum" in tgt:
+                shape = (d,)
+            else:
+                shape = (ne,) if d == 1 else (ne, d)
+            outputs.append(torch.empty(shape, dtype=dt, device=device))
+        with torch.cuda.device(device):
+            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device)
+            vp = (ctypes.c_void_p * max(nv, 1))(*[t.data_ptr() for t in values])
+            ip = (ctypes.c_void_p * max(ni, 1))(*[t.data_ptr() for t in indices])
+            op = (ctypes.c_void_p * max(len(outputs), 1))(*[t.data_ptr() for t in outputs])
+            st = syms.launch(ctypes.byref(desc), vp, ip,
+                             ctypes.c_void_p(row_end_offsets.data_ptr() if has_red else 0), op,
+                             ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws_bytes), _stream_ptr())
+        check(self.lib, st, "merged_spmv_launch")
+        self.launches += 1
+        if not outputs:
+            return None
+        return tuple(outputs)
+
+    __call__ = merged_spmv_launch
+
+    def device_status(self, dtype: torch.dtype, row_end_offsets: Optional[torch.Tensor] = None) -> int:
+        """Reads back the status word of the most recently used workspace (synchronises)."""
+        if not self._plans:
+            return 0
+        ws = next(reversed(self._plans.values()))[0]
+        out = torch.zeros(1, dtype=torch.int32, device=ws.device)
+        syms = self.symbols(dtype)
+        check(self.lib, syms.device_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(out.data_ptr()), _stream_ptr()),
+              "device_status")
+        return int(out.item())
+
+
+def load_builtin(name: str, **kw) -> GraphExtension:
+    """Extension object for one of the graphs compiled into libflexspmv_b200.so."""
+    from .graphs import ALL_GRAPHS
+    return GraphExtension(ALL_GRAPHS[name](), **kw)

@@ -1,0 +1,346 @@
+"""IR -> CUDA: turns the reference tracer's 6-tuple into one translation unit that plugs the fused
+per-edge map into the hand-written sm_100a kernels (csrc/flex_tile_kernel.cuh for graphs with a
+reduce-by-row, csrc/flex_edge_kernel.cuh for the aggregator / map-only flavour) and exports the five
+C-ABI symbols of ``FLEXSPMV_DECLARE_GRAPH`` (include/flexspmv.h).
+
+This is the counterpart of the reference's GPU emitter (codegen/merged_gen_gpu.py:17-465), which
+string-substitutes selector / map / reducer snippets into CUB-derived templates.  The op vocabulary
+and its meaning are the reference's (trace/graph_trace.py:229-276, codegen/merged_gen_core.py:122-236);
+what differs is the target: instead of relying on C++ overload resolution over ``Tensor<ValueT,Dim>``
+(data_struct_shared.cuh) the emitter resolves, per operation, which overload the reference code would
+select (equal widths / broadcast / scalar on either side) and emits an explicitly named call from
+csrc/flex_tensor.cuh.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Tuple
+
+from ..graphs import GraphIR, dim_of, operator_signature
+
+CTYPE = {"float32": ("float", "f32"), "float64": ("double", "f64"), "int64": ("long long", "i64")}
+VBYTES = {"float32": 4, "float64": 8, "int64": 8}
+
+_BIN = {"add": "Add", "sub": "Sub", "mul": "Mul", "pow": "Pow", "truediv": "Div", "lt": "Lt", "gt": "Gt"}
+_CXX_OP = {"add": "+", "sub": "-", "mul": "*", "truediv": "/"}
+
+
+class Var:
+    def __init__(self, kind: str, dim: int, expr: str):
+        self.kind, self.dim, self.expr = kind, dim, expr   # kind: 'vec' | 'scalar'
+
+
+def _lit(a) -> str:
+    return f"V({repr(a)})"
+
+
+def _stream_bytes_per_edge(ir: GraphIR, vb: int) -> Tuple[int, int]:
+    """(bytes staged per edge, number of staged streams): every distinct edge tensor plus one int32
+    index array per distinct non-row-identity selector."""
+    seen, total = set(), 0
+    for s in ir.selector_register:
+        if s.get("selector") != 1 and s["target"] not in seen:
+            seen.add(s["target"])
+            total += vb * dim_of(s["shape"])
+    for s in ir.selector_register:
+        if s.get("selector") == 1 and not s.get("row_identity") and ("idx:" + s["selector_name"]) not in seen:
+            seen.add("idx:" + s["selector_name"])
+            total += 4
+    return total, len(seen)
+
+
+def smem_bytes(ir: GraphIR, dtype: str, block: int, ipt: int, stages: int) -> int:
+    """Upper bound of the tile kernel's dynamic shared memory (mirrors TileSmemLayout in
+    csrc/flex_tile_kernel.cuh for 64-bit row offsets, the larger of the two instantiations)."""
+    vb = VBYTES[dtype]
+    per_edge, ns = _stream_bytes_per_edge(ir, vb)
+    acc = max(1, sum(dim_of(o["shape"]) for o in ir.outputs if str(o["target"]) == "reducer"))
+    tile = block * ipt
+    stage = -(-(tile * max(8, per_edge) + 32 * (ns + 1) + 16) // 128) * 128
+    fixed = 8 * stages + (32 + 4 * max(ns, 1) + 16) * stages + 4 * (block + 1) + 4 * (block // 32) \
+        + vb * acc * (block // 32) + vb * acc * 2 + 16 + 8 * 16 + 128
+    return fixed + vb * acc * (tile // 2) + stages * stage
+
+
+def choose_config(ir: GraphIR, dtype: str, smem_budget: int = 110 * 1024) -> Tuple[int, int, int, int]:
+    """(block threads, merge items per thread, stages, min CTAs per SM).  Items per thread are odd
+    (conflict-free shared-memory strides when a thread's items are all edges), shrink with the bytes
+    a thread keeps in registers for its in-flight gathers, and shrink further until two CTAs fit the
+    228 KB of shared memory of one SM."""
+    vb = VBYTES[dtype]
+    regs = sum(dim_of(s["shape"]) * vb // 4 for s in ir.selector_register if s.get("selector") == 1)
+    regs = max(regs, 1)
+    ipt = max(3, min(11, 64 // regs))
+    if ipt % 2 == 0:
+        ipt -= 1
+    block, stages = 256, 2
+    while ipt > 1 and smem_bytes(ir, dtype, block, ipt, stages) > smem_budget:
+        ipt -= 2
+    while block > 64 and smem_bytes(ir, dtype, block, ipt, stages) > smem_budget:
+        block //= 2
+    return block, ipt, stages, 2
+
+
+def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None) -> str:
+    cty, sfx = CTYPE[dtype]
+    symbol = symbol or f"{ir.name}_{sfx}"
+    block, ipt, stages, min_ctas = config or choose_config(ir, dtype)
+    non_gather, gathers, index_names = operator_signature(ir)
+    value_names = non_gather + gathers
+    in_dims = {i["name"]: dim_of(i["shape"]) for i in ir.inputs if i["dtype"] != "int"}
+    has_reducer = ir.has_reducer
+    if has_reducer and ir.aggregator_operations:
+        raise ValueError("a graph with a reducer cannot also hold a `sum` aggregator "
+                         "(the reference's reducer template has no aggregator slot either)")
+
+    # ---- streams (staged per-edge arrays) ---------------------------------------------------------
+    streams: List[Tuple[str, str, int]] = []      # (param field, element C type, bytes per edge)
+    stream_of: Dict[str, int] = {}
+    for s in ir.selector_register:
+        if s.get("selector") != 1 and s["target"] not in stream_of:
+            stream_of[s["target"]] = len(streams)
+            streams.append((s["target"], "V", f"int(sizeof(V)) * {dim_of(s['shape'])}"))
+    for s in ir.selector_register:
+        if s.get("selector") == 1 and not s.get("row_identity"):
+            key = "idx:" + s["selector_name"]
+            if key not in stream_of:
+                stream_of[key] = len(streams)
+                streams.append((s["selector_name"] + "_idx", "int", "4"))
+
+    # ---- outputs ------------------------------------------------------------------------------------
+    reducers, aggs, map_outs = [], [], []
+    acc_off = agg_off = 0
+    for oi, o in enumerate(ir.outputs):
+        d = dim_of(o["shape"])
+        tgt = str(o["target"])
+        if tgt == "reducer":
+            reducers.append((o["name"], d, acc_off, oi))
+            acc_off += d
+        elif "sum" in tgt:
+            aggs.append((o["name"], d, agg_off, oi))
+            agg_off += d
+        else:
+            map_outs.append((o["name"], d, oi))
+    red_by_name = {r[0]: r for r in reducers}
+    agg_by_name = {a[0]: a for a in aggs}
+
+    L: List[str] = []
+    w = L.append
+    w(f"// GENERATED by flexspmv_b200.codegen.emit_cuda -- graph '{ir.name}' ({dtype}), digest {ir.digest()}")
+    w('#include "flex_graph_api.cuh"')
+    w("namespace {")
+    w("struct Graph {")
+    w(f"  using V = {cty};")
+    w(f"  static constexpr int kNumValues = {len(value_names)}, kNumIndices = {len(index_names)}, kNumOutputs = {len(ir.outputs)};")
+    w(f"  static constexpr bool kHasReducer = {'true' if has_reducer else 'false'};")
+    w(f"  static constexpr int kNumReducers = {len(reducers)}, kAccDim = {max(acc_off, 1)}, kAggDim = {agg_off};")
+    w(f"  static constexpr int kNumStreams = {len(streams)};")
+    w("  static constexpr int kStreamBytesPerEdge = 0" + "".join(f" + {b}" for _, _, b in streams) + ";")
+    w("  struct Params {")
+    for n in value_names:
+        w(f"    V* {n};")
+    for n in index_names:
+        w(f"    const int* {n}_idx;")
+    for o in ir.outputs:
+        w(f"    V* out_{o['name']};")
+    w("  };")
+    w("  static Params make_params(const void* const* values, const void* const* indices, void* const* outputs) {")
+    w("    Params p{};")
+    for i, n in enumerate(value_names):
+        w(f"    p.{n} = static_cast<V*>(const_cast<void*>(values[{i}]));")
+    for i, n in enumerate(index_names):
+        w(f"    p.{n}_idx = static_cast<const int*>(indices[{i}]);")
+    for i, o in enumerate(ir.outputs):
+        w(f"    p.out_{o['name']} = static_cast<V*>(outputs[{i}]);")
+    w("    (void)values; (void)indices; (void)outputs;")
+    w("    return p;")
+    w("  }")
+    # alignment: streamed arrays 16 B, gather sources to their vector chunk
+    w("  static bool pointers_aligned(const Params& p) {")
+    w("    bool ok = true;")
+    for f, _, _ in streams:
+        w(f"    ok = ok && (reinterpret_cast<uintptr_t>(p.{f}) % 16 == 0);")
+    seen = set()
+    for s in ir.selector_register:
+        if s.get("selector") == 1 and s["target"] not in seen:
+            seen.add(s["target"])
+            w(f"    ok = ok && (reinterpret_cast<uintptr_t>(p.{s['target']}) % fx::VecIO<V, {dim_of(s['shape'])}>::kChunk == 0);")
+    w("    (void)p; return ok;")
+    w("  }")
+    w("  template <int I> __host__ __device__ static constexpr int stream_bytes() {")
+    for i, (_, _, b) in enumerate(streams):
+        w(f"    if constexpr (I == {i}) return {b};")
+    w("    return 0;")
+    w("  }")
+    w("  template <int I> __device__ __forceinline__ static const char* stream_ptr(const Params& p) {")
+    for i, (f, _, _) in enumerate(streams):
+        w(f"    if constexpr (I == {i}) return reinterpret_cast<const char*>(p.{f});")
+    w("    (void)p; return nullptr;")
+    w("  }")
+    w("  template <int R> __host__ __device__ static constexpr int red_dim() {")
+    for i, (_, d, _, _) in enumerate(reducers):
+        w(f"    if constexpr (R == {i}) return {d};")
+    w("    return 1;")
+    w("  }")
+    w("  template <int R> __host__ __device__ static constexpr int red_off() {")
+    for i, (_, _, off, _) in enumerate(reducers):
+        w(f"    if constexpr (R == {i}) return {off};")
+    w("    return 0;")
+    w("  }")
+    w("  template <int R> __device__ __forceinline__ static V* red_out(const Params& p) {")
+    for i, (n, _, _, _) in enumerate(reducers):
+        w(f"    if constexpr (R == {i}) return p.out_{n};")
+    w("    (void)p; return nullptr;")
+    w("  }")
+    w("  __device__ __forceinline__ static void store_aggregate(const Params& p, int i, V s) {")
+    for n, d, off, _ in aggs:
+        w(f"    if (i >= {off} && i < {off + d}) p.out_{n}[i - {off}] = s;")
+    w("    (void)p; (void)i; (void)s;")
+    w("  }")
+
+    # ---- gather -------------------------------------------------------------------------------------
+    gsel = [s for s in ir.selector_register if s.get("selector") == 1]
+    w("  struct Gathered {")
+    for s in gsel:
+        w(f"    fx::Vec<V, {dim_of(s['shape'])}> {s['name']};")
+    if not gsel:
+        w("    int unused;")
+    w("  };")
+    w("  template <class Tile, class IdxT>")
+    w("  __device__ __forceinline__ static void gather(const Params& p, const Tile& t, IdxT le, long long row, Gathered& g) {")
+    for s in gsel:
+        d = dim_of(s["shape"])
+        if s.get("row_identity"):
+            w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + row * {d});")
+        else:
+            si = stream_of["idx:" + s["selector_name"]]
+            w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + (long long)(*t.template stream<{si}, int>(le)) * {d});")
+    w("    (void)p; (void)t; (void)le; (void)row; (void)g;")
+    w("  }")
+
+    # ---- map ----------------------------------------------------------------------------------------
+    env: Dict[str, Var] = {}
+    body: List[str] = []
+    b = body.append
+    for s in ir.selector_register:
+        d = dim_of(s["shape"])
+        if s.get("selector") == 1:
+            b(f"    const fx::Vec<V, {d}>& {s['name']} = g.{s['name']};")
+            env[s["name"]] = Var("vec", d, s["name"])
+        else:
+            si = stream_of[s["target"]]
+            b(f"    fx::Vec<V, {d}> {s['selector_name']} = fx::ld_vec<V, {d}>(t.template stream<{si}, V>(le));")
+            env[s["selector_name"]] = Var("vec", d, s["selector_name"])
+
+    def operand(a):
+        if isinstance(a, str):
+            if a not in env:
+                raise ValueError(f"graph '{ir.name}': operand '{a}' is not defined before use")
+            return env[a]
+        return Var("lit", 0, _lit(a))
+
+    for op in ir.map_operations:
+        kind, name, args = op["op"], op["name"], op["args"]
+        d = dim_of(op["shape"])
+        if kind in _BIN:
+            A, B = operand(args[0]), operand(args[1])
+            if A.kind == "vec" and B.kind == "vec":
+                opn = _BIN[kind]
+                if kind == "truediv" and A.dim == B.dim:
+                    opn = "DivGuard"        # member operator/ of equal widths guards a zero divisor
+                b(f"    const auto {name} = fx::zip({A.expr}, {B.expr}, fx::{opn}{{}});")
+                env[name] = Var("vec", max(A.dim, B.dim), name)
+            elif A.kind == "vec":
+                opn = _BIN[kind]
+                if kind == "pow" and B.kind == "lit" and not isinstance(args[1], str) and float(args[1]) == 0.5 \
+                        and dtype != "int64":
+                    opn = "PowHalf"     # x ^ 0.5: one exactly rounded sqrt instead of the library pow
+                b(f"    const auto {name} = fx::zip_vs({A.expr}, {B.expr}, fx::{opn}{{}});")
+                env[name] = Var("vec", A.dim, name)
+            elif B.kind == "vec":
+                if kind in ("lt", "gt"):
+                    raise ValueError("scalar on the left of lt/gt has no overload in the reference")
+                opn = "DivGuard" if kind == "truediv" else _BIN[kind]
+                b(f"    const auto {name} = fx::zip_sv({A.expr}, {B.expr}, fx::{opn}{{}});")
+                env[name] = Var("vec", B.dim, name)
+            else:
+                if kind not in _CXX_OP or (A.kind == "lit" and B.kind == "lit"):
+                    raise ValueError(f"unsupported scalar-scalar op {kind}")
+                b(f"    const fx::Vec<V, 1> {name}{{{{ V({A.expr} {_CXX_OP[kind]} {B.expr}) }}}};")
+                env[name] = Var("vec", 1, name)
+        elif kind == "neg":
+            A = operand(args[0])
+            b(f"    const auto {name} = fx::neg({A.expr});")
+            env[name] = Var("vec", A.dim, name)
+        elif kind in ("exp", "abs", "sign"):
+            A = operand(args[0])
+            b(f"    const auto {name} = fx::vec_{kind}({A.expr});")
+            env[name] = Var("vec", A.dim, name)
+        elif kind == "norm":
+            A = operand(args[0])
+            b(f"    const V {name} = fx::norm({A.expr});")
+            env[name] = Var("scalar", 1, name)
+        elif kind == "getitem":
+            A = operand(args[0])
+            b(f"    const auto {name} = fx::item({A.expr}, {int(args[1][1])});")
+            env[name] = Var("vec", 1, name)
+        elif kind == "clone":
+            A = operand(args[0])
+            if A.kind == "vec":
+                b(f"    const auto {name} = {A.expr};")
+                env[name] = Var("vec", A.dim, name)
+            else:
+                b(f"    const fx::Vec<V, 1> {name}{{{{ {A.expr} }}}};")
+                env[name] = Var("vec", 1, name)
+        elif kind == "where":
+            C, X, Y = operand(args[0]), operand(args[1]), operand(args[2])
+            b(f"    const auto {name} = fx::where3({C.expr}, {X.expr}, {Y.expr});")
+            env[name] = Var("vec", max([C.dim] + [v.dim for v in (X, Y) if v.kind == "vec"]), name)
+        elif kind == "copy_":
+            S = operand(args[1])
+            b(f"    fx::st_vec(p.{args[0]} + (long long)e * {d}, {S.expr});")
+        elif kind == "setitem":
+            S = operand(args[2])
+            b(f"    fx::st_vec(p.{args[0]} + (long long)e * {d}, {S.expr});")
+            b(f"    {args[0]} = {S.expr};")
+        elif kind == "add_":
+            A, B = operand(args[0]), operand(args[1])
+            if B.kind == "vec":
+                b(f"    {A.expr} = fx::zip({A.expr}, {B.expr}, fx::Add{{}});")
+            else:
+                b(f"    {A.expr} = fx::zip_vs({A.expr}, {B.expr}, fx::Add{{}});")
+            b(f"    fx::st_vec(p.{args[0]} + (long long)e * {d}, {A.expr});")
+        elif kind == "reducer":
+            A = operand(args[0])
+            _, rd, off, _ = red_by_name[name]
+            if A.kind == "vec":
+                if A.dim != rd:
+                    raise ValueError(f"reducer {name}: width {A.dim} != {rd}")
+                b(f"    fx::accumulate<{off}>(acc, {A.expr});")
+            else:
+                b(f"    fx::accumulate_scalar<{off}, {rd}>(acc, {A.expr});")
+        elif kind == "sum":
+            A = operand(args[0])
+            _, ad, off, _ = agg_by_name[name]
+            if A.kind == "vec":
+                b(f"    fx::accumulate<{off}>(acc, {A.expr});")
+            else:
+                b(f"    fx::accumulate_scalar<{off}, {ad}>(acc, {A.expr});")
+        else:
+            raise ValueError(f"Operation {kind} not supported")
+    for n, d, _ in map_outs:
+        v = operand(n)
+        if v.kind == "vec":
+            b(f"    fx::st_vec(p.out_{n} + (long long)e * {d}, {v.expr});")
+        else:
+            b(f"    p.out_{n}[(long long)e] = {v.expr};")
+
+    w("  template <class Tile, class IdxT>")
+    w("  __device__ __forceinline__ static void map(const Params& p, const Tile& t, IdxT le, long long e, const Gathered& g, V* acc) {")
+    L.extend(body)
+    w("    (void)p; (void)t; (void)le; (void)e; (void)g; (void)acc;")
+    w("  }")
+    w("};")
+    w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}>;")
+    w("}  // namespace")
+    w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg)")
+    return "\n".join(L) + "\n"

@@ -1,0 +1,176 @@
+// Library-wide entry points of the C ABI: merge-path partition, nnz-balanced row blocks, CSR
+// validation, status strings.  Integer-only kernels; results are bit-identical to the reference's
+// search (include/merged_spmv_kernels.cuh:19-99).
+#include <cuda_runtime.h>
+
+#include "flex_common.cuh"
+
+namespace flex {
+
+int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// One thread per tile boundary: coordinate of diagonal t * tile_items (clamped to rows + edges).
+template <typename OffsetT>
+__global__ void partition_kernel(const OffsetT* __restrict__ row_offsets, long long num_rows, long long num_edges,
+                                 long long tile_items, long long num_tiles, OffsetT* __restrict__ coords) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t > num_tiles) return;
+  long long d = t * tile_items;
+  if (d > num_rows + num_edges) d = num_rows + num_edges;
+  OffsetT x, y;
+  merge_path_search<OffsetT, OffsetT>((OffsetT)d, row_offsets + 1, (OffsetT)0, (OffsetT)num_rows, (OffsetT)num_edges, x, y);
+  coords[2 * t] = x;
+  coords[2 * t + 1] = y;
+}
+
+int partition_launch(const void* d_row_offsets, int offset_bits, long long num_rows, long long num_edges,
+                     int tile_items, void* d_coords, cudaStream_t stream) {
+  if (!d_row_offsets || !d_coords || tile_items <= 0 || num_rows < 0 || num_edges < 0) return FLEXSPMV_ERR_BAD_ARG;
+  if (offset_bits != 32 && offset_bits != 64) return FLEXSPMV_ERR_BAD_ARG;
+  if (offset_bits == 32 && num_rows + num_edges >= (1ll << 31)) return FLEXSPMV_ERR_TOO_LARGE;
+  const long long tiles = (num_rows + num_edges + tile_items - 1) / tile_items;
+  const int block = 128;
+  const long long grid = (tiles + 1 + block - 1) / block;
+  if (grid > 0x7fffffffLL) return FLEXSPMV_ERR_TOO_LARGE;
+  if (offset_bits == 32)
+    partition_kernel<int><<<(unsigned)grid, block, 0, stream>>>(static_cast<const int*>(d_row_offsets), num_rows, num_edges,
+                                                                tile_items, tiles, static_cast<int*>(d_coords));
+  else
+    partition_kernel<long long><<<(unsigned)grid, block, 0, stream>>>(static_cast<const long long*>(d_row_offsets), num_rows,
+                                                                      num_edges, tile_items, tiles,
+                                                                      static_cast<long long*>(d_coords));
+  return (int)cudaGetLastError();
+}
+
+__global__ void header_init_kernel(WorkspaceHeader* dst, const WorkspaceHeader h) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *dst = h;
+}
+int header_init_launch(void* ws, const WorkspaceHeader& h, cudaStream_t stream) {
+  header_init_kernel<<<1, 32, 0, stream>>>(static_cast<WorkspaceHeader*>(ws), h);
+  return (int)cudaGetLastError();
+}
+
+template <typename OffsetT>
+__global__ void row_blocks_kernel(const OffsetT* __restrict__ row_offsets, long long num_rows, int parts, long long snap,
+                                  long long* __restrict__ first_row) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k > parts) return;
+  if (k == 0) { first_row[0] = 0; return; }
+  if (k == parts) { first_row[parts] = num_rows; return; }
+  const long long nnz = (long long)row_offsets[num_rows];
+  // k * nnz / parts without overflow: nnz < 2^63 / parts is guaranteed by parts <= 1024 and nnz < 2^52
+  const long long target = (long long)(((unsigned __int128)nnz * (unsigned)k) / (unsigned)parts);
+  long long lo = 0, hi = num_rows;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if ((long long)row_offsets[mid] < target) lo = mid + 1; else hi = mid;
+  }
+  if (snap > 1) lo = ((lo + snap / 2) / snap) * snap;
+  if (lo > num_rows) lo = num_rows;
+  first_row[k] = lo;
+}
+// rounding can make neighbours cross; enforce monotonicity in one thread (parts is tiny)
+__global__ void row_blocks_fix_kernel(long long* first_row, int parts) {
+  if (threadIdx.x == 0 && blockIdx.x == 0)
+    for (int k = 1; k <= parts; ++k)
+      if (first_row[k] < first_row[k - 1]) first_row[k] = first_row[k - 1];
+}
+
+template <typename OffsetT>
+__global__ void validate_kernel(const OffsetT* __restrict__ row_offsets, long long num_rows, long long num_edges,
+                                const int* __restrict__ index, long long num_vertices, int* status) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  bool bad_csr = false, bad_idx = false;
+  if (i == 0) bad_csr = (row_offsets[0] != 0) || ((long long)row_offsets[num_rows] != num_edges);
+  for (long long r = i; r < num_rows; r += stride) bad_csr |= row_offsets[r + 1] < row_offsets[r];
+  if (index)
+    for (long long e = i; e < num_edges; e += stride) bad_idx |= (index[e] < 0) || ((long long)index[e] >= num_vertices);
+  if (bad_csr) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_CSR);
+  else if (bad_idx) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_ARG);
+}
+
+}  // namespace flex
+
+extern "C" {
+
+int flexspmv_abi_version(void) { return FLEXSPMV_ABI_VERSION; }
+
+const char* flexspmv_error_string(int status) {
+  switch (status) {
+    case FLEXSPMV_OK: return "success";
+    case FLEXSPMV_ERR_BAD_ARG: return "bad argument (null pointer, negative size, unsupported offset width or index out of range)";
+    case FLEXSPMV_ERR_ALIGN: return "a device pointer is not aligned as required (streamed arrays: 16 bytes)";
+    case FLEXSPMV_ERR_WORKSPACE: return "workspace missing or too small";
+    case FLEXSPMV_ERR_TOO_LARGE: return "problem size beyond what this entry point supports";
+    case FLEXSPMV_ERR_BAD_CSR: return "row offsets are not a valid CSR offset array";
+    case FLEXSPMV_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case FLEXSPMV_ERR_NOT_PLANNED: return "workspace was not planned for this problem";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown flexspmv status";
+}
+
+int flexspmv_partition_bytes(int64_t num_rows, int64_t num_edges, int32_t offset_bits, int32_t tile_items, size_t* bytes) {
+  if (!bytes || tile_items <= 0 || num_rows < 0 || num_edges < 0 || (offset_bits != 32 && offset_bits != 64))
+    return FLEXSPMV_ERR_BAD_ARG;
+  const int64_t tiles = (num_rows + num_edges + tile_items - 1) / tile_items;
+  *bytes = (size_t)(tiles + 1) * (offset_bits == 64 ? 16u : 8u);
+  return 0;
+}
+
+int flexspmv_partition(const void* d_row_offsets, int32_t offset_bits, int64_t num_rows, int64_t num_edges,
+                       int32_t tile_items, void* d_coords, void* stream) {
+  return flex::partition_launch(d_row_offsets, offset_bits, num_rows, num_edges, tile_items, d_coords,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int flexspmv_row_blocks(const void* d_row_offsets, int32_t offset_bits, int64_t num_rows, int32_t parts, int64_t snap,
+                        int64_t* d_first_row, void* stream) {
+  if (!d_row_offsets || !d_first_row || parts < 1 || parts > 1024 || num_rows < 0) return FLEXSPMV_ERR_BAD_ARG;
+  if (offset_bits != 32 && offset_bits != 64) return FLEXSPMV_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int block = 128, grid = (parts + 1 + block - 1) / block;
+  if (offset_bits == 32)
+    flex::row_blocks_kernel<int><<<grid, block, 0, st>>>(static_cast<const int*>(d_row_offsets), num_rows, parts, snap,
+                                                         reinterpret_cast<long long*>(d_first_row));
+  else
+    flex::row_blocks_kernel<long long><<<grid, block, 0, st>>>(static_cast<const long long*>(d_row_offsets), num_rows, parts,
+                                                               snap, reinterpret_cast<long long*>(d_first_row));
+  flex::row_blocks_fix_kernel<<<1, 32, 0, st>>>(reinterpret_cast<long long*>(d_first_row), parts);
+  return (int)cudaGetLastError();
+}
+
+int flexspmv_validate_csr(const void* d_row_offsets, int32_t offset_bits, int64_t num_rows, int64_t num_edges,
+                          const int32_t* d_index, int64_t num_vertices, int32_t* d_status, void* stream) {
+  if (!d_row_offsets || !d_status || num_rows < 0 || num_edges < 0) return FLEXSPMV_ERR_BAD_ARG;
+  if (offset_bits != 32 && offset_bits != 64) return FLEXSPMV_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(d_status, 0, sizeof(int32_t), st);
+  if (e != cudaSuccess) return (int)e;
+  const int block = 256;
+  long long work = num_rows > num_edges ? num_rows : num_edges;
+  long long grid = (work + block - 1) / block;
+  if (grid < 1) grid = 1;
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (offset_bits == 32)
+    flex::validate_kernel<int><<<(unsigned)grid, block, 0, st>>>(static_cast<const int*>(d_row_offsets), num_rows, num_edges,
+                                                                 d_index, num_vertices, d_status);
+  else
+    flex::validate_kernel<long long><<<(unsigned)grid, block, 0, st>>>(static_cast<const long long*>(d_row_offsets), num_rows,
+                                                                       num_edges, d_index, num_vertices, d_status);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

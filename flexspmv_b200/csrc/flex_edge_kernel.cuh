@@ -1,0 +1,96 @@
+// Hand-written sm_100a kernel for fused graphs WITHOUT a reduce-by-row (the reference's "aggregator"
+// flavour: per-edge map outputs, in-place per-edge writes and global `sum` aggregators).  Edges are
+// independent, so tiles are plain runs of consecutive edges read with coalesced loads straight from
+// global memory; `sum` aggregators are reduced per thread, per warp (shuffles), per CTA (shared
+// memory) and finally across CTAs by the last CTA to finish, in CTA order: no atomics on the output,
+// no pre-zeroed output, deterministic.
+//
+// Replaces (reference): the aggregator agent's ConsumeTile + BlockReduce + atomicAdd,
+// cuda_template/aggregator/merged_agent_spmv_template.cuh:348-409 and
+// codegen/merged_gen_gpu.py:308-332.
+#pragma once
+#include "flex_common.cuh"
+#include "flex_tensor.cuh"
+
+namespace flex {
+
+template <class G>
+struct GlobalTile {
+  const typename G::Params* p;
+  template <int I, class T>
+  __device__ __forceinline__ const T* stream(long long e) const {
+    return reinterpret_cast<const T*>(G::template stream_ptr<I>(*p) + (size_t)e * G::template stream_bytes<I>());
+  }
+};
+
+struct EdgeKernelArgs {
+  WorkspaceHeader* header;
+  void* partials;        // [kMaxCtas][kAggDim] of V
+  long long num_edges;
+};
+
+template <class G, int BLOCK, int IPT>
+__global__ void __launch_bounds__(BLOCK) flex_edge_kernel(const typename G::Params p, const EdgeKernelArgs a) {
+  using V = typename G::V;
+  constexpr int kAgg = G::kAggDim > 0 ? G::kAggDim : 1;
+  constexpr int kWarps = BLOCK / 32;
+  __shared__ V s_part[kWarps * kAgg];
+  __shared__ int s_flag;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  GlobalTile<G> tile{&p};
+  V agg[kAgg];
+#pragma unroll
+  for (int i = 0; i < kAgg; ++i) agg[i] = V(0);
+
+  const long long tile_edges = (long long)BLOCK * IPT;
+  for (long long base = (long long)blockIdx.x * tile_edges; base < a.num_edges; base += (long long)gridDim.x * tile_edges) {
+    typename G::Gathered g[IPT];
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      const long long e = base + (long long)i * BLOCK + tid;
+      if (e < a.num_edges) G::gather(p, tile, e, e, g[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      const long long e = base + (long long)i * BLOCK + tid;
+      if (e < a.num_edges) G::map(p, tile, e, e, g[i], agg);
+    }
+  }
+
+  if constexpr (G::kAggDim > 0) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int i = 0; i < kAgg; ++i) agg[i] += __shfl_down_sync(0xffffffffu, agg[i], off);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < kAgg; ++i) s_part[warp * kAgg + i] = agg[i];
+    }
+    __syncthreads();
+    V* partials = static_cast<V*>(a.partials);
+    if (tid < kAgg) {
+      V s = V(0);
+      for (int w = 0; w < kWarps; ++w) s += s_part[w * kAgg + tid];
+      partials[(size_t)blockIdx.x * kAgg + tid] = s;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned t = atomicAdd(&a.header->ticket, 1u);
+      s_flag = (t == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_flag) {
+      __threadfence();
+      if (tid < kAgg) {
+        V s = V(0);
+        for (unsigned c = 0; c < gridDim.x; ++c) s += __ldcg(partials + (size_t)c * kAgg + tid);
+        G::store_aggregate(p, tid, s);
+      }
+      if (tid == 0) a.header->ticket = 0;
+    }
+  }
+}
+
+}  // namespace flex

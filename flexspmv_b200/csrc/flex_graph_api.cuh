@@ -1,0 +1,195 @@
+// Host side of one generated graph: workspace sizing, planning (merge-path partition into the
+// workspace), launch.  FLEXSPMV_DEFINE_GRAPH(symbol_suffix, GraphStruct, Cfg) emits the five
+// extern "C" entry points declared by FLEXSPMV_DECLARE_GRAPH in include/flexspmv.h.
+//
+// Replaces the reference's host dispatch (merged_spmv_dispatch / merged_spmv_launch,
+// include/merged_spmv.cuh:22-182): no per-call device-attribute queries, no per-call temp-storage
+// allocation, one kernel launch per operator call, partition cached in the caller's workspace.
+#pragma once
+#include <mutex>
+
+#include "flex_common.cuh"
+#include "flex_edge_kernel.cuh"
+#include "flex_tile_kernel.cuh"
+
+namespace flex {
+
+// implemented in flex_core.cu
+int partition_launch(const void* d_row_offsets, int offset_bits, long long num_rows, long long num_edges,
+                     int tile_items, void* d_coords, cudaStream_t stream);
+int device_sm_count();
+int header_init_launch(void* ws, const WorkspaceHeader& h, cudaStream_t stream);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <class G, class Cfg>
+struct GraphApi {
+  using V = typename G::V;
+  static constexpr int kEdgeBlock = 256, kEdgeIpt = 4;
+
+  static int tile_items(const flexspmv_desc* d) {
+    // the tile kernel's shared-memory carve-up is compiled for Cfg::kTile items; a smaller tile is
+    // allowed (tests exercise odd sizes), a larger one is not
+    if (d->tile_items <= 0) return Cfg::kTile;
+    return d->tile_items;
+  }
+  static int max_ctas(const flexspmv_desc* d, int resident) {
+    int m = d->max_ctas > 0 ? d->max_ctas : device_sm_count() * resident;
+    return m > kMaxCtas ? kMaxCtas : (m < 1 ? 1 : m);
+  }
+  static int check_desc(const flexspmv_desc* d) {
+    if (!d) return FLEXSPMV_ERR_BAD_ARG;
+    if (d->num_rows < 0 || d->num_edges < 0) return FLEXSPMV_ERR_BAD_ARG;
+    if (G::kHasReducer && d->offset_bits != 32 && d->offset_bits != 64) return FLEXSPMV_ERR_BAD_ARG;
+    if (G::kHasReducer && d->tile_items > Cfg::kTile) return FLEXSPMV_ERR_TOO_LARGE;
+    if (G::kHasReducer && d->offset_bits == 32 && d->num_rows + d->num_edges >= (1ll << 31)) return FLEXSPMV_ERR_TOO_LARGE;
+    return 0;
+  }
+  static long long num_tiles(const flexspmv_desc* d) {
+    if (!G::kHasReducer) return 0;
+    const long long t = tile_items(d);
+    return (d->num_rows + d->num_edges + t - 1) / t;
+  }
+  static void layout(const flexspmv_desc* d, WorkspaceHeader& h) {
+    const long long tiles = num_tiles(d);
+    const uint64_t pair = (d->offset_bits == 64 ? 16u : 8u);
+    h.coords_offset = sizeof(WorkspaceHeader);
+    h.carry_row_offset = align_up(h.coords_offset + (uint64_t)(tiles + 1) * pair, 256);
+    h.carry_val_offset = align_up(h.carry_row_offset + (uint64_t)kMaxCtas * 8u, 256);
+    const int width = G::kHasReducer ? G::kAccDim : (G::kAggDim > 0 ? G::kAggDim : 1);
+    h.total_bytes = align_up(h.carry_val_offset + (uint64_t)kMaxCtas * width * sizeof(V), 256);
+  }
+
+  static int info(flexspmv_graph_info* o) {
+    if (!o) return FLEXSPMV_ERR_BAD_ARG;
+    o->num_values = G::kNumValues; o->num_indices = G::kNumIndices; o->num_outputs = G::kNumOutputs;
+    o->has_reducer = G::kHasReducer ? 1 : 0; o->value_bytes = (int)sizeof(V);
+    o->default_tile_items = Cfg::kTile; o->block_threads = Cfg::kBlock; o->items_per_thread = Cfg::kIpt;
+    o->stages = Cfg::kStages;
+    o->smem_bytes = 0;
+    if constexpr (G::kHasReducer) o->smem_bytes = TileSmemLayout<G, long long, Cfg>::kTotal;
+    o->acc_dim = G::kHasReducer ? G::kAccDim : G::kAggDim; o->reserved = 0;
+    return 0;
+  }
+
+  static int workspace_bytes(const flexspmv_desc* d, size_t* bytes) {
+    if (int e = check_desc(d)) return e;
+    if (!bytes) return FLEXSPMV_ERR_BAD_ARG;
+    WorkspaceHeader h{};
+    layout(d, h);
+    *bytes = (size_t)h.total_bytes;
+    return 0;
+  }
+
+  static int plan(const flexspmv_desc* d, const void* row_offsets, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (int e = check_desc(d)) return e;
+    if (!ws) return FLEXSPMV_ERR_WORKSPACE;
+    WorkspaceHeader h{};
+    layout(d, h);
+    if (ws_bytes < h.total_bytes) return FLEXSPMV_ERR_WORKSPACE;
+    if (!aligned16(ws)) return FLEXSPMV_ERR_ALIGN;
+    h.magic = kMagic; h.ticket = 0; h.status = 0; h.offset_bits = d->offset_bits;
+    h.num_rows = d->num_rows; h.num_edges = d->num_edges; h.num_tiles = num_tiles(d);
+    h.tile_items = tile_items(d); h.max_ctas = d->max_ctas;
+    if (int e = header_init_launch(ws, h, st)) return e;   // a one-thread kernel: stream-ordered, no host sync
+    if (G::kHasReducer) {
+      if (!row_offsets) return FLEXSPMV_ERR_BAD_ARG;
+      if (!aligned16(row_offsets)) return FLEXSPMV_ERR_ALIGN;
+      return partition_launch(row_offsets, d->offset_bits, d->num_rows, d->num_edges, tile_items(d),
+                              static_cast<char*>(ws) + h.coords_offset, st);
+    }
+    return 0;
+  }
+
+  template <typename OffsetT>
+  static int launch_tiles(const flexspmv_desc* d, const typename G::Params& p, const void* row_offsets, void* ws,
+                          const WorkspaceHeader& h, cudaStream_t st) {
+    using L = TileSmemLayout<G, OffsetT, Cfg>;
+    static_assert(L::kTotal <= 227 * 1024, "tile kernel needs more shared memory than one sm_100a CTA can have");
+    auto kernel = flex_tile_kernel<G, OffsetT, Cfg>;
+    static int resident = 0;
+    static std::once_flag once;
+    static cudaError_t init_err = cudaSuccess;
+    std::call_once(once, [&] {
+      init_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+      if (init_err == cudaSuccess)
+        init_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, Cfg::kBlock, L::kTotal);
+    });
+    if (init_err != cudaSuccess) { (void)cudaGetLastError(); return (int)init_err; }
+    if (resident < 1) return FLEXSPMV_ERR_TOO_LARGE;
+    const long long tiles = h.num_tiles;
+    if (tiles == 0) return 0;
+    long long grid = max_ctas(d, resident);
+    if (grid > tiles) grid = tiles;
+    TileKernelArgs a;
+    a.row_offsets = row_offsets;
+    a.coords = static_cast<char*>(ws) + h.coords_offset;
+    a.header = static_cast<WorkspaceHeader*>(ws);
+    a.carry_row = reinterpret_cast<long long*>(static_cast<char*>(ws) + h.carry_row_offset);
+    a.carry_val = static_cast<char*>(ws) + h.carry_val_offset;
+    a.num_rows = d->num_rows; a.num_edges = d->num_edges; a.num_tiles = tiles;
+    kernel<<<(unsigned)grid, Cfg::kBlock, L::kTotal, st>>>(p, a);
+    return (int)cudaGetLastError();
+  }
+
+  static int launch(const flexspmv_desc* d, const void* const* values, const void* const* indices,
+                    const void* row_offsets, void* const* outputs, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (int e = check_desc(d)) return e;
+    if (!ws) return FLEXSPMV_ERR_WORKSPACE;
+    if ((G::kNumValues && !values) || (G::kNumIndices && !indices) || (G::kNumOutputs && !outputs)) return FLEXSPMV_ERR_BAD_ARG;
+    WorkspaceHeader h{};
+    layout(d, h);
+    if (ws_bytes < h.total_bytes) return FLEXSPMV_ERR_WORKSPACE;
+    h.num_tiles = num_tiles(d);
+    for (int i = 0; i < G::kNumValues; ++i) if (!values[i]) return FLEXSPMV_ERR_BAD_ARG;
+    for (int i = 0; i < G::kNumIndices; ++i) if (!indices[i]) return FLEXSPMV_ERR_BAD_ARG;
+    for (int i = 0; i < G::kNumOutputs; ++i) if (!outputs[i]) return FLEXSPMV_ERR_BAD_ARG;
+    typename G::Params p = G::make_params(values, indices, outputs);
+    if (!G::pointers_aligned(p)) return FLEXSPMV_ERR_ALIGN;
+    if constexpr (G::kHasReducer) {
+      if (!row_offsets) return FLEXSPMV_ERR_BAD_ARG;
+      if (!aligned16(row_offsets)) return FLEXSPMV_ERR_ALIGN;
+      if (d->offset_bits == 64) return launch_tiles<long long>(d, p, row_offsets, ws, h, st);
+      return launch_tiles<int>(d, p, row_offsets, ws, h, st);
+    } else {
+    if (d->num_edges == 0 && G::kAggDim == 0) return 0;
+    const long long tile_edges = (long long)kEdgeBlock * kEdgeIpt;
+    long long grid = (d->num_edges + tile_edges - 1) / tile_edges;
+    const long long cap = max_ctas(d, 2048 / kEdgeBlock);
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    EdgeKernelArgs a;
+    a.header = static_cast<WorkspaceHeader*>(ws);
+    a.partials = static_cast<char*>(ws) + h.carry_val_offset;
+    a.num_edges = d->num_edges;
+    flex_edge_kernel<G, kEdgeBlock, kEdgeIpt><<<(unsigned)grid, kEdgeBlock, 0, st>>>(p, a);
+    return (int)cudaGetLastError();
+    }
+  }
+
+  static int device_status(const void* ws, int32_t* d_out, cudaStream_t st) {
+    if (!ws || !d_out) return FLEXSPMV_ERR_BAD_ARG;
+    const char* src = static_cast<const char*>(ws) + offsetof(WorkspaceHeader, status);
+    return (int)cudaMemcpyAsync(d_out, src, sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+  }
+};
+
+}  // namespace flex
+
+#define FLEXSPMV_DEFINE_GRAPH(SYM, GRAPH, CFG)                                                                  \
+  extern "C" {                                                                                                  \
+  int flexspmv_##SYM##_info(flexspmv_graph_info* info) { return flex::GraphApi<GRAPH, CFG>::info(info); }       \
+  int flexspmv_##SYM##_workspace_bytes(const flexspmv_desc* d, size_t* b) {                                     \
+    return flex::GraphApi<GRAPH, CFG>::workspace_bytes(d, b);                                                   \
+  }                                                                                                             \
+  int flexspmv_##SYM##_plan(const flexspmv_desc* d, const void* ro, void* ws, size_t wb, void* st) {            \
+    return flex::GraphApi<GRAPH, CFG>::plan(d, ro, ws, wb, static_cast<cudaStream_t>(st));                      \
+  }                                                                                                             \
+  int flexspmv_##SYM##_launch(const flexspmv_desc* d, const void* const* v, const void* const* ix,              \
+                              const void* ro, void* const* o, void* ws, size_t wb, void* st) {                  \
+    return flex::GraphApi<GRAPH, CFG>::launch(d, v, ix, ro, o, ws, wb, static_cast<cudaStream_t>(st));          \
+  }                                                                                                             \
+  int flexspmv_##SYM##_device_status(const void* ws, int32_t* out, void* st) {                                  \
+    return flex::GraphApi<GRAPH, CFG>::device_status(ws, out, static_cast<cudaStream_t>(st));                   \
+  }                                                                                                             \
+  }

@@ -1,0 +1,411 @@
+// Hand-written sm_100a kernel for fused graphs WITH a reduce-by-row: persistent CTAs walk contiguous
+// runs of merge-path tiles; each tile's row-end offsets, index arrays and per-edge tensors are staged
+// into shared memory by 1-D bulk async copies (TMA, mbarrier complete_tx) issued STAGES tiles ahead;
+// every thread owns IPT consecutive merge items, gathers its vertex data, evaluates the generated map
+// in registers, and the per-row partial sums are combined by a warp-shuffle segmented scan, a small
+// cross-warp fold and a carry that travels from tile to tile inside the CTA.  Rows that end inside a
+// tile are staged in shared memory and written once, coalesced; the only cross-CTA state is one
+// carry per CTA, folded in by the last CTA to finish (ticket counter), in CTA order.  No atomics on
+// the output, no pre-zeroed output, run-to-run deterministic.
+//
+// Replaces (reference, paths inside the FlexSpmv project): SpmvKernel
+// include/merged_spmv_kernels.cuh:110-128 and AgentFlexSpmv::ConsumeTile / reduce<>
+// cuda_template/reducer/merged_agent_spmv_template.cuh:180-445 (CUB BlockScan + per-row atomicAdd).
+#pragma once
+#include "flex_common.cuh"
+#include "flex_tensor.cuh"
+
+namespace flex {
+
+template <int BLOCK_, int IPT_, int STAGES_, int MIN_CTAS_>
+struct TileCfg {
+  static constexpr int kBlock = BLOCK_;
+  static constexpr int kIpt = IPT_;
+  static constexpr int kStages = STAGES_;
+  static constexpr int kMinCtas = MIN_CTAS_;
+  static constexpr int kTile = BLOCK_ * IPT_;
+  static constexpr int kWarps = BLOCK_ / 32;
+  static constexpr int kRowsCap = (BLOCK_ * IPT_) / 2;  // rows of a tile staged in smem; the rest go direct
+};
+
+constexpr int kMaxCtas = 2048;            // capacity of the per-CTA carry arrays in the workspace
+constexpr uint64_t kWaitPolls = 1000000000ull;  // bound on every mbarrier wait: one second of %globaltimer
+
+template <class G>
+struct SmemTile {
+  const char* base[G::kNumStreams > 0 ? G::kNumStreams : 1];
+  template <int I, class T>
+  __device__ __forceinline__ const T* stream(int le) const {
+    return reinterpret_cast<const T*>(base[I] + (size_t)le * G::template stream_bytes<I>());
+  }
+};
+
+template <class G, typename OffsetT, class Cfg>
+struct TileSmemLayout {
+  using V = typename G::V;
+  static constexpr int kAcc = G::kAccDim;
+  static constexpr int kBytesPerEdge = G::kStreamBytesPerEdge;
+  static constexpr int kPerItem = (int(sizeof(OffsetT)) > kBytesPerEdge) ? int(sizeof(OffsetT)) : kBytesPerEdge;
+  // each staged window may grow by < 32 bytes from aligning both ends to 16
+  static constexpr int kStageBytes = int(align_up(uint64_t(Cfg::kTile) * kPerItem + 32u * (G::kNumStreams + 1) + 16, 128));
+  struct Ctl {
+    long long row0, nz0;
+    int nrows, nnz;
+    uint32_t roff_off;
+    uint32_t stream_off[G::kNumStreams > 0 ? G::kNumStreams : 1];
+  };
+  static constexpr int kOffBars = 0;
+  static constexpr int kOffCtl = int(align_up(kOffBars + 8 * Cfg::kStages, 16));
+  static constexpr int kOffXs = int(align_up(kOffCtl + sizeof(Ctl) * Cfg::kStages, 16));
+  static constexpr int kOffWKey = int(align_up(kOffXs + 4 * (Cfg::kBlock + 1), 16));
+  static constexpr int kOffWVal = int(align_up(kOffWKey + 4 * Cfg::kWarps, 16));
+  static constexpr int kOffCarry = int(align_up(kOffWVal + sizeof(V) * kAcc * Cfg::kWarps, 16));
+  static constexpr int kOffFlag = int(align_up(kOffCarry + sizeof(V) * kAcc * 2, 16));
+  static constexpr int kOffOut = int(align_up(kOffFlag + 16, 16));
+  static constexpr int kOffStages = int(align_up(kOffOut + sizeof(V) * kAcc * Cfg::kRowsCap, 128));
+  static constexpr int kTotal = kOffStages + kStageBytes * Cfg::kStages;
+};
+
+struct TileKernelArgs {
+  const void* row_offsets;  // leading 0 included
+  const void* coords;       // (num_tiles + 1) pairs of OffsetT
+  WorkspaceHeader* header;
+  long long* carry_row;     // [kMaxCtas]
+  void* carry_val;          // [kMaxCtas][kAcc] of V
+  long long num_rows;
+  long long num_edges;
+  long long num_tiles;
+};
+
+// One staged window: `count` elements of `eb` bytes starting at element `first` of an array of
+// `total` elements at `gbase` (16-byte aligned).  The bulk copy covers whole 16-byte chunks that lie
+// inside the array; a ragged tail (the array's last < 16 bytes) is fetched with plain loads.
+struct Window {
+  const char* src;     // 16-byte aligned start of the bulk part
+  uint32_t bulk_bytes; // multiple of 16 (may be 0)
+  uint32_t lead;       // bytes between src and the first wanted element
+  uint32_t span;       // smem bytes reserved (multiple of 16)
+  const char* tail_src;
+  uint32_t tail_bytes; // multiple of 4
+};
+__device__ __forceinline__ Window make_window(const void* gbase, uint32_t eb, long long first, long long count,
+                                              long long total) {
+  Window w;
+  const uintptr_t addr0 = (uintptr_t)gbase + (uintptr_t)first * eb;
+  const uintptr_t addr1 = addr0 + (uintptr_t)count * eb;
+  const uintptr_t a0 = addr0 & ~(uintptr_t)15;
+  const uintptr_t a1 = (addr1 + 15) & ~(uintptr_t)15;
+  const uintptr_t arr_floor = ((uintptr_t)gbase + (uintptr_t)total * eb) & ~(uintptr_t)15;
+  uintptr_t bulk_end = a1 < arr_floor ? a1 : arr_floor;
+  if (bulk_end < a0) bulk_end = a0;
+  w.src = (const char*)a0;
+  w.lead = (uint32_t)(addr0 - a0);
+  w.span = count > 0 ? (uint32_t)(a1 - a0) : 0u;
+  w.bulk_bytes = count > 0 ? (uint32_t)(bulk_end - a0) : 0u;
+  const uintptr_t t0 = bulk_end > addr0 ? bulk_end : addr0;
+  w.tail_src = (const char*)t0;
+  w.tail_bytes = (count > 0 && addr1 > t0) ? (uint32_t)(addr1 - t0) : 0u;
+  return w;
+}
+
+template <class G, typename OffsetT, class Cfg>
+__global__ void __launch_bounds__(Cfg::kBlock, Cfg::kMinCtas)
+flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
+  using V = typename G::V;
+  using L = TileSmemLayout<G, OffsetT, Cfg>;
+  using Ctl = typename L::Ctl;
+  constexpr int kAcc = G::kAccDim;
+  constexpr int NS = G::kNumStreams;
+  constexpr int BLOCK = Cfg::kBlock, IPT = Cfg::kIpt, S = Cfg::kStages;
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
+  Ctl* ctls = reinterpret_cast<Ctl*>(smem + L::kOffCtl);
+  int* s_xs = reinterpret_cast<int*>(smem + L::kOffXs);
+  int* s_wkey = reinterpret_cast<int*>(smem + L::kOffWKey);
+  V* s_wval = reinterpret_cast<V*>(smem + L::kOffWVal);
+  V* s_carry = reinterpret_cast<V*>(smem + L::kOffCarry);
+  int* s_flag = reinterpret_cast<int*>(smem + L::kOffFlag);
+  V* s_out = reinterpret_cast<V*>(smem + L::kOffOut);
+  unsigned char* s_stage = smem + L::kOffStages;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const OffsetT* row_offsets = static_cast<const OffsetT*>(a.row_offsets);
+  const OffsetT* coords = static_cast<const OffsetT*>(a.coords);
+
+  // a workspace that was never planned for this problem holds no usable coordinates: every CTA
+  // sees the same header, so all of them leave here and the ticket stays untouched
+  if (a.header->magic != kMagic || a.header->num_tiles != a.num_tiles || a.header->num_rows != a.num_rows ||
+      a.header->num_edges != a.num_edges || a.header->offset_bits != (int)(8 * sizeof(OffsetT))) {
+    if (tid == 0 && blockIdx.x == 0 && a.header->magic == kMagic) atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_NOT_PLANNED);
+    return;
+  }
+
+  // contiguous run of tiles of this CTA
+  const long long q = a.num_tiles / gridDim.x, rem = a.num_tiles % gridDim.x;
+  const long long t_begin = (long long)blockIdx.x * q + ((long long)blockIdx.x < rem ? blockIdx.x : rem);
+  const int count = (int)(q + ((long long)blockIdx.x < rem ? 1 : 0));
+
+  // ---- producer: stage one tile (thread 0 only) ---------------------------------------------------
+  auto issue = [&](long long tile, int s) {
+    const long long row0 = (long long)coords[2 * tile], nz0 = (long long)coords[2 * tile + 1];
+    const long long row1 = (long long)coords[2 * tile + 2], nz1 = (long long)coords[2 * tile + 3];
+    Ctl& c = ctls[s];
+    c.row0 = row0; c.nz0 = nz0; c.nrows = (int)(row1 - row0); c.nnz = (int)(nz1 - nz0);
+    unsigned char* dst = s_stage + (size_t)s * L::kStageBytes;
+    Window w[NS + 1];
+    w[0] = make_window(row_offsets, sizeof(OffsetT), row0 + 1, row1 - row0, a.num_rows + 1);
+    static_for<NS>([&](auto I) {
+      w[I.value + 1] = make_window(G::template stream_ptr<I.value>(p), G::template stream_bytes<I.value>(), nz0,
+                                   nz1 - nz0, a.num_edges);
+    });
+    uint32_t off[NS + 1], total = 0, cur = 0;
+#pragma unroll
+    for (int i = 0; i <= NS; ++i) { off[i] = cur; cur += w[i].span; total += w[i].bulk_bytes; }
+    c.roff_off = off[0] + w[0].lead;
+    static_for<NS>([&](auto I) { c.stream_off[I.value] = off[I.value + 1] + w[I.value + 1].lead; });
+    fence_proxy_async_smem();   // earlier generic reads/writes of this stage are ordered before the copies
+    mbar_expect_tx(&bars[s], total);
+#pragma unroll
+    for (int i = 0; i <= NS; ++i) {
+      if (w[i].bulk_bytes) bulk_g2s(dst + off[i], w[i].src, w[i].bulk_bytes, &bars[s]);
+      if (w[i].tail_bytes) {   // last < 16 bytes of an array: plain 4-byte loads
+        const uint32_t so = off[i] + (uint32_t)(w[i].tail_src - w[i].src);
+        for (uint32_t b = 0; b < w[i].tail_bytes; b += 4)
+          *reinterpret_cast<uint32_t*>(dst + so + b) = *reinterpret_cast<const uint32_t*>(w[i].tail_src + b);
+      }
+    }
+  };
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) mbar_init(&bars[s], 1);
+    mbar_fence_init();
+  }
+  if (tid < 2 * kAcc) s_carry[tid] = V(0);
+  __syncthreads();
+  if (tid == 0) {
+    for (int s = 0; s < S && s < count; ++s) issue(t_begin + s, s);
+  }
+
+  bool failed = false;
+  long long last_row1 = 0;
+  for (int k = 0; k < count; ++k) {
+    const int s = k % S;
+    const uint32_t parity = (uint32_t)(k / S) & 1u;
+    const int ok = __syncthreads_and(mbar_wait_bounded(&bars[s], parity, kWaitPolls) ? 1 : 0);
+    if (!ok) {
+      if (tid == 0) {
+        atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
+        a.header->debug[0] = (uint32_t)(t_begin + k); a.header->debug[1] = (uint32_t)s; a.header->debug[2] = blockIdx.x;
+      }
+      failed = true;
+      // give the copies still in flight (later stages) a bounded chance to land before leaving
+      for (int j = 1; j < S && k + j < count; ++j)
+        mbar_wait_bounded(&bars[(k + j) % S], (uint32_t)((k + j) / S) & 1u, kWaitPolls);
+      break;
+    }
+    const Ctl& c = ctls[s];
+    const long long row0 = c.row0, nz0 = c.nz0;
+    const int nrows = c.nrows, nnz = c.nnz;
+    const unsigned char* stage = s_stage + (size_t)s * L::kStageBytes;
+    const OffsetT* s_rend = reinterpret_cast<const OffsetT*>(stage + c.roff_off);
+    SmemTile<G> tile;
+    static_for<NS>([&](auto I) { tile.base[I.value] = reinterpret_cast<const char*>(stage + c.stream_off[I.value]); });
+    last_row1 = row0 + nrows;
+
+    // relative edge index at which local row r ends (rows >= nrows end beyond the tile)
+    auto rend = [&](int r) -> int { return r < nrows ? (int)((long long)s_rend[r] - nz0) : 0x7fffffff; };
+
+    // ---- this thread's merge-path span ------------------------------------------------------------
+    const int total_items = nrows + nnz;
+    const int d0 = min(tid * IPT, total_items);
+    const int d1 = min(d0 + IPT, total_items);
+    int xs, ys;
+    {
+      long long x, y;
+      merge_path_search<long long, OffsetT>((long long)d0, s_rend, nz0, (long long)nrows, (long long)nnz, x, y);
+      xs = (int)x; ys = (int)y;
+    }
+    s_xs[tid] = xs;
+    if (tid == 0) s_xs[BLOCK] = nrows;
+    __syncthreads();   // [A]
+    const int xe = s_xs[tid + 1];
+    const int ye = d1 - xe;
+
+    // ---- locate the row of every owned edge and issue the gathers ---------------------------------
+    int rowk[IPT];
+    typename G::Gathered g[IPT];
+    {
+      int r = xs, re = rend(xs);
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) {
+        const int e = ys + i;
+        rowk[i] = -1;
+        if (e < ye) {
+          while (re <= e) { ++r; re = rend(r); }
+          rowk[i] = r;
+          G::gather(p, tile, e, row0 + r, g[i]);
+        }
+      }
+    }
+
+    // ---- map + per-thread segmented sums ----------------------------------------------------------
+    V acc[kAcc], first_val[kAcc];
+#pragma unroll
+    for (int i = 0; i < kAcc; ++i) { acc[i] = V(0); first_val[i] = V(0); }
+    bool had_emit = false;
+    int cur = xs;
+    auto store_row = [&](int r, const V* v) {   // final value of a row that ends in this tile
+      static_for<G::kNumReducers>([&](auto R) {
+        constexpr int d = G::template red_dim<R.value>();
+        constexpr int o = G::template red_off<R.value>();
+        if (r < Cfg::kRowsCap) {
+          V* dst = s_out + (size_t)o * Cfg::kRowsCap + (size_t)r * d;
+#pragma unroll
+          for (int i = 0; i < d; ++i) dst[i] = v[o + i];
+        } else {
+          V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + r) * d;
+#pragma unroll
+          for (int i = 0; i < d; ++i) dst[i] = v[o + i];
+        }
+      });
+    };
+    auto flush_to = [&](int target) {   // rows cur .. target-1 end here: first gets acc, the rest are empty
+      if (!had_emit) {
+        had_emit = true;
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) first_val[i] = acc[i];
+      } else {
+        store_row(cur, acc);
+      }
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) acc[i] = V(0);
+      for (int r = cur + 1; r < target; ++r) store_row(r, acc);
+      cur = target;
+    };
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (rowk[i] >= 0) {
+        if (rowk[i] != cur) flush_to(rowk[i]);
+        G::map(p, tile, ys + i, nz0 + ys + i, g[i], acc);
+      }
+    }
+    if (cur < xe) flush_to(xe);
+
+    // ---- segmented inclusive scan of the carries (key = row the carry belongs to) -------------------
+    const int key = xe;
+    V val[kAcc];
+#pragma unroll
+    for (int i = 0; i < kAcc; ++i) val[i] = acc[i];
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int k2 = __shfl_up_sync(0xffffffffu, key, off);
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) {
+        const V v2 = shfl_up_any(val[i], off);
+        if (lane >= off && k2 == key) val[i] += v2;
+      }
+    }
+    if (lane == 31) {
+      s_wkey[warp] = key;
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) s_wval[warp * kAcc + i] = val[i];
+    }
+    const int pk = __shfl_up_sync(0xffffffffu, key, 1);
+    V pv[kAcc];
+#pragma unroll
+    for (int i = 0; i < kAcc; ++i) pv[i] = shfl_up_any(val[i], 1);
+    __syncthreads();   // [B] every thread is done reading this stage
+
+    if (tid == 0 && k + S < count) issue(t_begin + k + S, s);
+
+    // fold: CTA carry (belongs to local row 0) then the aggregates of the warps before this one
+    int fk = 0;
+    V fv[kAcc];
+#pragma unroll
+    for (int i = 0; i < kAcc; ++i) fv[i] = s_carry[(k & 1) * kAcc + i];
+    for (int w = 0; w < warp; ++w) {
+      const int wk = s_wkey[w];
+      if (wk == fk) {
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) fv[i] += s_wval[w * kAcc + i];
+      } else {
+        fk = wk;
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) fv[i] = s_wval[w * kAcc + i];
+      }
+    }
+    if (tid == BLOCK - 1) {   // carry into the next tile = inclusive value of the last thread
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) s_carry[((k + 1) & 1) * kAcc + i] = (fk == key) ? fv[i] + val[i] : val[i];
+    }
+    if (lane > 0) {
+      if (pk == fk) {
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) fv[i] += pv[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) fv[i] = pv[i];
+      }
+    }
+    if (had_emit) {   // the first row this thread closed started in earlier threads / tiles
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) first_val[i] = fv[i] + first_val[i];
+      store_row(xs, first_val);
+    }
+    __syncthreads();   // [C]
+
+    // ---- coalesced write of the rows that ended in this tile ----------------------------------------
+    const int rows_staged = nrows < Cfg::kRowsCap ? nrows : Cfg::kRowsCap;
+    static_for<G::kNumReducers>([&](auto R) {
+      constexpr int d = G::template red_dim<R.value>();
+      constexpr int o = G::template red_off<R.value>();
+      V* dst = G::template red_out<R.value>(p) + (size_t)row0 * d;
+      const V* src = s_out + (size_t)o * Cfg::kRowsCap;
+      for (int j = tid; j < rows_staged * d; j += BLOCK) dst[j] = src[j];
+    });
+  }
+
+  // ---- hand the CTA's carry to the last CTA ---------------------------------------------------------
+  __syncthreads();
+  if (tid < kAcc) {
+    V* cv = static_cast<V*>(a.carry_val) + (size_t)blockIdx.x * kAcc;
+    cv[tid] = failed ? V(0) : s_carry[(count & 1) * kAcc + tid];
+  }
+  if (tid == 0) a.carry_row[blockIdx.x] = (failed || count == 0) ? a.num_rows : last_row1;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned t = atomicAdd(&a.header->ticket, 1u);
+    s_flag[0] = (t == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_flag[0]) {
+    __threadfence();
+    const int n_cta = gridDim.x;
+    const V* cvals = static_cast<const V*>(a.carry_val);
+    for (int c = tid; c < n_cta; c += BLOCK) {
+      const long long row = __ldcg(a.carry_row + c);
+      if (row >= a.num_rows) continue;
+      if (c > 0 && __ldcg(a.carry_row + c - 1) == row) continue;   // not the head of its run
+      V sum[kAcc];
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) sum[i] = __ldcg(cvals + (size_t)c * kAcc + i);
+      for (int c2 = c + 1; c2 < n_cta && __ldcg(a.carry_row + c2) == row; ++c2) {
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) sum[i] += __ldcg(cvals + (size_t)c2 * kAcc + i);
+      }
+      static_for<G::kNumReducers>([&](auto R) {
+        constexpr int d = G::template red_dim<R.value>();
+        constexpr int o = G::template red_off<R.value>();
+        V* dst = G::template red_out<R.value>(p) + (size_t)row * d;
+#pragma unroll
+        for (int i = 0; i < d; ++i) dst[i] = __ldcg(dst + i) + sum[o + i];
+      });
+    }
+    if (tid == 0) a.header->ticket = 0;
+  }
+}
+
+}  // namespace flex

@@ -222,6 +222,8 @@ def random_problem(graph_ir, num_rows: int, num_vertices: int, nnz: int, seed: i
         rows = num_vertices if inp["name"] in gather_src else nnz
         a = draw((rows, d))
         values[inp["name"]] = a[:, 0].copy() if d == 1 else a
+    if graph_ir.name == "rusanov":     # water depth must be positive for the flux to be defined
+        values["U"][:, 0] = (np.abs(values["U"][:, 0]) + 0.5).astype(dtype)
     for s in graph_ir.selector_register:
         if s.get("selector") != 1 or s["selector_name"] in indices:
             continue

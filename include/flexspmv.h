@@ -1,0 +1,173 @@
+/*
+ * flexspmv.h -- C ABI of the B200 (sm_100a) fused gather -> per-edge map -> segmented reduce-by-row
+ * library (libflexspmv_b200.so).
+ *
+ * Conventions for every entry point:
+ *   - plain C, no exceptions cross the boundary; the return value is a status:
+ *       0 = success, negative = FLEXSPMV_ERR_* below, positive = a cudaError_t from the runtime;
+ *   - all device work is enqueued on the caller's stream (a cudaStream_t passed as void*); nothing
+ *     synchronises the device or the stream and nothing is allocated or freed: scratch memory comes
+ *     from the caller ("workspace"), sized by the matching *_workspace_bytes call;
+ *   - device pointers of streamed arrays (per-edge tensors, index arrays, row offsets) must be
+ *     16-byte aligned (bulk-copy staging); gather sources and outputs need only their natural
+ *     alignment;
+ *   - row offsets always include the leading 0 (length num_rows + 1), as the reference operator
+ *     receives them (the callee skips it: include/merged_spmv.cuh:169,
+ *     cpu_template/merged_spmv_template_reducer.h:97).
+ *
+ * Reference interfaces replaced (paths inside the FlexSpmv project):
+ *   merged::merged_spmv_launch<ValueT,OffsetT>(FlexParams, void* d_temp, size_t& bytes, bool, stream)
+ *       include/merged_spmv.cuh:149-182 (two-phase temp-storage convention) and its dispatch
+ *       merged_spmv_dispatch include/merged_spmv.cuh:22-144      -> flexspmv_<graph>_* below
+ *   SpmvSearchKernel / MergePathSearch  include/merged_spmv_kernels.cuh:19-99 -> flexspmv_partition
+ *   FlexParams pointer bundle           include/merged_utils.cuh:243-262      -> flexspmv_desc + the
+ *       three pointer arrays of flexspmv_<graph>_launch
+ */
+#ifndef FLEXSPMV_H_
+#define FLEXSPMV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLEXSPMV_ABI_VERSION 1
+
+enum {
+  FLEXSPMV_OK = 0,
+  FLEXSPMV_ERR_BAD_ARG = -1,       /* null pointer, negative size, unsupported offset width        */
+  FLEXSPMV_ERR_ALIGN = -2,         /* a streamed array is not 16-byte aligned                      */
+  FLEXSPMV_ERR_WORKSPACE = -3,     /* workspace missing or smaller than *_workspace_bytes reports  */
+  FLEXSPMV_ERR_TOO_LARGE = -4,     /* size beyond what the entry point supports                    */
+  FLEXSPMV_ERR_BAD_CSR = -5,       /* row offsets not monotone / inconsistent with num_edges       */
+  FLEXSPMV_ERR_TIMEOUT = -6,       /* a bounded device-side wait ran out (read via *_device_status)*/
+  FLEXSPMV_ERR_NOT_PLANNED = -7    /* launch called on a workspace that was never planned          */
+};
+
+/* Problem descriptor shared by the plan / launch calls of every graph. */
+typedef struct flexspmv_desc {
+  int64_t num_rows;      /* rows of the reduce-by-row (0 for graphs without a reducer)              */
+  int64_t num_edges;     /* edges = non-zeros = length of every per-edge array                      */
+  int64_t num_vertices;  /* rows of the gather sources (informational; used by validation)          */
+  int32_t offset_bits;   /* 32 or 64: width of the row-offset entries                               */
+  int32_t tile_items;    /* merge items (rows + edges) per tile; 0 = the graph's compiled default   */
+  int32_t max_ctas;      /* cap on persistent CTAs; 0 = SM count x resident CTAs per SM             */
+  int32_t reserved;
+} flexspmv_desc;
+
+/* ---- library-wide ----------------------------------------------------------------------------- */
+
+/* ABI version of the loaded library (FLEXSPMV_ABI_VERSION it was built with). */
+int flexspmv_abi_version(void);
+
+/* Static, NUL-terminated description of a status returned by this library. */
+const char *flexspmv_error_string(int status);
+
+/*
+ * Merge-path partition: coordinates (row, edge) where the diagonals t * tile_items, t in
+ * [0, num_tiles], cross the merge path of (row END offsets) x (0..num_edges-1); num_tiles =
+ * ceil((num_rows + num_edges) / tile_items).  Output: (num_tiles + 1) pairs of int32 (offset_bits 32)
+ * or int64 (offset_bits 64) in device memory, bit-identical to the reference search.
+ * Replaces SpmvSearchKernel, include/merged_spmv_kernels.cuh:60-99 (MergePathSearch :19-50).
+ */
+int flexspmv_partition_bytes(int64_t num_rows, int64_t num_edges, int32_t offset_bits,
+                             int32_t tile_items, size_t *bytes);
+int flexspmv_partition(const void *d_row_offsets, int32_t offset_bits, int64_t num_rows,
+                       int64_t num_edges, int32_t tile_items, void *d_coords, void *stream);
+
+/*
+ * nnz-balanced contiguous row blocks for the multi-GPU split: d_first_row[k] (int64, parts + 1
+ * entries, device) = lower_bound(row_offsets, k * nnz / parts), rounded to the nearest multiple of
+ * `snap` rows (snap <= 1: no rounding); d_first_row[0] = 0, d_first_row[parts] = num_rows.
+ * No counterpart in the reference (it has no multi-GPU code); the search is the same lower-bound
+ * family as MergePathSearch.
+ */
+int flexspmv_row_blocks(const void *d_row_offsets, int32_t offset_bits, int64_t num_rows,
+                        int32_t parts, int64_t snap, int64_t *d_first_row, void *stream);
+
+/*
+ * Debug validator: checks on the device that row offsets start at 0, are non-decreasing and end at
+ * num_edges, and (when d_index != NULL) that every index lies in [0, num_vertices).  Writes 0 or a
+ * FLEXSPMV_ERR_* to the int32 *d_status (device).  No reference counterpart (the reference never
+ * validates: python_wrapper/dynamic_replace_submodule.py:20-41 assumes sorted rows).
+ */
+int flexspmv_validate_csr(const void *d_row_offsets, int32_t offset_bits, int64_t num_rows,
+                          int64_t num_edges, const int32_t *d_index, int64_t num_vertices,
+                          int32_t *d_status, void *stream);
+
+/* ---- per fused graph ---------------------------------------------------------------------------
+ * One set of five symbols per (graph, value type); the per-edge map is compiled into the kernel, so
+ * a graph is identified by its symbol prefix.  For graph G and value type T (f32 | f64 | i64):
+ *
+ *   flexspmv_G_T_info            sizes of the three pointer arrays and of the compiled defaults
+ *   flexspmv_G_T_workspace_bytes scratch size for a problem (first phase of the reference's
+ *                                two-phase temp-storage call, include/merged_spmv.cuh:84-92)
+ *   flexspmv_G_T_plan            partitions the problem into the workspace (cacheable while the row
+ *                                offsets do not change; replaces the per-call search kernel,
+ *                                include/merged_spmv.cuh:98-119)
+ *   flexspmv_G_T_launch          one fused pass (replaces SpmvKernel + AgentFlexSpmv::ConsumeTile,
+ *                                include/merged_spmv_kernels.cuh:110-128,
+ *                                cuda_template/reducer/merged_agent_spmv_template.cuh:350-445, and
+ *                                the aggregator flavour cuda_template/aggregator/...:348-409).
+ *                                Every output element is written (outputs need no zero fill).
+ *   flexspmv_G_T_device_status   copies the workspace's device status word into *d_status_out
+ *                                (device int32) without synchronising
+ *
+ * Pointer arrays of launch (device pointers; order = the operator's positional order,
+ * codegen/merged_gen_binding.py:65-78):
+ *   values[]  non-gather value inputs then gather value inputs
+ *   indices[] one int32 index array per distinct selector target
+ *   outputs[] one array per graph output (reducer (num_rows, dim), sum (dim), per-edge (ne, dim))
+ */
+typedef struct flexspmv_graph_info {
+  int32_t num_values;
+  int32_t num_indices;
+  int32_t num_outputs;
+  int32_t has_reducer;
+  int32_t value_bytes;
+  int32_t default_tile_items;
+  int32_t block_threads;
+  int32_t items_per_thread;
+  int32_t stages;
+  int32_t smem_bytes;
+  int32_t acc_dim;
+  int32_t reserved;
+} flexspmv_graph_info;
+
+#define FLEXSPMV_DECLARE_GRAPH(G)                                                                   \
+  int flexspmv_##G##_info(flexspmv_graph_info *info);                                               \
+  int flexspmv_##G##_workspace_bytes(const flexspmv_desc *desc, size_t *bytes);                     \
+  int flexspmv_##G##_plan(const flexspmv_desc *desc, const void *d_row_offsets, void *d_workspace,  \
+                          size_t workspace_bytes, void *stream);                                    \
+  int flexspmv_##G##_launch(const flexspmv_desc *desc, const void *const *values,                   \
+                            const void *const *indices, const void *d_row_offsets,                  \
+                            void *const *outputs, void *d_workspace, size_t workspace_bytes,        \
+                            void *stream);                                                          \
+  int flexspmv_##G##_device_status(const void *d_workspace, int32_t *d_status_out, void *stream);
+
+/* graphs built into libflexspmv_b200.so (the benchmark configurations and the unit-test graphs) */
+FLEXSPMV_DECLARE_GRAPH(spmv_f32)
+FLEXSPMV_DECLARE_GRAPH(spmv_f64)
+FLEXSPMV_DECLARE_GRAPH(spmv_i64)
+FLEXSPMV_DECLARE_GRAPH(spring_mass_f32)
+FLEXSPMV_DECLARE_GRAPH(spring_mass_f64)
+FLEXSPMV_DECLARE_GRAPH(rusanov_f64)
+FLEXSPMV_DECLARE_GRAPH(rusanov_f32)
+FLEXSPMV_DECLARE_GRAPH(mixed_dims_f32)
+FLEXSPMV_DECLARE_GRAPH(mixed_dims_f64)
+FLEXSPMV_DECLARE_GRAPH(mixed_dims_i64)
+FLEXSPMV_DECLARE_GRAPH(ops_zoo_f32)
+FLEXSPMV_DECLARE_GRAPH(ops_zoo_f64)
+FLEXSPMV_DECLARE_GRAPH(edge_sum_f32)
+FLEXSPMV_DECLARE_GRAPH(edge_sum_f64)
+FLEXSPMV_DECLARE_GRAPH(edge_sum_i64)
+FLEXSPMV_DECLARE_GRAPH(edge_copy_f32)
+FLEXSPMV_DECLARE_GRAPH(edge_copy_f64)
+FLEXSPMV_DECLARE_GRAPH(edge_copy_i64)
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLEXSPMV_H_ */

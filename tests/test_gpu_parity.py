@@ -1,0 +1,152 @@
+"""GPU parity: the CUDA path, called through the operator shim and the C ABI, against the CPU oracle
+on identical seeded inputs.  Shapes follow the reference's self-checking harnesses
+(src/flex_spmv_full_red.cu:391-427,624-635; main.cpp:413-415): sorted random cut points so empty rows
+and rows spanning many tiles both occur, dims 1/2/6 mixed in one graph, exact equality for int64."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from flexspmv_b200 import graphs, problems
+from flexspmv_b200.binding import Desc, GraphExtension, load_library
+from oracle import ir_eval
+from parity import assert_outputs_match
+
+pytestmark = pytest.mark.gpu
+
+NP2T = {np.dtype(np.float32): torch.float32, np.dtype(np.float64): torch.float64, np.dtype(np.int64): torch.int64}
+
+
+def run_gpu(ext: GraphExtension, ir, prob, dtype, offsets_dtype=None):
+    dev = torch.device("cuda:0")
+    non_gather, gathers, index_names = graphs.operator_signature(ir)
+    vals = [torch.from_numpy(np.ascontiguousarray(prob.values[n].astype(dtype))).to(dev) for n in non_gather + gathers]
+    idxs = [torch.from_numpy(np.ascontiguousarray(prob.indices[n])).to(dev) for n in index_names]
+    if prob.row_offsets is not None:
+        ro = prob.row_offsets.astype(offsets_dtype) if offsets_dtype is not None else prob.row_offsets
+        ro_t = torch.from_numpy(np.ascontiguousarray(ro)).to(dev)
+    else:
+        ro_t = torch.tensor([42], dtype=torch.int32, device=dev)
+    outs = ext.merged_spmv_launch(*vals, *idxs, ro_t, prob.num_rows, prob.num_cols)
+    torch.cuda.synchronize()
+    outs = [] if outs is None else [o.cpu().numpy() for o in outs]
+    written = {n: v.cpu().numpy() for n, v in zip(non_gather + gathers, vals)}
+    return outs, written
+
+
+SHAPES = [
+    # rows, vertices, nnz
+    (1, 1, 1),
+    (37, 37, 211),
+    (500, 500, 40),          # mostly empty rows
+    (3, 3, 5000),            # rows spanning several tiles
+    (1543, 1543, 12313),
+    (12314, 12314, 123134),  # the reference harness' default shape
+    (9000, 9000, 0x3ffff),
+]
+
+CASES = [(g, dt) for g in graphs.ALL_GRAPHS for dt in graphs.GRAPH_DTYPES[g]]
+
+
+@pytest.mark.parametrize("gname,dt", CASES)
+def test_graph_matches_oracle(gname, dt):
+    ir = graphs.ALL_GRAPHS[gname]()
+    ext = GraphExtension(ir)
+    dtype = np.dtype(dt)
+    for (nr, nv, nnz) in SHAPES:
+        prob = problems.random_problem(ir, nr, nv, nnz, seed=1000 + nr + nnz, dtype=dtype)
+        ref, ref_written, sums = ir_eval.run_graph(ir, prob, dtype, num_threads=8, want_abs_sums=True)
+        got, got_written = run_gpu(ext, ir, prob, dtype)
+        assert_outputs_match(ir, got, ref, sums, dtype, what=f"{gname}/{dt}/{nr}x{nnz}")
+        for name, arr in ref_written.items():     # in-place map ops write through input pointers
+            g = got_written[name].reshape(arr.shape)
+            assert np.array_equal(g, arr), f"{gname}: in-place input {name} differs"
+
+
+@pytest.mark.parametrize("tile_items", [1, 7, 320, 896, 1000])
+def test_small_tiles_and_few_ctas(tile_items):
+    """Odd tile sizes (incl. the reference's 320 / 896) and a grid of 3 CTAs force long carry chains
+    across tiles and across CTAs."""
+    ir = graphs.spmv_graph()
+    for dt in ("float64", "int64"):
+        dtype = np.dtype(dt)
+        ext = GraphExtension(ir, tile_items=tile_items, max_ctas=3)
+        nnz = 2000 if tile_items < 10 else 60000
+        prob = problems.random_problem(ir, 97, 97, nnz, seed=5, dtype=dtype)
+        ref, _, sums = ir_eval.run_graph(ir, prob, dtype, num_threads=4, want_abs_sums=True)
+        got, _ = run_gpu(ext, ir, prob, dtype)
+        assert_outputs_match(ir, got, ref, sums, dtype, what=f"tile {tile_items}")
+
+
+def test_int64_row_offsets_match_int32():
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    prob = problems.random_problem(ir, 4000, 4000, 70000, seed=11, dtype=np.float64)
+    a, _ = run_gpu(ext, ir, prob, np.float64)
+    b, _ = run_gpu(ext, ir, prob, np.float64, offsets_dtype=np.int64)
+    assert np.array_equal(a[0], b[0])
+
+
+def test_run_to_run_deterministic():
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    prob = problems.random_problem(ir, 5000, 5000, 400000, seed=3, dtype=np.float32)
+    a, _ = run_gpu(ext, ir, prob, np.float32)
+    for _ in range(3):
+        b, _ = run_gpu(ext, ir, prob, np.float32)
+        assert np.array_equal(a[0], b[0])
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("tile_items", [320, 896, 1792, 5])
+def test_partition_coordinates_bit_exact(bits, tile_items):
+    lib = load_library()
+    rng = np.random.default_rng(9)
+    for (nr, nnz) in [(1, 0), (0, 0), (12314, 123134), (50, 100000), (100000, 50)]:
+        ro = problems.random_cut_csr(nr, nnz, rng).astype(np.int32 if bits == 32 else np.int64)
+        ref = ir_eval.tile_coordinates(ro, tile_items)
+        ro_t = torch.from_numpy(ro).cuda()
+        nbytes = ctypes.c_size_t()
+        assert lib.flexspmv_partition_bytes(ctypes.c_int64(nr), ctypes.c_int64(nnz), bits, tile_items, ctypes.byref(nbytes)) == 0
+        out = torch.empty(nbytes.value // (bits // 8), dtype=torch.int32 if bits == 32 else torch.int64, device="cuda")
+        st = lib.flexspmv_partition(ctypes.c_void_p(ro_t.data_ptr()), bits, ctypes.c_int64(nr), ctypes.c_int64(nnz),
+                                    tile_items, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(0))
+        assert st == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy().reshape(-1, 2), ref)
+
+
+def test_row_blocks_bit_exact():
+    lib = load_library()
+    rng = np.random.default_rng(2)
+    ro = problems.random_cut_csr(5000, 777777, rng).astype(np.int64)
+    ro_t = torch.from_numpy(ro).cuda()
+    for parts, snap in [(1, 1), (2, 1), (8, 1), (8, 64), (3, 1000)]:
+        out = torch.empty(parts + 1, dtype=torch.int64, device="cuda")
+        assert lib.flexspmv_row_blocks(ctypes.c_void_p(ro_t.data_ptr()), 64, ctypes.c_int64(5000), parts,
+                                       ctypes.c_int64(snap), ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(0)) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), ir_eval.nnz_balanced_row_blocks(ro, parts, snap))
+
+
+def test_errors_are_loud():
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    prob = problems.random_problem(ir, 10, 10, 50, seed=1, dtype=np.float32)
+    vals = torch.from_numpy(prob.values["vals"]).cuda()
+    x = torch.from_numpy(prob.values["x"]).cuda()
+    idx = torch.from_numpy(prob.indices["selector"]).cuda()
+    ro = torch.from_numpy(prob.row_offsets).cuda()
+    with pytest.raises(RuntimeError):
+        ext.merged_spmv_launch(vals.cpu(), x, idx, ro, 10, 10)            # CPU tensor
+    with pytest.raises(RuntimeError):
+        ext.merged_spmv_launch(vals.half(), x.half(), idx, ro, 10, 10)    # unsupported dtype
+    with pytest.raises(RuntimeError):
+        ext.merged_spmv_launch(vals, x.double(), idx, ro, 10, 10)         # dtype mismatch
+    with pytest.raises(RuntimeError):
+        ext.merged_spmv_launch(vals, x, idx.long(), ro, 10, 10)           # index dtype
+    with pytest.raises(RuntimeError):
+        ext.merged_spmv_launch(vals[1:], x, idx, ro, 10, 10)              # misaligned streamed array (and short)
+    lib = load_library()
+    assert lib.flexspmv_partition(None, 32, ctypes.c_int64(1), ctypes.c_int64(1), 4, None, None) != 0
