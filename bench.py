@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the fused gather-map-reduce SpMV hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--grid n]
+    torchrun --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload: the multi-GPU configuration, a 7-point Laplacian on a 512^3 grid (fp64 values,
+int64 row offsets, int32 columns, 937,951,232 non-zeros), rows split into nnz-balanced z-slabs, one
+rank per GPU, iterated as x <- A x with a one-plane halo exchange per neighbour per iteration (NCCL).
+A step is one iteration (halo exchange + one fused SpMV launch per rank).  The problem is fixed as N
+grows (strong scaling).  The metric is the reference's effective bandwidth: every compulsory array
+counted once per SpMV (src/flex_spmv_full_red.cu:347-359 of the reference) divided by the time.
+
+One JSON line is printed by rank 0.  At N = 1 it also carries the per-configuration results of the
+four single-GPU configurations (kernel-only, warm and with L2 flushed between launches) and the CPU
+baseline: the reference's own generated CPU operator (OmpMergeSystem, compiled from the reference's
+sources into oracle/_ref) timed on a bounded slab of the same matrix on the host cores.
+`--impl reference` times only that CPU operator.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fused SpMV effective GB/s"
+UNIT = "GB/s"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def poisson3d_bytes(n: int) -> tuple[int, int]:
+    n3 = n ** 3
+    nnz = 7 * n3 - 6 * n * n
+    return 12 * nnz + 8 * (n3 + 1) + 16 * n3, nnz
+
+
+# --------------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi in the background during the timed region (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU reference arm
+# --------------------------------------------------------------------------------------------------
+def cpu_reference(grid: int, steps: int, warmup: int, planes: int = 32) -> dict:
+    """The reference's generated CPU operator on a z-slab of the benchmark matrix, all host threads."""
+    from flexspmv_b200 import graphs, problems
+    from oracle import ref_run
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    threads = min(cores, 256)
+    planes = min(planes, grid - 2) if grid > 2 else grid
+    z0 = 1 if grid > 2 else 0
+    prob = problems.poisson3d(grid, z_begin=z0, z_end=z0 + planes, offset_dtype=np.int32)
+    shift = (z0 - 1) * grid * grid if z0 > 0 else 0
+    n2 = grid * grid
+    prob.indices["selector"] = (prob.indices["selector"].astype(np.int64) - shift).astype(np.int32)
+    prob.values["x"] = np.ascontiguousarray(prob.values["x"][shift:shift + (planes + 2) * n2])
+    prob.num_cols = prob.values["x"].shape[0]
+    ir = graphs.spmv_graph()
+    nnz = prob.nnz
+    alg = 12 * nnz + 8 * (prob.num_rows + 1) + 8 * prob.num_cols + 8 * prob.num_rows
+    if ref_run.available("spmv"):
+        kind = "reference"
+        call = ref_run.PreparedCall(ir, prob, np.float64, num_threads=threads)
+        run = call.run
+    else:   # oracle/_ref did not travel: time the C/numpy restatement instead
+        kind, threads = "port", 1
+        from oracle import ir_eval
+        run = lambda: ir_eval.run_graph(ir, prob, np.float64, num_threads=1)   # noqa: E731
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {"value": alg / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
+            "sample": f"{planes} of {grid} z-planes of the {grid}^3 7-point Laplacian ({prob.num_rows} rows, {nnz} non-zeros), "
+                      f"{steps} calls after {warmup} warm-up, int32 offsets (the reference's only width)",
+            "ms_per_step": dt * 1e3, "edges_per_s": nnz / dt}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 50))
+    r = cpu_reference(args.grid, steps, max(1, min(args.warmup, 3)))
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": max(1, min(args.warmup, 3)), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": f"3D Poisson {args.grid}^3 7-point SpMV, fp64 (CPU arm: a bounded z-slab sample of it)"},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "edges_per_s": r["edges_per_s"]}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+# single-GPU configurations 0-3 (kernel-only numbers, reported beside the headline at N = 1)
+# --------------------------------------------------------------------------------------------------
+def time_config(name, ir, ext, values, indices, ro, outputs, num_rows, nnz, num_cols, alg_bytes, iters, peak, flush_buf):
+    import torch
+    def launch():
+        ext.launch_into(values, indices, ro, outputs, num_rows, nnz, num_cols)
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    warm_ms = e0.elapsed_time(e1) / iters
+    cold = []
+    for _ in range(min(iters, 20)):
+        flush_buf.zero_()            # 256 MB write: evicts the inputs from L2 (not timed)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); launch(); b.record()
+        torch.cuda.synchronize()
+        cold.append(a.elapsed_time(b))
+    cold_ms = float(np.median(cold))
+    return {"config": name, "rows": int(num_rows), "edges": int(nnz), "algorithmic_bytes": int(alg_bytes),
+            "warm": {"ms": warm_ms, "gbs": alg_bytes / warm_ms / 1e6, "frac_of_hbm_peak": alg_bytes / warm_ms / 1e6 / peak,
+                     "edges_per_s": nnz / warm_ms * 1e3, "iters": iters},
+            "cold_l2_flushed": {"ms": cold_ms, "gbs": alg_bytes / cold_ms / 1e6, "frac_of_hbm_peak": alg_bytes / cold_ms / 1e6 / peak,
+                                "edges_per_s": nnz / cold_ms * 1e3, "iters": len(cold)}}
+
+
+def single_gpu_configs(peak: float) -> list:
+    import torch
+    from flexspmv_b200 import graphs, problems
+    from flexspmv_b200.binding import GraphExtension
+    dev = torch.device("cuda", torch.cuda.current_device())
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = []
+
+    def upload(ir, prob):
+        non_gather, gathers, index_names = graphs.operator_signature(ir)
+        vals = [torch.from_numpy(np.ascontiguousarray(prob.values[n])).to(dev) for n in non_gather + gathers]
+        idxs = [torch.from_numpy(np.ascontiguousarray(prob.indices[n])).to(dev) for n in index_names]
+        ro = torch.from_numpy(np.ascontiguousarray(prob.row_offsets)).to(dev)
+        return vals, idxs, ro
+
+    specs = [("config0 2D Poisson 512^2 fp64", "spmv", lambda: problems.poisson2d(512), 8, 200),
+             ("config1 spring-mass 1024^2 fp32", "spring_mass", lambda: problems.spring_mass(1024), 4, 200),
+             ("config2 shallow-water Rusanov 1024^2 fp64", "rusanov", lambda: problems.shallow_water(1024), 8, 200)]
+    for name, gname, make, vb, iters in specs:
+        ir = graphs.ALL_GRAPHS[gname]()
+        prob = make()
+        vals, idxs, ro = upload(ir, prob)
+        dt = vals[0].dtype
+        outs = [torch.empty((prob.num_rows,) + (() if graphs.dim_of(o["shape"]) == 1 else (graphs.dim_of(o["shape"]),)),
+                            dtype=dt, device=dev) for o in ir.outputs]
+        alg = problems.algorithmic_bytes(ir, prob.num_rows, prob.nnz, prob.num_cols, vb, 4)
+        out.append(time_config(name, ir, GraphExtension(ir), vals, idxs, ro, outs, prob.num_rows, prob.nnz, prob.num_cols,
+                               alg, iters, peak, flush))
+        del vals, idxs, ro, outs
+    # config 3 is generated on the device (268 M non-zeros)
+    ir = graphs.spmv_graph()
+    ro, cols, vals, x = problems.powerlaw_device(1 << 24, 3, dev)
+    n, m = x.numel(), cols.numel()
+    y = torch.empty(n, dtype=torch.float32, device=dev)
+    alg = problems.algorithmic_bytes(ir, n, m, n, 4, 4)
+    out.append(time_config("config3 power-law CSR n=2^24 fp32", ir, GraphExtension(ir), [vals, x], [cols], ro, [y], n, m, n, alg,
+                           50, peak, flush))
+    del ro, cols, vals, x, y, flush
+    torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# the CUDA arm
+# --------------------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from flexspmv_b200 import multi_gpu
+    from flexspmv_b200.binding import load_builtin
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    peak, peak_kind = load_peaks()
+    n = args.grid
+    n2 = n * n
+    K, W = args.steps, max(args.warmup, 3)
+
+    # ---- partition + local matrix -----------------------------------------------------------------
+    bounds = multi_gpu.poisson3d_slab_bounds(n, world, dev)
+    z0, z1 = bounds[rank], bounds[rank + 1]
+    first_row = [b * n2 for b in bounds]
+    min_col = [max(0, first_row[r] - n2) if first_row[r + 1] > first_row[r] else first_row[r] for r in range(world)]
+    max_col = [min(n ** 3, first_row[r + 1] + n2) - 1 if first_row[r + 1] > first_row[r] else first_row[r] - 1 for r in range(world)]
+    plan = multi_gpu.make_halo_plans(first_row, min_col, max_col)[rank]
+    ro, cols, vals = multi_gpu.poisson3d_planes_device(n, z0, z1, dev, col_shift=plan.col_shift)
+    g = torch.Generator(device=dev)
+    g.manual_seed(4 * 1000 + rank)
+    x0 = torch.rand(plan.rows, generator=g, device=dev, dtype=torch.float64) * 2.0 - 1.0
+    ext = load_builtin("spmv")
+    op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x0, ext=ext)
+    alg_bytes, nnz_total = poisson3d_bytes(n)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def renorm(step_index: int) -> int:
+        # ||A|| <= 12: rescale before the iterate can overflow fp64 (one tiny extra kernel every 200 steps)
+        if step_index and step_index % 200 == 0:
+            op.owned().mul_(2.0 ** -700)
+            return 1
+        return 0
+
+    for i in range(W):
+        op.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = ext.launches
+    extra = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(K):
+        extra += renorm(W + i)
+        op.step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    clocks = sampler.stop() if rank == 0 else None
+    my_launches = ext.launches - launches0 + extra
+    launches = torch.tensor([my_launches], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(launches)
+    ms_per_step = total_ms / K
+    value = alg_bytes / ms_per_step / 1e6     # GB/s over the whole job
+
+    # ---- end to end through the reference-facing operator with host buffers ---------------------------
+    E = max(1, min(K, args.e2e_steps))
+    hx = torch.empty(plan.rows, dtype=torch.float64).pin_memory()
+    hx.copy_(x0.cpu())
+    hy = torch.empty(plan.rows, dtype=torch.float64).pin_memory()
+    xbuf = op.buf[0]
+    lo = plan.halo_lo
+
+    def e2e_step():
+        xbuf[lo:lo + plan.rows].copy_(hx, non_blocking=True)              # host -> device: this step's input vector
+        multi_gpu.exchange_halos(xbuf, plan)
+        (y,) = ext.merged_spmv_launch(vals, xbuf, cols, ro, plan.rows, plan.local_len)   # the operator the reference wrapper calls
+        hy.copy_(y, non_blocking=True)                                    # device -> host: the step's result
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(E):
+        e2e_step()
+    a1.record()
+    barrier()
+    ems = torch.tensor([a0.elapsed_time(a1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+    e2e_ms = float(ems.item()) / E
+    hb = torch.tensor([plan.rows * 8], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(hb)
+    e2e = {"value": alg_bytes / e2e_ms / 1e6, "unit": UNIT, "h2d_bytes_per_step": int(hb.item()), "d2h_bytes_per_step": int(hb.item()),
+           "ms_per_step": e2e_ms, "steps": E,
+           "what": "per step: pinned-host x -> device, halo exchange, merged_spmv_launch (allocates y), y -> pinned host; "
+                   "the CSR matrix is static across iterations and stays resident"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": f"config4: 3D Poisson {n}^3 7-point SpMV, fp64 values, int64 row offsets, int32 columns, "
+                               f"{nnz_total} non-zeros, x <- A x with one z-plane halo per neighbour per iteration",
+                   "partition": f"{world} nnz-balanced z-slab(s), merge-path tile plan cached across iterations",
+                   "l2": "inputs larger than L2 (per-GPU matrix slab >= 1.8 GB)", "algorithmic_bytes_per_step": alg_bytes,
+                   "halo_bytes_per_neighbour_per_direction": n2 * 8 if world > 1 else 0},
+        "edges_per_s": nnz_total / ms_per_step * 1e3,
+        "frac_of_hbm_peak": value / (peak * world), "hbm_peak_gbs_per_gpu": peak, "hbm_peak_kind": peak_kind,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches.item()),
+    }
+    if world == 1:
+        info = ext.symbols(torch.float64).graph_info
+        line["roofline"] = {"bound": "hbm", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak, "traffic": None,
+                            "kernel": "flex_tile_kernel<spmv_f64, int64 offsets>", "peak_kind": f"of {peak_kind}",
+                            "launch_ms": ms_per_step, "algorithmic_bytes_per_launch": alg_bytes,
+                            "tile": {"block": info.block_threads, "items_per_thread": info.items_per_thread,
+                                     "stages": info.stages, "smem_bytes": info.smem_bytes}}
+        traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(traffic_file):
+            with open(traffic_file) as f:
+                t = json.load(f)
+            if "dram_bytes_per_algorithmic_byte" in t:
+                line["roofline"]["traffic"] = t["dram_bytes_per_algorithmic_byte"] * alg_bytes
+                line["roofline"]["traffic_source"] = t.get("source")
+        del op, ro, cols, vals, x0, xbuf
+        torch.cuda.empty_cache()
+        if not args.no_configs:
+            line["configs"] = single_gpu_configs(peak)
+        if not args.no_cpu:
+            r = cpu_reference(n, 5, 1)
+            line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"]["edges_per_s"] = r["edges_per_s"]
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--grid", type=int, default=512)
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table (N = 1)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (N = 1)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

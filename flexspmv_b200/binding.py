@@ -221,6 +221,30 @@ class GraphExtension:
 
     __call__ = merged_spmv_launch
 
+    def launch_into(self, values: Sequence[torch.Tensor], indices: Sequence[torch.Tensor],
+                    row_end_offsets: Optional[torch.Tensor], outputs: Sequence[torch.Tensor],
+                    num_rows: int, num_edges: int, num_cols: int = 0) -> None:
+        """Same fused pass as ``merged_spmv_launch`` but into caller-provided output tensors (any
+        tensor or slice whose storage is large enough; e.g. the owned part of the next iteration's
+        vector).  No allocation, no checks beyond the C ABI's own; one kernel launch."""
+        dt = values[0].dtype
+        syms = self.symbols(dt)
+        has_red = self.ir.has_reducer
+        device = values[0].device
+        desc = Desc(num_rows if has_red else 0, num_edges, num_cols,
+                    64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
+                    self.tile_items, self.max_ctas, 0)
+        with torch.cuda.device(device):
+            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device)
+            vp = (ctypes.c_void_p * max(len(values), 1))(*[t.data_ptr() for t in values])
+            ip = (ctypes.c_void_p * max(len(indices), 1))(*[t.data_ptr() for t in indices])
+            op = (ctypes.c_void_p * max(len(outputs), 1))(*[t.data_ptr() for t in outputs])
+            st = syms.launch(ctypes.byref(desc), vp, ip,
+                             ctypes.c_void_p(row_end_offsets.data_ptr() if has_red else 0), op,
+                             ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws_bytes), _stream_ptr())
+        check(self.lib, st, "launch_into")
+        self.launches += 1
+
     def device_status(self, dtype: torch.dtype, row_end_offsets: Optional[torch.Tensor] = None) -> int:
         """Reads back the status word of the most recently used workspace (synchronises)."""
         if not self._plans:

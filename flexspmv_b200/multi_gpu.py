@@ -1,0 +1,221 @@
+"""Row-block partitioned SpMV across the GPUs of one node: one process per GPU, rows split into
+nnz-balanced contiguous blocks, each rank holding its block as a local CSR whose column indices point
+into a local vector laid out ``[halo_below | owned | halo_above]``, and a nearest-neighbour halo
+exchange of the vector entries each iteration over NCCL (NVLink / NVSwitch) -- or gloo on CPU for the
+index-logic tests.  The reference has no multi-GPU code of its own (its drivers only forward a
+``--comm_backend`` flag to the third-party ``easier`` runtime: easier_spmv.py:142,
+test_full/easier_full.py:46); the partition search is the same lower-bound family as its
+MergePathSearch (include/merged_spmv_kernels.cuh:19-50).
+
+Only matrices whose out-of-block columns fall inside the neighbouring blocks (banded / stencil
+matrices, e.g. the 7-point Laplacian split into z-slabs) are supported: the exchange is two
+send/recv pairs per rank, no gather lists.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+
+
+def balanced_row_blocks(row_offsets: torch.Tensor, parts: int, snap: int = 1) -> torch.Tensor:
+    """first_row[k] = lower_bound(row_offsets, k*nnz/parts) rounded to a multiple of ``snap`` rows;
+    torch restatement used on CPU tensors (tests, gloo ranks).  On CUDA tensors the C-ABI kernel
+    ``flexspmv_row_blocks`` is used."""
+    n = row_offsets.numel() - 1
+    if row_offsets.is_cuda:
+        import ctypes
+        from .binding import check, load_library
+        lib = load_library()
+        out = torch.empty(parts + 1, dtype=torch.int64, device=row_offsets.device)
+        bits = 64 if row_offsets.dtype == torch.int64 else 32
+        with torch.cuda.device(row_offsets.device):
+            st = lib.flexspmv_row_blocks(ctypes.c_void_p(row_offsets.data_ptr()), bits, ctypes.c_int64(n), parts,
+                                         ctypes.c_int64(snap), ctypes.c_void_p(out.data_ptr()),
+                                         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        check(lib, st, "flexspmv_row_blocks")
+        return out
+    ro = row_offsets.to(torch.int64)
+    nnz = int(ro[-1])
+    first = [0]
+    for k in range(1, parts):
+        target = (nnz * k) // parts
+        lo = int(torch.searchsorted(ro, torch.tensor([target], dtype=torch.int64), right=False)[0])
+        if snap > 1:
+            lo = ((lo + snap // 2) // snap) * snap
+        lo = min(lo, n)
+        lo = max(lo, first[-1])
+        first.append(lo)
+    first.append(n)
+    return torch.tensor(first, dtype=torch.int64)
+
+
+@dataclass
+class HaloPlan:
+    """Index logic of one rank's block (pure integers; identical on CPU and GPU)."""
+    rank: int
+    world: int
+    row_begin: int
+    row_end: int
+    halo_lo: int      # entries needed from the block below (global columns [row_begin-halo_lo, row_begin))
+    halo_hi: int      # entries needed from the block above (global columns [row_end, row_end+halo_hi))
+    send_lo: int      # entries the rank below needs from the head of this block
+    send_hi: int      # entries the rank above needs from the tail of this block
+
+    @property
+    def rows(self) -> int:
+        return self.row_end - self.row_begin
+
+    @property
+    def local_len(self) -> int:
+        return self.halo_lo + self.rows + self.halo_hi
+
+    @property
+    def col_shift(self) -> int:
+        """global column - col_shift = index into the local vector"""
+        return self.row_begin - self.halo_lo
+
+
+def make_halo_plans(first_row: List[int], min_col: List[int], max_col: List[int]) -> List[HaloPlan]:
+    """first_row: world+1 block boundaries; min_col/max_col: smallest / largest global column
+    referenced by each block's rows (for an empty block pass row_begin / row_begin-1)."""
+    world = len(first_row) - 1
+    plans = []
+    for r in range(world):
+        rb, re = first_row[r], first_row[r + 1]
+        lo = max(0, rb - min_col[r])
+        hi = max(0, max_col[r] - re + 1)
+        plans.append(HaloPlan(r, world, rb, re, lo, hi, 0, 0))
+    for r in range(world):
+        if plans[r].halo_lo:
+            if r == 0 or plans[r].halo_lo > plans[r - 1].rows:
+                raise NotImplementedError("halo reaches beyond the neighbouring block (matrix is not banded enough)")
+            plans[r - 1].send_hi = plans[r].halo_lo
+        if plans[r].halo_hi:
+            if r == world - 1 or plans[r].halo_hi > plans[r + 1].rows:
+                raise NotImplementedError("halo reaches beyond the neighbouring block (matrix is not banded enough)")
+            plans[r + 1].send_lo = plans[r].halo_hi
+    return plans
+
+
+def exchange_halos(x_local: torch.Tensor, plan: HaloPlan, group=None) -> None:
+    """One halo exchange of the local vector (in place): the head / tail of the owned part go to the
+    neighbours' halo regions.  NCCL send/recv pairs batched in one group (or gloo on CPU)."""
+    import torch.distributed as dist
+    if plan.world == 1:
+        return
+    lo, rows = plan.halo_lo, plan.rows
+    owned = x_local[lo:lo + rows]
+    ops = []
+    if plan.rank > 0:
+        if plan.send_lo:
+            ops.append(dist.P2POp(dist.isend, owned[:plan.send_lo], plan.rank - 1, group))
+        if plan.halo_lo:
+            ops.append(dist.P2POp(dist.irecv, x_local[:lo], plan.rank - 1, group))
+    if plan.rank < plan.world - 1:
+        if plan.send_hi:
+            ops.append(dist.P2POp(dist.isend, owned[rows - plan.send_hi:], plan.rank + 1, group))
+        if plan.halo_hi:
+            ops.append(dist.P2POp(dist.irecv, x_local[lo + rows:], plan.rank + 1, group))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+
+
+# ----------------------------------------------------------------------------------------------
+# config 4 built per rank on the device
+# ----------------------------------------------------------------------------------------------
+
+def poisson3d_planes_device(n: int, z_begin: int, z_end: int, device, value_dtype=torch.float64,
+                            offset_dtype=torch.int64, col_shift: int = 0, chunk_planes: int = 16):
+    """CSR of the rows of z-planes [z_begin, z_end) of the 7-point Laplacian on an n^3 grid (x
+    fastest, Dirichlet, 6 / -1), built on ``device`` in chunks of planes.  Column indices are global
+    minus ``col_shift``.  Same matrix as problems.poisson3d (tests compare them)."""
+    n2 = n * n
+    rows = (z_end - z_begin) * n2
+    counts = torch.empty(rows, dtype=torch.int64, device=device)
+    cols_parts, vals_parts = [], []
+    diag = torch.tensor([-1.0, -1.0, -1.0, 6.0, -1.0, -1.0, -1.0], dtype=value_dtype, device=device)
+    steps = torch.tensor([-n2, -n, -1, 0, 1, n, n2], dtype=torch.int64, device=device)
+    for zb in range(z_begin, z_end, chunk_planes):
+        ze = min(z_end, zb + chunk_planes)
+        idx = torch.arange(zb * n2, ze * n2, dtype=torch.int64, device=device)
+        k = idx // n2
+        r = idx - k * n2
+        j = r // n
+        i = r - j * n
+        valid = torch.stack([k > 0, j > 0, i > 0, torch.ones_like(i, dtype=torch.bool), i < n - 1, j < n - 1, k < n - 1], dim=1)
+        cand = idx[:, None] + steps[None, :]
+        counts[(zb - z_begin) * n2:(ze - z_begin) * n2] = valid.sum(dim=1)
+        cols_parts.append((cand[valid] - col_shift).to(torch.int32))
+        vals_parts.append(diag.expand(idx.numel(), 7)[valid].contiguous())
+        del idx, k, r, j, i, valid, cand
+    ro = torch.zeros(rows + 1, dtype=torch.int64, device=device)
+    torch.cumsum(counts, dim=0, out=ro[1:])
+    del counts
+    cols = torch.cat(cols_parts) if len(cols_parts) > 1 else cols_parts[0]
+    del cols_parts
+    vals = torch.cat(vals_parts) if len(vals_parts) > 1 else vals_parts[0]
+    del vals_parts
+    return ro.to(offset_dtype), cols, vals
+
+
+def poisson3d_row_offsets(n: int, device, offset_dtype=torch.int64, chunk_planes: int = 64) -> torch.Tensor:
+    """Row offsets (leading 0) of the whole n^3 7-point Laplacian, from the closed-form row lengths
+    7 - (number of grid faces the point touches); used to choose the slab boundaries."""
+    n2 = n * n
+    counts = torch.empty(n * n2, dtype=torch.int64, device=device)
+    for zb in range(0, n, chunk_planes):
+        ze = min(n, zb + chunk_planes)
+        idx = torch.arange(zb * n2, ze * n2, dtype=torch.int64, device=device)
+        k = idx // n2
+        r = idx - k * n2
+        j = r // n
+        i = r - j * n
+        c = 7 - (k == 0).to(torch.int64) - (k == n - 1).to(torch.int64) - (j == 0).to(torch.int64) \
+            - (j == n - 1).to(torch.int64) - (i == 0).to(torch.int64) - (i == n - 1).to(torch.int64)
+        counts[zb * n2:ze * n2] = c
+    ro = torch.zeros(n * n2 + 1, dtype=torch.int64, device=device)
+    torch.cumsum(counts, dim=0, out=ro[1:])
+    return ro.to(offset_dtype)
+
+
+def poisson3d_slab_bounds(n: int, world: int, device) -> List[int]:
+    """z-plane boundaries of the nnz-balanced slabs: the row-block search (C-ABI kernel on CUDA, its
+    torch restatement on CPU) on the global row offsets, snapped to whole planes (snap = n^2 rows)."""
+    ro = poisson3d_row_offsets(n, device)
+    first = balanced_row_blocks(ro, world, snap=n * n)
+    return [int(v) // (n * n) for v in first.cpu().tolist()]
+
+
+class PartitionedSpmv:
+    """One rank's share of y = A x for a row-block partitioned banded matrix, iterated as
+    x <- A x: the local vector is double-buffered ([halo_lo | owned | halo_hi] each) so an
+    iteration is "exchange halos of the current buffer, then one fused SpMV launch that writes the
+    owned part of the other buffer"."""
+
+    def __init__(self, plan: HaloPlan, row_offsets: torch.Tensor, cols_local: torch.Tensor, vals: torch.Tensor,
+                 x_owned: torch.Tensor, group=None, ext=None):
+        from .binding import load_builtin
+        self.plan, self.group = plan, group
+        self.ro, self.cols, self.vals = row_offsets, cols_local, vals
+        self.ext = ext or load_builtin("spmv")
+        dev = vals.device
+        self.buf = [torch.zeros(plan.local_len, dtype=vals.dtype, device=dev) for _ in range(2)]
+        self.cur = 0
+        self.buf[0][plan.halo_lo:plan.halo_lo + plan.rows] = x_owned
+        self.nnz = int(cols_local.numel())
+
+    def owned(self, which: Optional[int] = None) -> torch.Tensor:
+        b = self.buf[self.cur if which is None else which]
+        return b[self.plan.halo_lo:self.plan.halo_lo + self.plan.rows]
+
+    def step(self) -> torch.Tensor:
+        """halo exchange + y = A_local x_local; y becomes the next iteration's owned vector."""
+        x = self.buf[self.cur]
+        exchange_halos(x, self.plan, self.group)
+        y = self.owned(1 - self.cur)
+        self.ext.launch_into([self.vals, x], [self.cols], self.ro, [y], self.plan.rows, self.nnz, self.plan.local_len)
+        self.cur = 1 - self.cur
+        return y

@@ -270,3 +270,36 @@ def algorithmic_bytes(graph_ir, num_rows: int, nnz: int, num_vertices: int, valu
         else:
             b += value_bytes * d * nnz
     return b
+
+
+# ----------------------------------------------------------------------------------------------
+# device-side generators for the largest configuration (torch generator, same distributions)
+# ----------------------------------------------------------------------------------------------
+
+def powerlaw_device(n: int = 1 << 24, seed: int = 3, device="cuda", mean_len: float = 16.0, cap: int = 100_000):
+    """Config 3 built directly in GPU memory: same construction as ``powerlaw`` (power-law lengths,
+    uniform columns sorted within each row through the key row<<32|col, N(0,1) values, U(-1,1) x) but
+    drawn from torch's device generator, so the arrays are not bit-identical to the numpy ones.
+    Returns (row_offsets int32, cols int32, vals float32, x float32)."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    cap = min(cap, n)
+    u = torch.rand(n, generator=g, device=device, dtype=torch.float64)
+    raw = torch.clamp(torch.floor(1.0 / (1.0 - u)), max=float(cap))
+    ln = torch.clamp(torch.round(raw * (mean_len / raw.mean())), 1, cap).to(torch.int64)
+    del u, raw
+    ro = torch.zeros(n + 1, dtype=torch.int64, device=device)
+    torch.cumsum(ln, dim=0, out=ro[1:])
+    m = int(ro[-1].item())
+    assert m < 2 ** 31
+    key = torch.repeat_interleave(torch.arange(n, dtype=torch.int64, device=device), ln)
+    del ln
+    key <<= 32
+    key |= torch.randint(0, n, (m,), generator=g, device=device, dtype=torch.int64)
+    key = torch.sort(key).values
+    cols = (key & 0xFFFFFFFF).to(torch.int32)
+    del key
+    vals = torch.randn(m, generator=g, device=device, dtype=torch.float32)
+    x = torch.rand(n, generator=g, device=device, dtype=torch.float32) * 2.0 - 1.0
+    return ro.to(torch.int32), cols, vals, x
