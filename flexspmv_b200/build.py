@@ -18,9 +18,9 @@ from .graphs import ALL_GRAPHS, GRAPH_DTYPES
 PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
-BUILD = os.path.join(ROOT, "build", "flexspmv")
+BUILD = os.environ.get("FLEXSPMV_BUILD_DIR", os.path.join(ROOT, "build", "flexspmv"))
 LIB_DIR = os.path.join(PKG, "lib")
-LIB_PATH = os.path.join(LIB_DIR, "libflexspmv_b200.so")
+LIB_PATH = os.environ.get("FLEXSPMV_LIB_OUT", os.path.join(LIB_DIR, "libflexspmv_b200.so"))
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 NVCC_FLAGS = [
@@ -63,7 +63,7 @@ def generated_units():
 
 def build(force: bool = False, jobs: int | None = None, verbose_ptxas: bool = False) -> str:
     os.makedirs(BUILD, exist_ok=True)
-    os.makedirs(LIB_DIR, exist_ok=True)
+    os.makedirs(os.path.dirname(LIB_PATH), exist_ok=True)
     hd = _headers_digest()
     extra = ["-Xptxas", "-v"] if verbose_ptxas else []
     work = []   # (src, obj)

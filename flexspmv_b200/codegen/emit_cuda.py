@@ -58,32 +58,42 @@ def smem_bytes(ir: GraphIR, dtype: str, block: int, ipt: int, stages: int) -> in
     stage = -(-(tile * max(8, per_edge) + 32 * (ns + 1) + 16) // 128) * 128
     fixed = 8 * stages + (32 + 4 * max(ns, 1) + 16) * stages + 4 * (block + 1) + 4 * (block // 32) \
         + vb * acc * (block // 32) + vb * acc * 2 + 16 + 8 * 16 + 128
-    return fixed + vb * acc * (tile // 2) + stages * stage
+    return fixed + 4 * (tile + 1) + 2 * tile + vb * acc * tile + stages * stage
 
 
-def choose_config(ir: GraphIR, dtype: str, smem_budget: int = 110 * 1024) -> Tuple[int, int, int, int]:
-    """(block threads, merge items per thread, stages, min CTAs per SM).  Items per thread are odd
-    (conflict-free shared-memory strides when a thread's items are all edges), shrink with the bytes
-    a thread keeps in registers for its in-flight gathers, and shrink further until two CTAs fit the
-    228 KB of shared memory of one SM."""
-    vb = VBYTES[dtype]
-    regs = sum(dim_of(s["shape"]) * vb // 4 for s in ir.selector_register if s.get("selector") == 1)
-    regs = max(regs, 1)
-    ipt = max(3, min(11, 64 // regs))
-    if ipt % 2 == 0:
-        ipt -= 1
+def choose_config(ir: GraphIR, dtype: str) -> Tuple[int, int, int, int]:
+    """(consumer threads, merge items per thread, stages, min CTAs per SM).  The kernel is bound by
+    latency per tile rather than by bytes in flight, so the heuristic prefers many resident CTAs (4,
+    then 3, then 2 per SM) over big tiles: it takes the largest odd items-per-thread in [3, 5] whose
+    shared-memory carve-up still lets that many CTAs share the 228 KB of one SM."""
     block, stages = 256, 2
-    while ipt > 1 and smem_bytes(ir, dtype, block, ipt, stages) > smem_budget:
-        ipt -= 2
-    while block > 64 and smem_bytes(ir, dtype, block, ipt, stages) > smem_budget:
+    for ctas in (4, 3, 2):
+        budget = (227 * 1024) // ctas - 1024
+        for ipt in (5, 3):
+            if smem_bytes(ir, dtype, block, ipt, stages) <= budget:
+                return block, ipt, stages, ctas
+    ipt = 1
+    while block > 64 and smem_bytes(ir, dtype, block, ipt, stages) > 110 * 1024:
         block //= 2
     return block, ipt, stages, 2
+
+
+def _override(symbol: str):
+    """Tuning hook: FLEXSPMV_CFG_OVERRIDE="spmv_f64=256,7,2,3;rusanov_f64=128,5,3,4" replaces the
+    heuristic tile configuration (block, items per thread, stages, min CTAs per SM) at build time."""
+    import os
+    for part in os.environ.get("FLEXSPMV_CFG_OVERRIDE", "").split(";"):
+        if "=" in part:
+            k, v = part.split("=", 1)
+            if k.strip() == symbol:
+                return tuple(int(x) for x in v.split(","))
+    return None
 
 
 def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None) -> str:
     cty, sfx = CTYPE[dtype]
     symbol = symbol or f"{ir.name}_{sfx}"
-    block, ipt, stages, min_ctas = config or choose_config(ir, dtype)
+    block, ipt, stages, min_ctas = config or _override(symbol) or choose_config(ir, dtype)
     non_gather, gathers, index_names = operator_signature(ir)
     value_names = non_gather + gathers
     in_dims = {i["name"]: dim_of(i["shape"]) for i in ir.inputs if i["dtype"] != "int"}
@@ -134,6 +144,8 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None) 
     w(f"  static constexpr bool kHasReducer = {'true' if has_reducer else 'false'};")
     w(f"  static constexpr int kNumReducers = {len(reducers)}, kAccDim = {max(acc_off, 1)}, kAggDim = {agg_off};")
     w(f"  static constexpr int kNumStreams = {len(streams)};")
+    needs_row = any(s.get("selector") == 1 and s.get("row_identity") for s in ir.selector_register)
+    w(f"  static constexpr bool kGatherNeedsRow = {'true' if needs_row else 'false'};")
     w("  static constexpr int kStreamBytesPerEdge = 0" + "".join(f" + {b}" for _, _, b in streams) + ";")
     w("  struct Params {")
     for n in value_names:

@@ -113,7 +113,7 @@ struct GraphApi {
     std::call_once(once, [&] {
       init_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
       if (init_err == cudaSuccess)
-        init_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, Cfg::kBlock, L::kTotal);
+        init_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, Cfg::kBlock + 32, L::kTotal);
     });
     if (init_err != cudaSuccess) { (void)cudaGetLastError(); return (int)init_err; }
     if (resident < 1) return FLEXSPMV_ERR_TOO_LARGE;
@@ -128,7 +128,7 @@ struct GraphApi {
     a.carry_row = reinterpret_cast<long long*>(static_cast<char*>(ws) + h.carry_row_offset);
     a.carry_val = static_cast<char*>(ws) + h.carry_val_offset;
     a.num_rows = d->num_rows; a.num_edges = d->num_edges; a.num_tiles = tiles;
-    kernel<<<(unsigned)grid, Cfg::kBlock, L::kTotal, st>>>(p, a);
+    kernel<<<(unsigned)grid, Cfg::kBlock + 32, L::kTotal, st>>>(p, a);   // + the producer warp
     return (int)cudaGetLastError();
   }
 

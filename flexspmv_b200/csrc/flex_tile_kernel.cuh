@@ -25,10 +25,10 @@ struct TileCfg {
   static constexpr int kMinCtas = MIN_CTAS_;
   static constexpr int kTile = BLOCK_ * IPT_;
   static constexpr int kWarps = BLOCK_ / 32;
-  static constexpr int kRowsCap = (BLOCK_ * IPT_) / 2;  // rows of a tile staged in smem; the rest go direct
 };
 
 constexpr int kMaxCtas = 2048;            // capacity of the per-CTA carry arrays in the workspace
+constexpr int kShortRowMax = 64;              // tiles whose rows are all at most this long reduce one thread per row
 constexpr uint64_t kWaitPolls = 1000000000ull;  // bound on every mbarrier wait: one second of %globaltimer
 
 template <class G>
@@ -55,14 +55,16 @@ struct TileSmemLayout {
     uint32_t stream_off[G::kNumStreams > 0 ? G::kNumStreams : 1];
   };
   static constexpr int kOffBars = 0;
-  static constexpr int kOffCtl = int(align_up(kOffBars + 8 * Cfg::kStages, 16));
+  static constexpr int kOffCtl = int(align_up(kOffBars + 16 * Cfg::kStages, 16));
   static constexpr int kOffXs = int(align_up(kOffCtl + sizeof(Ctl) * Cfg::kStages, 16));
   static constexpr int kOffWKey = int(align_up(kOffXs + 4 * (Cfg::kBlock + 1), 16));
   static constexpr int kOffWVal = int(align_up(kOffWKey + 4 * Cfg::kWarps, 16));
   static constexpr int kOffCarry = int(align_up(kOffWVal + sizeof(V) * kAcc * Cfg::kWarps, 16));
   static constexpr int kOffFlag = int(align_up(kOffCarry + sizeof(V) * kAcc * 2, 16));
-  static constexpr int kOffOut = int(align_up(kOffFlag + 16, 16));
-  static constexpr int kOffStages = int(align_up(kOffOut + sizeof(V) * kAcc * Cfg::kRowsCap, 128));
+  static constexpr int kOffRel = int(align_up(kOffFlag + 16, 16));
+  static constexpr int kOffRowId = int(align_up(kOffRel + 4 * (Cfg::kTile + 1), 16));
+  static constexpr int kOffProd = int(align_up(kOffRowId + (G::kGatherNeedsRow ? 2 * Cfg::kTile : 0), 16));
+  static constexpr int kOffStages = int(align_up(kOffProd + sizeof(V) * kAcc * Cfg::kTile, 128));
   static constexpr int kTotal = kOffStages + kStageBytes * Cfg::kStages;
 };
 
@@ -109,7 +111,7 @@ __device__ __forceinline__ Window make_window(const void* gbase, uint32_t eb, lo
 }
 
 template <class G, typename OffsetT, class Cfg>
-__global__ void __launch_bounds__(Cfg::kBlock, Cfg::kMinCtas)
+__global__ void __launch_bounds__(Cfg::kBlock + 32, Cfg::kMinCtas)
 flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   using V = typename G::V;
   using L = TileSmemLayout<G, OffsetT, Cfg>;
@@ -119,14 +121,16 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   constexpr int BLOCK = Cfg::kBlock, IPT = Cfg::kIpt, S = Cfg::kStages;
 
   extern __shared__ __align__(128) unsigned char smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);    // "full": a stage's copies have landed
+  uint64_t* empty = bars + S;                                          // "empty": the consumers released a stage
   Ctl* ctls = reinterpret_cast<Ctl*>(smem + L::kOffCtl);
-  int* s_xs = reinterpret_cast<int*>(smem + L::kOffXs);
   int* s_wkey = reinterpret_cast<int*>(smem + L::kOffWKey);
   V* s_wval = reinterpret_cast<V*>(smem + L::kOffWVal);
   V* s_carry = reinterpret_cast<V*>(smem + L::kOffCarry);
   int* s_flag = reinterpret_cast<int*>(smem + L::kOffFlag);
-  V* s_out = reinterpret_cast<V*>(smem + L::kOffOut);
+  int* s_rel = reinterpret_cast<int*>(smem + L::kOffRel);
+  unsigned short* s_rowid = reinterpret_cast<unsigned short*>(smem + L::kOffRowId);
+  V* s_prod = reinterpret_cast<V*>(smem + L::kOffProd);
   unsigned char* s_stage = smem + L::kOffStages;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -146,7 +150,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   const long long t_begin = (long long)blockIdx.x * q + ((long long)blockIdx.x < rem ? blockIdx.x : rem);
   const int count = (int)(q + ((long long)blockIdx.x < rem ? 1 : 0));
 
-  // ---- producer: stage one tile (thread 0 only) ---------------------------------------------------
+  // ---- producer: stage one tile (lane 0 of the producer warp) ---------------------------------------
   auto issue = [&](long long tile, int s) {
     const long long row0 = (long long)coords[2 * tile], nz0 = (long long)coords[2 * tile + 1];
     const long long row1 = (long long)coords[2 * tile + 2], nz1 = (long long)coords[2 * tile + 3];
@@ -164,45 +168,66 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     for (int i = 0; i <= NS; ++i) { off[i] = cur; cur += w[i].span; total += w[i].bulk_bytes; }
     c.roff_off = off[0] + w[0].lead;
     static_for<NS>([&](auto I) { c.stream_off[I.value] = off[I.value + 1] + w[I.value + 1].lead; });
-    fence_proxy_async_smem();   // earlier generic reads/writes of this stage are ordered before the copies
-    mbar_expect_tx(&bars[s], total);
+    // the ragged tail (last < 16 bytes of an array) is fetched with plain loads BEFORE the arrive below,
+    // whose release makes it (and the control block) visible to every consumer that acquires the phase
 #pragma unroll
     for (int i = 0; i <= NS; ++i) {
-      if (w[i].bulk_bytes) bulk_g2s(dst + off[i], w[i].src, w[i].bulk_bytes, &bars[s]);
-      if (w[i].tail_bytes) {   // last < 16 bytes of an array: plain 4-byte loads
+      if (w[i].tail_bytes) {
         const uint32_t so = off[i] + (uint32_t)(w[i].tail_src - w[i].src);
         for (uint32_t b = 0; b < w[i].tail_bytes; b += 4)
           *reinterpret_cast<uint32_t*>(dst + so + b) = *reinterpret_cast<const uint32_t*>(w[i].tail_src + b);
       }
     }
+    fence_proxy_async_smem();   // earlier generic accesses to this stage are ordered before the bulk copies
+    mbar_expect_tx(&bars[s], total);
+#pragma unroll
+    for (int i = 0; i <= NS; ++i) {
+      if (w[i].bulk_bytes) bulk_g2s(dst + off[i], w[i].src, w[i].bulk_bytes, &bars[s]);
+    }
   };
 
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < S; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < S; ++s) { mbar_init(&bars[s], 1); mbar_init(&empty[s], 1); }
     mbar_fence_init();
   }
   if (tid < 2 * kAcc) s_carry[tid] = V(0);
-  __syncthreads();
-  if (tid == 0) {
-    for (int s = 0; s < S && s < count; ++s) issue(t_begin + s, s);
+  __syncthreads();   // the only barrier that includes the producer warp
+
+  // ---- producer warp: runs up to S tiles ahead of the consumers, off their critical path -----------
+  if (warp == Cfg::kWarps) {
+    if (lane == 0) {
+      int issued = 0;
+      bool pfail = false;
+      for (int k = 0; k < count; ++k) {
+        const int s = k % S;
+        if (k >= S && !mbar_wait_bounded(&empty[s], (uint32_t)(k / S - 1) & 1u, kWaitPolls)) { pfail = true; break; }
+        issue(t_begin + k, s);
+        issued = k + 1;
+      }
+      if (pfail) {   // the consumers never released a stage: flag it, let copies in flight land, leave
+        atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
+        a.header->debug[4] = (uint32_t)issued; a.header->debug[5] = blockIdx.x;
+        for (int j = issued > S ? issued - S : 0; j < issued; ++j)
+          mbar_wait_bounded(&bars[j % S], (uint32_t)(j / S) & 1u, kWaitPolls);
+      }
+    }
+    return;
   }
 
+  // ---- consumers (threads 0 .. BLOCK-1); their barriers are the named barrier 1 ---------------------
   bool failed = false;
   long long last_row1 = 0;
   for (int k = 0; k < count; ++k) {
     const int s = k % S;
     const uint32_t parity = (uint32_t)(k / S) & 1u;
-    const int ok = __syncthreads_and(mbar_wait_bounded(&bars[s], parity, kWaitPolls) ? 1 : 0);
+    const bool ok = named_bar_and(1, BLOCK, mbar_wait_bounded(&bars[s], parity, kWaitPolls));
     if (!ok) {
       if (tid == 0) {
         atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
         a.header->debug[0] = (uint32_t)(t_begin + k); a.header->debug[1] = (uint32_t)s; a.header->debug[2] = blockIdx.x;
       }
       failed = true;
-      // give the copies still in flight (later stages) a bounded chance to land before leaving
-      for (int j = 1; j < S && k + j < count; ++j)
-        mbar_wait_bounded(&bars[(k + j) % S], (uint32_t)((k + j) / S) & 1u, kWaitPolls);
       break;
     }
     const Ctl& c = ctls[s];
@@ -214,87 +239,151 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     static_for<NS>([&](auto I) { tile.base[I.value] = reinterpret_cast<const char*>(stage + c.stream_off[I.value]); });
     last_row1 = row0 + nrows;
 
-    // relative edge index at which local row r ends (rows >= nrows end beyond the tile)
-    auto rend = [&](int r) -> int { return r < nrows ? (int)((long long)s_rend[r] - nz0) : 0x7fffffff; };
+    // row ends as 32-bit edge indices relative to the tile, with a sentinel behind the last row; on the
+    // way, find out whether any row (or the trailing partial row) of the tile is long
+    bool my_long = false;
+    for (int r = tid; r < nrows; r += BLOCK) {
+      const long long end_r = (long long)s_rend[r];
+      const long long beg_r = r ? (long long)s_rend[r - 1] : nz0;
+      s_rel[r] = (int)(end_r - nz0);
+      my_long |= (end_r - beg_r) > kShortRowMax;
+    }
+    if (tid == 0) {
+      s_rel[nrows] = 0x7fffffff;
+      const long long beg_t = nrows ? (long long)s_rend[nrows - 1] : nz0;
+      my_long |= (nz0 + nnz - beg_t) > kShortRowMax;
+    }
 
-    // ---- this thread's merge-path span ------------------------------------------------------------
+    // this thread's merge-path span (long-row tiles only): items [d0, d1), starting at (row xs, edge ys)
     const int total_items = nrows + nnz;
     const int d0 = min(tid * IPT, total_items);
-    const int d1 = min(d0 + IPT, total_items);
-    int xs, ys;
-    {
-      long long x, y;
-      merge_path_search<long long, OffsetT>((long long)d0, s_rend, nz0, (long long)nrows, (long long)nnz, x, y);
-      xs = (int)x; ys = (int)y;
-    }
-    s_xs[tid] = xs;
-    if (tid == 0) s_xs[BLOCK] = nrows;
-    __syncthreads();   // [A]
-    const int xe = s_xs[tid + 1];
-    const int ye = d1 - xe;
+    const int n_items = min(d0 + IPT, total_items) - d0;
+    int xs = 0, ys = 0;
+    bool long_tile = false;
 
-    // ---- locate the row of every owned edge and issue the gathers ---------------------------------
-    int rowk[IPT];
-    typename G::Gathered g[IPT];
+    if constexpr (G::kGatherNeedsRow) {
+      // the map needs the row of every edge
+      long_tile = named_bar_or(1, BLOCK, my_long);   // [R] s_rel complete, tile classified
+      if (!long_tile) {
+        // short rows: one thread per row (the trailing partial row is local row `nrows`)
+        for (int r = tid; r <= nrows; r += BLOCK) {
+          const int lo = r ? s_rel[r - 1] : 0;
+          const int hi = r < nrows ? s_rel[r] : nnz;
+          for (int e = lo; e < hi; ++e) s_rowid[e] = (unsigned short)r;
+        }
+      } else {
+        merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
+        int row = xs, nz = ys, re = s_rel[xs];
+#pragma unroll
+        for (int i = 0; i < IPT; ++i) {
+          if (i < n_items) {
+            if (nz < re) { s_rowid[nz] = (unsigned short)row; ++nz; }
+            else { ++row; re = s_rel[row]; }
+          }
+        }
+      }
+      named_bar_sync(1, BLOCK);   // [W] s_rowid complete
+    }
+
+    // ---- phase 1: gather + map of every edge, lanes on consecutive edges; products to shared memory ---
     {
-      int r = xs, re = rend(xs);
+      typename G::Gathered g[IPT];
 #pragma unroll
       for (int i = 0; i < IPT; ++i) {
-        const int e = ys + i;
-        rowk[i] = -1;
-        if (e < ye) {
-          while (re <= e) { ++r; re = rend(r); }
-          rowk[i] = r;
-          G::gather(p, tile, e, row0 + r, g[i]);
+        const int e = i * BLOCK + tid;
+        if (e < nnz) {
+          long long row = 0;
+          if constexpr (G::kGatherNeedsRow) row = row0 + s_rowid[e];
+          G::gather(p, tile, e, row, g[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) {
+        const int e = i * BLOCK + tid;
+        if (e < nnz) {
+          V prod[kAcc];
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
+          G::map(p, tile, e, nz0 + e, g[i], prod);
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) s_prod[j * Cfg::kTile + e] = prod[j];
         }
       }
     }
+    if constexpr (G::kGatherNeedsRow) named_bar_sync(1, BLOCK);        // [P] products complete
+    else long_tile = named_bar_or(1, BLOCK, my_long);                   // [P] + s_rel complete, tile classified
+    if (tid == 0) mbar_arrive(&empty[s]);   // the staged arrays are dead: the producer may refill this stage
 
-    // ---- map + per-thread segmented sums ----------------------------------------------------------
+    if (!long_tile) {
+      // ---- phase 2, short rows: one thread per row sums its products and stores the row (coalesced);
+      //      local row 0 continues the CTA's carry, local row `nrows` (partial) becomes the next carry ----
+      for (int r = tid; r <= nrows; r += BLOCK) {
+        const int lo = r ? s_rel[r - 1] : 0;
+        const int hi = r < nrows ? s_rel[r] : nnz;
+        V sum[kAcc];
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[(k & 1) * kAcc + j] : V(0);
+        for (int e = lo; e < hi; ++e) {
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) sum[j] += s_prod[j * Cfg::kTile + e];
+        }
+        if (r < nrows) {
+          static_for<G::kNumReducers>([&](auto R) {
+            constexpr int d = G::template red_dim<R.value>();
+            constexpr int o = G::template red_off<R.value>();
+            V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + r) * d;
+#pragma unroll
+            for (int j = 0; j < d; ++j) dst[j] = sum[o + j];
+          });
+        } else {
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) s_carry[((k + 1) & 1) * kAcc + j] = sum[j];
+        }
+      }
+      continue;   // the next tile's first barrier orders these reads before anything is overwritten
+    }
+
+    // ---- phase 2, long rows: every thread reduces its merge-path span: exactly n_items steps, each
+    //      consuming one edge (accumulate) or one row end (store the row, reset) ------------------------
+    if constexpr (!G::kGatherNeedsRow) merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
     V acc[kAcc], first_val[kAcc];
 #pragma unroll
-    for (int i = 0; i < kAcc; ++i) { acc[i] = V(0); first_val[i] = V(0); }
-    bool had_emit = false;
-    int cur = xs;
-    auto store_row = [&](int r, const V* v) {   // final value of a row that ends in this tile
-      static_for<G::kNumReducers>([&](auto R) {
-        constexpr int d = G::template red_dim<R.value>();
-        constexpr int o = G::template red_off<R.value>();
-        if (r < Cfg::kRowsCap) {
-          V* dst = s_out + (size_t)o * Cfg::kRowsCap + (size_t)r * d;
+    for (int j = 0; j < kAcc; ++j) { acc[j] = V(0); first_val[j] = V(0); }
+    int row = xs;
+    {
+      int nz = ys, re = s_rel[xs];
 #pragma unroll
-          for (int i = 0; i < d; ++i) dst[i] = v[o + i];
-        } else {
-          V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + r) * d;
+      for (int i = 0; i < IPT; ++i) {
+        if (i < n_items) {
+          if (nz < re) {
 #pragma unroll
-          for (int i = 0; i < d; ++i) dst[i] = v[o + i];
+            for (int j = 0; j < kAcc; ++j) acc[j] += s_prod[j * Cfg::kTile + nz];
+            ++nz;
+          } else {
+            // the first row a thread closes may have begun in earlier threads: keep it for after the scan
+            if (row == xs) {
+#pragma unroll
+              for (int j = 0; j < kAcc; ++j) first_val[j] = acc[j];
+            } else {
+              static_for<G::kNumReducers>([&](auto R) {
+                constexpr int d = G::template red_dim<R.value>();
+                constexpr int o = G::template red_off<R.value>();
+                V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + row) * d;
+#pragma unroll
+                for (int j = 0; j < d; ++j) dst[j] = acc[o + j];
+              });
+            }
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) acc[j] = V(0);
+            ++row;
+            re = s_rel[row];
+          }
         }
-      });
-    };
-    auto flush_to = [&](int target) {   // rows cur .. target-1 end here: first gets acc, the rest are empty
-      if (!had_emit) {
-        had_emit = true;
-#pragma unroll
-        for (int i = 0; i < kAcc; ++i) first_val[i] = acc[i];
-      } else {
-        store_row(cur, acc);
-      }
-#pragma unroll
-      for (int i = 0; i < kAcc; ++i) acc[i] = V(0);
-      for (int r = cur + 1; r < target; ++r) store_row(r, acc);
-      cur = target;
-    };
-#pragma unroll
-    for (int i = 0; i < IPT; ++i) {
-      if (rowk[i] >= 0) {
-        if (rowk[i] != cur) flush_to(rowk[i]);
-        G::map(p, tile, ys + i, nz0 + ys + i, g[i], acc);
       }
     }
-    if (cur < xe) flush_to(xe);
 
     // ---- segmented inclusive scan of the carries (key = row the carry belongs to) -------------------
-    const int key = xe;
+    const int key = row;
     V val[kAcc];
 #pragma unroll
     for (int i = 0; i < kAcc; ++i) val[i] = acc[i];
@@ -316,9 +405,8 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     V pv[kAcc];
 #pragma unroll
     for (int i = 0; i < kAcc; ++i) pv[i] = shfl_up_any(val[i], 1);
-    __syncthreads();   // [B] every thread is done reading this stage
+    named_bar_sync(1, BLOCK);   // [B] warp aggregates visible
 
-    if (tid == 0 && k + S < count) issue(t_begin + k + S, s);
 
     // fold: CTA carry (belongs to local row 0) then the aggregates of the warps before this one
     int fk = 0;
@@ -349,38 +437,32 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         for (int i = 0; i < kAcc; ++i) fv[i] = pv[i];
       }
     }
-    if (had_emit) {   // the first row this thread closed started in earlier threads / tiles
+    if (row > xs) {   // first closed row = what earlier threads / tiles carried + this thread's part
+      static_for<G::kNumReducers>([&](auto R) {
+        constexpr int d = G::template red_dim<R.value>();
+        constexpr int o = G::template red_off<R.value>();
+        V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + xs) * d;
 #pragma unroll
-      for (int i = 0; i < kAcc; ++i) first_val[i] = fv[i] + first_val[i];
-      store_row(xs, first_val);
+        for (int j = 0; j < d; ++j) dst[j] = fv[o + j] + first_val[o + j];
+      });
     }
-    __syncthreads();   // [C]
-
-    // ---- coalesced write of the rows that ended in this tile ----------------------------------------
-    const int rows_staged = nrows < Cfg::kRowsCap ? nrows : Cfg::kRowsCap;
-    static_for<G::kNumReducers>([&](auto R) {
-      constexpr int d = G::template red_dim<R.value>();
-      constexpr int o = G::template red_off<R.value>();
-      V* dst = G::template red_out<R.value>(p) + (size_t)row0 * d;
-      const V* src = s_out + (size_t)o * Cfg::kRowsCap;
-      for (int j = tid; j < rows_staged * d; j += BLOCK) dst[j] = src[j];
-    });
+    // s_wkey / s_wval / s_prod / s_rel are next written after the next tile's first barrier
   }
 
   // ---- hand the CTA's carry to the last CTA ---------------------------------------------------------
-  __syncthreads();
+  named_bar_sync(1, BLOCK);
   if (tid < kAcc) {
     V* cv = static_cast<V*>(a.carry_val) + (size_t)blockIdx.x * kAcc;
     cv[tid] = failed ? V(0) : s_carry[(count & 1) * kAcc + tid];
   }
   if (tid == 0) a.carry_row[blockIdx.x] = (failed || count == 0) ? a.num_rows : last_row1;
   __threadfence();
-  __syncthreads();
+  named_bar_sync(1, BLOCK);
   if (tid == 0) {
     const unsigned t = atomicAdd(&a.header->ticket, 1u);
     s_flag[0] = (t == gridDim.x - 1) ? 1 : 0;
   }
-  __syncthreads();
+  named_bar_sync(1, BLOCK);
   if (s_flag[0]) {
     __threadfence();
     const int n_cta = gridDim.x;
