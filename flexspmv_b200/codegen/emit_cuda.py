@@ -90,7 +90,7 @@ def _override(symbol: str):
     return None
 
 
-def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None) -> str:
+def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, static_scratch_bytes: int = 0) -> str:
     cty, sfx = CTYPE[dtype]
     symbol = symbol or f"{ir.name}_{sfx}"
     block, ipt, stages, min_ctas = config or _override(symbol) or choose_config(ir, dtype)
@@ -355,4 +355,6 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None) 
     w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}>;")
     w("}  // namespace")
     w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg)")
+    if static_scratch_bytes:
+        w(f"FLEXSPMV_DEFINE_STATIC_SCRATCH_LAUNCH({symbol}, Graph, Cfg, {int(static_scratch_bytes)})")
     return "\n".join(L) + "\n"

@@ -116,6 +116,8 @@ const char* flexspmv_error_string(int status) {
     case FLEXSPMV_ERR_BAD_CSR: return "row offsets are not a valid CSR offset array";
     case FLEXSPMV_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case FLEXSPMV_ERR_NOT_PLANNED: return "workspace was not planned for this problem";
+    case FLEXSPMV_ERR_STATIC_SCRATCH:
+      return "problem too large for the built-in static scratch array (FLEXSPMV_STATIC_SCRATCH_BYTES); use the workspace API";
     default: break;
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));

@@ -193,3 +193,50 @@ struct GraphApi {
     return flex::GraphApi<GRAPH, CFG>::device_status(ws, out, static_cast<cudaStream_t>(st));                   \
   }                                                                                                             \
   }
+
+
+// ---- an entry point for callers that cannot allocate device memory -----------------------------------
+// FLEXSPMV_DEFINE_STATIC_SCRATCH_LAUNCH(symbol_suffix, GraphStruct, Cfg, BYTES) expands, inside the
+// translation unit of one graph, to a file-scope device array of BYTES bytes and to
+//   int flexspmv_<suffix>_launch_static(desc, values, indices, row_offsets, outputs, stream)
+// which plans the problem into that array and launches the fused pass, calling no allocator of any kind.
+// The array's name is only a host-side handle for the symbol; its device address is looked up once per
+// device with cudaGetSymbolAddress (with that device current) and cached.
+#define FLEXSPMV_DEFINE_STATIC_SCRATCH_LAUNCH(SYM, GRAPH, CFG, BYTES)                                           \
+  static __device__ __align__(256) unsigned char flexspmv_static_scratch_##SYM[BYTES];                          \
+  namespace {                                                                                                   \
+  struct StaticScratch_##SYM {                                                                                  \
+    std::mutex mu;                                                                                              \
+    void* ptr[64] = {};                                                                                         \
+    int lookup(void** out) {                                                                                    \
+      int dev = -1;                                                                                             \
+      cudaError_t e = cudaGetDevice(&dev);                                                                      \
+      if (e != cudaSuccess) return (int)e;                                                                      \
+      if (dev < 0 || dev >= 64) return FLEXSPMV_ERR_BAD_ARG;                                                    \
+      std::lock_guard<std::mutex> lock(mu);                                                                     \
+      if (!ptr[dev]) {                                                                                          \
+        void* p = nullptr;                                                                                      \
+        e = cudaGetSymbolAddress(&p, flexspmv_static_scratch_##SYM);                                            \
+        if (e != cudaSuccess) return (int)e;                                                                    \
+        ptr[dev] = p;                                                                                           \
+      }                                                                                                         \
+      *out = ptr[dev];                                                                                          \
+      return 0;                                                                                                 \
+    }                                                                                                           \
+  } static_scratch_##SYM;                                                                                       \
+  }                                                                                                             \
+  extern "C" int flexspmv_##SYM##_launch_static(const flexspmv_desc* d, const void* const* v,                   \
+                                                const void* const* ix, const void* ro, void* const* o,          \
+                                                void* st) {                                                     \
+    using Api = flex::GraphApi<GRAPH, CFG>;                                                                     \
+    size_t need = 0;                                                                                            \
+    if (int e = Api::workspace_bytes(d, &need)) return e;                                                       \
+    if (need > (size_t)(BYTES)) return FLEXSPMV_ERR_STATIC_SCRATCH;                                             \
+    void* ws = nullptr;                                                                                         \
+    if (int e = static_scratch_##SYM.lookup(&ws)) return e;                                                     \
+    cudaStream_t stream = static_cast<cudaStream_t>(st);                                                        \
+    /* the array keeps the previous call's contents: planning rewrites the header (ticket, status) and */      \
+    /* every tile coordinate this problem reads; the carry slots are written before they are read      */      \
+    if (int e = Api::plan(d, ro, ws, (size_t)(BYTES), stream)) return e;                                        \
+    return Api::launch(d, v, ix, ro, o, ws, (size_t)(BYTES), stream);                                           \
+  }

@@ -43,7 +43,8 @@ enum {
   FLEXSPMV_ERR_TOO_LARGE = -4,     /* size beyond what the entry point supports                    */
   FLEXSPMV_ERR_BAD_CSR = -5,       /* row offsets not monotone / inconsistent with num_edges       */
   FLEXSPMV_ERR_TIMEOUT = -6,       /* a bounded device-side wait ran out (read via *_device_status)*/
-  FLEXSPMV_ERR_NOT_PLANNED = -7    /* launch called on a workspace that was never planned          */
+  FLEXSPMV_ERR_NOT_PLANNED = -7,   /* launch called on a workspace that was never planned          */
+  FLEXSPMV_ERR_STATIC_SCRATCH = -8 /* problem needs more scratch than the built-in static array     */
 };
 
 /* Problem descriptor shared by the plan / launch calls of every graph. */
@@ -166,6 +167,36 @@ FLEXSPMV_DECLARE_GRAPH(edge_sum_i64)
 FLEXSPMV_DECLARE_GRAPH(edge_copy_f32)
 FLEXSPMV_DECLARE_GRAPH(edge_copy_f64)
 FLEXSPMV_DECLARE_GRAPH(edge_copy_i64)
+
+/*
+ * flexspmv_spmv_f64_launch_static -- the fused fp64 SpMV for callers that must not allocate.
+ *
+ * No counterpart in the reference: its operator allocates temporary storage with cudaMalloc on every
+ * call (cuda_template/merged_binding_template.cu:42-49).  Some hosts of this library cannot do that at
+ * all -- code running inside a region where the CUDA allocator is off limits (a stream-ordered
+ * pipeline whose memory was fixed at start-up, a plug-in that only receives pointers from its host
+ * application, a real-time loop that may not take the allocator's locks).  They pass inputs and
+ * outputs as usual; the scratch the kernels need (tile coordinates, per-CTA carries, a status block)
+ * lives in a device array compiled into the library, FLEXSPMV_STATIC_SCRATCH_BYTES (2 MiB) per GPU
+ * that loads the library, held until the process exits.
+ *
+ *   - Same arguments and results as flexspmv_spmv_f64_plan followed by flexspmv_spmv_f64_launch, minus
+ *     the workspace: every call partitions the problem into the static array (two small kernels) and
+ *     runs the fused pass, all on `stream`.  It calls no cudaMalloc, cudaFree or allocating library
+ *     routine.
+ *   - Problems whose scratch need (flexspmv_spmv_f64_workspace_bytes) exceeds the array are refused
+ *     with FLEXSPMV_ERR_STATIC_SCRATCH; with the default tile size that is about 160 million rows +
+ *     non-zeros with 64-bit offsets, twice that with 32-bit offsets.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's contents; each
+ *     call rewrites what it needs, but two calls whose kernels overlap on the GPU (different streams
+ *     without an ordering between them) race on it.  Order such calls, or use the workspace API.
+ */
+#define FLEXSPMV_STATIC_SCRATCH_BYTES (2u << 20)
+int flexspmv_spmv_f64_launch_static(const flexspmv_desc *desc, const void *const *values,
+                                    const void *const *indices, const void *d_row_offsets,
+                                    void *const *outputs, void *stream);
 
 #ifdef __cplusplus
 }
