@@ -209,24 +209,35 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     w("    (void)p; (void)i; (void)s;")
     w("  }")
 
-    # ---- gather -------------------------------------------------------------------------------------
+    # ---- gather: what depends only on the row (row-identity selectors) and what depends on the edge ----
     gsel = [s for s in ir.selector_register if s.get("selector") == 1]
-    w("  struct Gathered {")
-    for s in gsel:
+    row_sel = [s for s in gsel if s.get("row_identity")]
+    edge_sel = [s for s in gsel if not s.get("row_identity")]
+    w("  struct GRow {")
+    for s in row_sel:
         w(f"    fx::Vec<V, {dim_of(s['shape'])}> {s['name']};")
-    if not gsel:
+    if not row_sel:
         w("    int unused;")
     w("  };")
-    w("  template <class Tile, class IdxT>")
-    w("  __device__ __forceinline__ static void gather(const Params& p, const Tile& t, IdxT le, long long row, Gathered& g) {")
-    for s in gsel:
+    w("  struct GEdge {")
+    for s in edge_sel:
+        w(f"    fx::Vec<V, {dim_of(s['shape'])}> {s['name']};")
+    if not edge_sel:
+        w("    int unused;")
+    w("  };")
+    w("  __device__ __forceinline__ static void gather_row(const Params& p, long long row, GRow& g) {")
+    for s in row_sel:
         d = dim_of(s["shape"])
-        if s.get("row_identity"):
-            w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + row * {d});")
-        else:
-            si = stream_of["idx:" + s["selector_name"]]
-            w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + (long long)(*t.template stream<{si}, int>(le)) * {d});")
-    w("    (void)p; (void)t; (void)le; (void)row; (void)g;")
+        w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + row * {d});")
+    w("    (void)p; (void)row; (void)g;")
+    w("  }")
+    w("  template <class Tile, class IdxT>")
+    w("  __device__ __forceinline__ static void gather_edge(const Params& p, const Tile& t, IdxT le, GEdge& g) {")
+    for s in edge_sel:
+        d = dim_of(s["shape"])
+        si = stream_of["idx:" + s["selector_name"]]
+        w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + (long long)(*t.template stream<{si}, int>(le)) * {d});")
+    w("    (void)p; (void)t; (void)le; (void)g;")
     w("  }")
 
     # ---- map ----------------------------------------------------------------------------------------
@@ -236,7 +247,8 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     for s in ir.selector_register:
         d = dim_of(s["shape"])
         if s.get("selector") == 1:
-            b(f"    const fx::Vec<V, {d}>& {s['name']} = g.{s['name']};")
+            src = "gr" if s.get("row_identity") else "ge"
+            b(f"    const fx::Vec<V, {d}>& {s['name']} = {src}.{s['name']};")
             env[s["name"]] = Var("vec", d, s["name"])
         else:
             si = stream_of[s["target"]]
@@ -347,12 +359,15 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
             b(f"    p.out_{n}[(long long)e] = {v.expr};")
 
     w("  template <class Tile, class IdxT>")
-    w("  __device__ __forceinline__ static void map(const Params& p, const Tile& t, IdxT le, long long e, const Gathered& g, V* acc) {")
+    w("  __device__ __forceinline__ static void map(const Params& p, const Tile& t, IdxT le, long long e, const GRow& gr, const GEdge& ge, V* acc) {")
     L.extend(body)
-    w("    (void)p; (void)t; (void)le; (void)e; (void)g; (void)acc;")
+    w("    (void)p; (void)t; (void)le; (void)e; (void)gr; (void)ge; (void)acc;")
     w("  }")
     w("};")
-    w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}>;")
+    edge_regs = sum(dim_of(s_["shape"]) * VBYTES[dtype] // 4 for s_ in ir.selector_register
+                    if s_.get("selector") == 1 and not s_.get("row_identity"))
+    batch = max(2, min(8, 24 // max(edge_regs, 1)))
+    w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}>;")
     w("}  // namespace")
     w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg)")
     if static_scratch_bytes:

@@ -44,16 +44,17 @@ __global__ void __launch_bounds__(BLOCK) flex_edge_kernel(const typename G::Para
 
   const long long tile_edges = (long long)BLOCK * IPT;
   for (long long base = (long long)blockIdx.x * tile_edges; base < a.num_edges; base += (long long)gridDim.x * tile_edges) {
-    typename G::Gathered g[IPT];
+    typename G::GEdge g[IPT];
+    typename G::GRow gr[IPT];    // a graph without a reducer has no rows: a row-identity selector reads entry e
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       const long long e = base + (long long)i * BLOCK + tid;
-      if (e < a.num_edges) G::gather(p, tile, e, e, g[i]);
+      if (e < a.num_edges) { G::gather_row(p, e, gr[i]); G::gather_edge(p, tile, e, g[i]); }
     }
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       const long long e = base + (long long)i * BLOCK + tid;
-      if (e < a.num_edges) G::map(p, tile, e, e, g[i], agg);
+      if (e < a.num_edges) G::map(p, tile, e, e, gr[i], g[i], agg);
     }
   }
 

@@ -17,7 +17,7 @@
 
 namespace flex {
 
-template <int BLOCK_, int IPT_, int STAGES_, int MIN_CTAS_>
+template <int BLOCK_, int IPT_, int STAGES_, int MIN_CTAS_, int BATCH_ = 8>
 struct TileCfg {
   static constexpr int kBlock = BLOCK_;
   static constexpr int kIpt = IPT_;
@@ -25,6 +25,7 @@ struct TileCfg {
   static constexpr int kMinCtas = MIN_CTAS_;
   static constexpr int kTile = BLOCK_ * IPT_;
   static constexpr int kWarps = BLOCK_ / 32;
+  static constexpr int kBatch = BATCH_;   // edges of one row whose gathers are in flight together (short-row tiles)
 };
 
 constexpr int kMaxCtas = 2048;            // capacity of the per-CTA carry arrays in the workspace
@@ -254,7 +255,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       my_long |= (nz0 + nnz - beg_t) > kShortRowMax;
     }
 
-    // this thread's merge-path span (long-row tiles only): items [d0, d1), starting at (row xs, edge ys)
+    // this thread's merge-path span (used by long-row tiles): items [d0, d1), starting at (row xs, edge ys)
     const int total_items = nrows + nnz;
     const int d0 = min(tid * IPT, total_items);
     const int n_items = min(d0 + IPT, total_items) - d0;
@@ -262,24 +263,53 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     bool long_tile = false;
 
     if constexpr (G::kGatherNeedsRow) {
-      // the map needs the row of every edge
       long_tile = named_bar_or(1, BLOCK, my_long);   // [R] s_rel complete, tile classified
       if (!long_tile) {
-        // short rows: one thread per row (the trailing partial row is local row `nrows`)
+        // ---- short rows, map needs per-row data: one thread per row does gather + map + sum in
+        //      registers (the row's own vertex data is loaded once) and stores the row; local row 0
+        //      continues the CTA's carry, local row `nrows` (partial) becomes the next carry -----------
         for (int r = tid; r <= nrows; r += BLOCK) {
           const int lo = r ? s_rel[r - 1] : 0;
           const int hi = r < nrows ? s_rel[r] : nnz;
-          for (int e = lo; e < hi; ++e) s_rowid[e] = (unsigned short)r;
-        }
-      } else {
-        merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
-        int row = xs, nz = ys, re = s_rel[xs];
+          V sum[kAcc];
 #pragma unroll
-        for (int i = 0; i < IPT; ++i) {
-          if (i < n_items) {
-            if (nz < re) { s_rowid[nz] = (unsigned short)row; ++nz; }
-            else { ++row; re = s_rel[row]; }
+          for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[(k & 1) * kAcc + j] : V(0);
+          typename G::GRow gr;
+          if (lo < hi) G::gather_row(p, row0 + r, gr);
+          for (int e0 = lo; e0 < hi; e0 += Cfg::kBatch) {
+            typename G::GEdge ge[Cfg::kBatch];
+#pragma unroll
+            for (int b = 0; b < Cfg::kBatch; ++b)
+              if (e0 + b < hi) G::gather_edge(p, tile, e0 + b, ge[b]);
+#pragma unroll
+            for (int b = 0; b < Cfg::kBatch; ++b)
+              if (e0 + b < hi) G::map(p, tile, e0 + b, nz0 + e0 + b, gr, ge[b], sum);
           }
+          if (r < nrows) {
+            static_for<G::kNumReducers>([&](auto R) {
+              constexpr int d = G::template red_dim<R.value>();
+              constexpr int o = G::template red_off<R.value>();
+              V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + r) * d;
+#pragma unroll
+              for (int j = 0; j < d; ++j) dst[j] = sum[o + j];
+            });
+          } else {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) s_carry[((k + 1) & 1) * kAcc + j] = sum[j];
+          }
+        }
+        named_bar_sync(1, BLOCK);               // [S] every thread is done reading the staged arrays
+        if (tid == 0) mbar_arrive(&empty[s]);   // the producer may refill this stage
+        continue;
+      }
+      // long rows: each thread walks its merge-path span once and records the row of every edge
+      merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
+      int row = xs, nz = ys, re = s_rel[xs];
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) {
+        if (i < n_items) {
+          if (nz < re) { s_rowid[nz] = (unsigned short)row; ++nz; }
+          else { ++row; re = s_rel[row]; }
         }
       }
       named_bar_sync(1, BLOCK);   // [W] s_rowid complete
@@ -287,14 +317,14 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 
     // ---- phase 1: gather + map of every edge, lanes on consecutive edges; products to shared memory ---
     {
-      typename G::Gathered g[IPT];
+      typename G::GEdge ge[IPT];
+      typename G::GRow gr[G::kGatherNeedsRow ? IPT : 1];
 #pragma unroll
       for (int i = 0; i < IPT; ++i) {
         const int e = i * BLOCK + tid;
         if (e < nnz) {
-          long long row = 0;
-          if constexpr (G::kGatherNeedsRow) row = row0 + s_rowid[e];
-          G::gather(p, tile, e, row, g[i]);
+          if constexpr (G::kGatherNeedsRow) G::gather_row(p, row0 + s_rowid[e], gr[i]);
+          G::gather_edge(p, tile, e, ge[i]);
         }
       }
 #pragma unroll
@@ -304,7 +334,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
           V prod[kAcc];
 #pragma unroll
           for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
-          G::map(p, tile, e, nz0 + e, g[i], prod);
+          G::map(p, tile, e, nz0 + e, gr[G::kGatherNeedsRow ? i : 0], ge[i], prod);
 #pragma unroll
           for (int j = 0; j < kAcc; ++j) s_prod[j * Cfg::kTile + e] = prod[j];
         }
@@ -342,10 +372,10 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       }
       continue;   // the next tile's first barrier orders these reads before anything is overwritten
     }
+    if constexpr (!G::kGatherNeedsRow) merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
 
     // ---- phase 2, long rows: every thread reduces its merge-path span: exactly n_items steps, each
     //      consuming one edge (accumulate) or one row end (store the row, reset) ------------------------
-    if constexpr (!G::kGatherNeedsRow) merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
     V acc[kAcc], first_val[kAcc];
 #pragma unroll
     for (int j = 0; j < kAcc; ++j) { acc[j] = V(0); first_val[j] = V(0); }
