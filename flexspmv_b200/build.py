@@ -28,7 +28,7 @@ NVCC_FLAGS = [
     "-fmad=false",            # one IEEE operation per map operation, as the reference CPU code evaluates it
     "--expt-relaxed-constexpr", "-diag-suppress", "177", "-Xcompiler", "-fPIC", "-Xcompiler", "-O2",
     "-I", CSRC, "-I", os.path.join(ROOT, "include"),
-]
+] + os.environ.get("FLEXSPMV_NVCC_EXTRA", "").split()
 
 
 def _headers_digest() -> str:

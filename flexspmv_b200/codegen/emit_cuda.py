@@ -48,6 +48,24 @@ def _stream_bytes_per_edge(ir: GraphIR, vb: int) -> Tuple[int, int]:
     return total, len(seen)
 
 
+def direct_loads(ir: GraphIR, dtype: str) -> bool:
+    """True when every per-edge record is 4, 8 or 16 bytes wide: a warp then reads 128-512 contiguous
+    bytes per load instruction straight from global memory and staging through shared memory would only
+    add traffic on the L1 data pipe.  Wider records (edge tensors of 3 or 6 values, ...) are staged by bulk
+    copies so that the global side stays one contiguous transfer.  Measured on B200 (config 4, fp64
+    SpMV): without the bulk-copy prefetch the direct path exposes the whole coordinate -> index -> gather
+    latency chain per tile and reaches 44-47% of the HBM peak against 67% staged, so staging is the
+    default for every graph and this path is only built with FLEXSPMV_DIRECT_LOADS=1."""
+    import os
+    if os.environ.get("FLEXSPMV_DIRECT_LOADS") != "1":
+        return False
+    vb = VBYTES[dtype]
+    for s_ in ir.selector_register:
+        if s_.get("selector") != 1 and vb * dim_of(s_["shape"]) not in (4, 8, 16):
+            return False
+    return True
+
+
 def smem_bytes(ir: GraphIR, dtype: str, block: int, ipt: int, stages: int) -> int:
     """Upper bound of the tile kernel's dynamic shared memory (mirrors TileSmemLayout in
     csrc/flex_tile_kernel.cuh for 64-bit row offsets, the larger of the two instantiations)."""
@@ -55,10 +73,12 @@ def smem_bytes(ir: GraphIR, dtype: str, block: int, ipt: int, stages: int) -> in
     per_edge, ns = _stream_bytes_per_edge(ir, vb)
     acc = max(1, sum(dim_of(o["shape"]) for o in ir.outputs if str(o["target"]) == "reducer"))
     tile = block * ipt
-    stage = -(-(tile * max(8, per_edge) + 32 * (ns + 1) + 16) // 128) * 128
+    stage = 0 if direct_loads(ir, dtype) else -(-(tile * max(8, per_edge) + 32 * (ns + 1) + 16) // 128) * 128
     fixed = 8 * stages + (32 + 4 * max(ns, 1) + 16) * stages + 4 * (block + 1) + 4 * (block // 32) \
         + vb * acc * (block // 32) + vb * acc * 2 + 16 + 8 * 16 + 128
-    return fixed + 4 * (tile + 1) + 2 * tile + vb * acc * tile + stages * stage
+    needs_row = any(s_.get("selector") == 1 and s_.get("row_identity") for s_ in ir.selector_register)
+    buffers = 1   # 2 only when the kernel is built with tile pipelining (TileCfg::kPipeline)
+    return fixed + 4 * (tile + 1) * buffers + (2 * tile if needs_row else 0) + vb * acc * tile * buffers + stages * stage
 
 
 def choose_config(ir: GraphIR, dtype: str) -> Tuple[int, int, int, int]:
@@ -144,6 +164,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     w(f"  static constexpr bool kHasReducer = {'true' if has_reducer else 'false'};")
     w(f"  static constexpr int kNumReducers = {len(reducers)}, kAccDim = {max(acc_off, 1)}, kAggDim = {agg_off};")
     w(f"  static constexpr int kNumStreams = {len(streams)};")
+    w(f"  static constexpr bool kDirectLoads = {'true' if direct_loads(ir, dtype) else 'false'};")
     needs_row = any(s.get("selector") == 1 and s.get("row_identity") for s in ir.selector_register)
     w(f"  static constexpr bool kGatherNeedsRow = {'true' if needs_row else 'false'};")
     w("  static constexpr int kStreamBytesPerEdge = 0" + "".join(f" + {b}" for _, _, b in streams) + ";")
@@ -231,13 +252,38 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
         w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + row * {d});")
     w("    (void)p; (void)row; (void)g;")
     w("  }")
+    # per-edge data that comes out of the staged arrays: copied to registers first, so that the stage can
+    # be handed back to the producer before the gathers are even issued
+    edge_regs_list = [s_ for s_ in ir.selector_register if s_.get("selector") != 1]
+    w("  struct EReg {")
+    for s_ in edge_sel:
+        w(f"    int idx_{s_['name']};")
+    seen_e = set()
+    for s_ in edge_regs_list:
+        if s_["selector_name"] not in seen_e:
+            seen_e.add(s_["selector_name"])
+            w(f"    fx::Vec<V, {dim_of(s_['shape'])}> {s_['selector_name']};")
+    if not edge_sel and not edge_regs_list:
+        w("    int unused;")
+    w("  };")
     w("  template <class Tile, class IdxT>")
-    w("  __device__ __forceinline__ static void gather_edge(const Params& p, const Tile& t, IdxT le, GEdge& g) {")
-    for s in edge_sel:
-        d = dim_of(s["shape"])
-        si = stream_of["idx:" + s["selector_name"]]
-        w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + (long long)(*t.template stream<{si}, int>(le)) * {d});")
-    w("    (void)p; (void)t; (void)le; (void)g;")
+    w("  __device__ __forceinline__ static void load_edge(const Tile& t, IdxT le, EReg& r) {")
+    for s_ in edge_sel:
+        si = stream_of["idx:" + s_["selector_name"]]
+        w(f"    r.idx_{s_['name']} = *t.template stream<{si}, int>(le);")
+    seen_e = set()
+    for s_ in edge_regs_list:
+        if s_["selector_name"] not in seen_e:
+            seen_e.add(s_["selector_name"])
+            si = stream_of[s_["target"]]
+            w(f"    r.{s_['selector_name']} = fx::ld_vec<V, {dim_of(s_['shape'])}>(t.template stream<{si}, V>(le));")
+    w("    (void)t; (void)le; (void)r;")
+    w("  }")
+    w("  __device__ __forceinline__ static void gather_edge(const Params& p, const EReg& r, GEdge& g) {")
+    for s_ in edge_sel:
+        d = dim_of(s_["shape"])
+        w(f"    g.{s_['name']} = fx::ldg_vec<V, {d}>(p.{s_['target']} + (long long)r.idx_{s_['name']} * {d});")
+    w("    (void)p; (void)r; (void)g;")
     w("  }")
 
     # ---- map ----------------------------------------------------------------------------------------
@@ -251,8 +297,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
             b(f"    const fx::Vec<V, {d}>& {s['name']} = {src}.{s['name']};")
             env[s["name"]] = Var("vec", d, s["name"])
         else:
-            si = stream_of[s["target"]]
-            b(f"    fx::Vec<V, {d}> {s['selector_name']} = fx::ld_vec<V, {d}>(t.template stream<{si}, V>(le));")
+            b(f"    fx::Vec<V, {d}> {s['selector_name']} = r.{s['selector_name']};")
             env[s["selector_name"]] = Var("vec", d, s["selector_name"])
 
     def operand(a):
@@ -358,10 +403,9 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
         else:
             b(f"    p.out_{n}[(long long)e] = {v.expr};")
 
-    w("  template <class Tile, class IdxT>")
-    w("  __device__ __forceinline__ static void map(const Params& p, const Tile& t, IdxT le, long long e, const GRow& gr, const GEdge& ge, V* acc) {")
+    w("  __device__ __forceinline__ static void map(const Params& p, const EReg& r, long long e, const GRow& gr, const GEdge& ge, V* acc) {")
     L.extend(body)
-    w("    (void)p; (void)t; (void)le; (void)e; (void)gr; (void)ge; (void)acc;")
+    w("    (void)p; (void)r; (void)e; (void)gr; (void)ge; (void)acc;")
     w("  }")
     w("};")
     edge_regs = sum(dim_of(s_["shape"]) * VBYTES[dtype] // 4 for s_ in ir.selector_register

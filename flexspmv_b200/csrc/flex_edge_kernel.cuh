@@ -44,17 +44,18 @@ __global__ void __launch_bounds__(BLOCK) flex_edge_kernel(const typename G::Para
 
   const long long tile_edges = (long long)BLOCK * IPT;
   for (long long base = (long long)blockIdx.x * tile_edges; base < a.num_edges; base += (long long)gridDim.x * tile_edges) {
+    typename G::EReg er[IPT];
     typename G::GEdge g[IPT];
     typename G::GRow gr[IPT];    // a graph without a reducer has no rows: a row-identity selector reads entry e
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       const long long e = base + (long long)i * BLOCK + tid;
-      if (e < a.num_edges) { G::gather_row(p, e, gr[i]); G::gather_edge(p, tile, e, g[i]); }
+      if (e < a.num_edges) { G::load_edge(tile, e, er[i]); G::gather_row(p, e, gr[i]); G::gather_edge(p, er[i], g[i]); }
     }
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       const long long e = base + (long long)i * BLOCK + tid;
-      if (e < a.num_edges) G::map(p, tile, e, e, gr[i], g[i], agg);
+      if (e < a.num_edges) G::map(p, er[i], e, gr[i], g[i], agg);
     }
   }
 

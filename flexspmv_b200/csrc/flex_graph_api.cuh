@@ -107,13 +107,14 @@ struct GraphApi {
     using L = TileSmemLayout<G, OffsetT, Cfg>;
     static_assert(L::kTotal <= 227 * 1024, "tile kernel needs more shared memory than one sm_100a CTA can have");
     auto kernel = flex_tile_kernel<G, OffsetT, Cfg>;
+    constexpr int kThreads = Cfg::kBlock + (G::kDirectLoads ? 0 : 32);   // staged mode adds the producer warp
     static int resident = 0;
     static std::once_flag once;
     static cudaError_t init_err = cudaSuccess;
     std::call_once(once, [&] {
       init_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
       if (init_err == cudaSuccess)
-        init_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, Cfg::kBlock + 32, L::kTotal);
+        init_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kThreads, L::kTotal);
     });
     if (init_err != cudaSuccess) { (void)cudaGetLastError(); return (int)init_err; }
     if (resident < 1) return FLEXSPMV_ERR_TOO_LARGE;
@@ -128,7 +129,7 @@ struct GraphApi {
     a.carry_row = reinterpret_cast<long long*>(static_cast<char*>(ws) + h.carry_row_offset);
     a.carry_val = static_cast<char*>(ws) + h.carry_val_offset;
     a.num_rows = d->num_rows; a.num_edges = d->num_edges; a.num_tiles = tiles;
-    kernel<<<(unsigned)grid, Cfg::kBlock + 32, L::kTotal, st>>>(p, a);   // + the producer warp
+    kernel<<<(unsigned)grid, kThreads, L::kTotal, st>>>(p, a);
     return (int)cudaGetLastError();
   }
 

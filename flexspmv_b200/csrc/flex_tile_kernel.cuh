@@ -14,11 +14,16 @@
 #pragma once
 #include "flex_common.cuh"
 #include "flex_tensor.cuh"
+#include <type_traits>
 
 namespace flex {
 
-template <int BLOCK_, int IPT_, int STAGES_, int MIN_CTAS_, int BATCH_ = 8>
+template <int BLOCK_, int IPT_, int STAGES_, int MIN_CTAS_, int BATCH_ = 8, bool PIPELINE_ = false>
 struct TileCfg {
+  // software pipelining across tiles (gathers of tile k in flight while tile k-1 is reduced); measured
+  // slower than the plain loop on B200 (58% against 68% of the HBM peak on the 7-point fp64 SpMV: one
+  // CTA less per SM for the second s_prod / s_rel buffer), so it is off by default
+  static constexpr bool kPipeline = PIPELINE_;
   static constexpr int kBlock = BLOCK_;
   static constexpr int kIpt = IPT_;
   static constexpr int kStages = STAGES_;
@@ -35,9 +40,25 @@ constexpr uint64_t kWaitPolls = 1000000000ull;  // bound on every mbarrier wait:
 template <class G>
 struct SmemTile {
   const char* base[G::kNumStreams > 0 ? G::kNumStreams : 1];
+  __device__ __forceinline__ void advance(int records) {
+    static_for<G::kNumStreams>([&](auto I) { base[I.value] += (size_t)records * G::template stream_bytes<I.value>(); });
+  }
   template <int I, class T>
   __device__ __forceinline__ const T* stream(int le) const {
     return reinterpret_cast<const T*>(base[I] + (size_t)le * G::template stream_bytes<I>());
+  }
+};
+
+// Direct mode: the per-edge arrays are read straight from global memory with coalesced loads (lanes on
+// consecutive edges); `le` is relative to the tile's first edge.
+template <class G>
+struct DirectTile {
+  const typename G::Params* p;
+  long long nz0;
+  __device__ __forceinline__ void advance(int records) { nz0 += records; }
+  template <int I, class T>
+  __device__ __forceinline__ const T* stream(int le) const {
+    return reinterpret_cast<const T*>(G::template stream_ptr<I>(*p) + (size_t)(nz0 + le) * G::template stream_bytes<I>());
   }
 };
 
@@ -48,7 +69,8 @@ struct TileSmemLayout {
   static constexpr int kBytesPerEdge = G::kStreamBytesPerEdge;
   static constexpr int kPerItem = (int(sizeof(OffsetT)) > kBytesPerEdge) ? int(sizeof(OffsetT)) : kBytesPerEdge;
   // each staged window may grow by < 32 bytes from aligning both ends to 16
-  static constexpr int kStageBytes = int(align_up(uint64_t(Cfg::kTile) * kPerItem + 32u * (G::kNumStreams + 1) + 16, 128));
+  static constexpr int kStageBytes =
+      G::kDirectLoads ? 0 : int(align_up(uint64_t(Cfg::kTile) * kPerItem + 32u * (G::kNumStreams + 1) + 16, 128));
   struct Ctl {
     long long row0, nz0;
     int nrows, nnz;
@@ -63,9 +85,10 @@ struct TileSmemLayout {
   static constexpr int kOffCarry = int(align_up(kOffWVal + sizeof(V) * kAcc * Cfg::kWarps, 16));
   static constexpr int kOffFlag = int(align_up(kOffCarry + sizeof(V) * kAcc * 2, 16));
   static constexpr int kOffRel = int(align_up(kOffFlag + 16, 16));
-  static constexpr int kOffRowId = int(align_up(kOffRel + 4 * (Cfg::kTile + 1), 16));
+  static constexpr int kBuffers = (!G::kGatherNeedsRow && Cfg::kPipeline) ? 2 : 1;   // s_rel / s_prod double-buffered when tiles are pipelined
+  static constexpr int kOffRowId = int(align_up(kOffRel + 4 * (Cfg::kTile + 1) * kBuffers, 16));
   static constexpr int kOffProd = int(align_up(kOffRowId + (G::kGatherNeedsRow ? 2 * Cfg::kTile : 0), 16));
-  static constexpr int kOffStages = int(align_up(kOffProd + sizeof(V) * kAcc * Cfg::kTile, 128));
+  static constexpr int kOffStages = int(align_up(kOffProd + sizeof(V) * kAcc * Cfg::kTile * kBuffers, 128));
   static constexpr int kTotal = kOffStages + kStageBytes * Cfg::kStages;
 };
 
@@ -112,7 +135,7 @@ __device__ __forceinline__ Window make_window(const void* gbase, uint32_t eb, lo
 }
 
 template <class G, typename OffsetT, class Cfg>
-__global__ void __launch_bounds__(Cfg::kBlock + 32, Cfg::kMinCtas)
+__global__ void __launch_bounds__(Cfg::kBlock + (G::kDirectLoads ? 0 : 32), Cfg::kMinCtas)
 flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   using V = typename G::V;
   using L = TileSmemLayout<G, OffsetT, Cfg>;
@@ -120,6 +143,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   constexpr int kAcc = G::kAccDim;
   constexpr int NS = G::kNumStreams;
   constexpr int BLOCK = Cfg::kBlock, IPT = Cfg::kIpt, S = Cfg::kStages;
+  constexpr bool DIRECT = G::kDirectLoads;   // narrow per-edge records: coalesced loads, no staging, no producer warp
 
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);    // "full": a stage's copies have landed
@@ -152,61 +176,76 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   const int count = (int)(q + ((long long)blockIdx.x < rem ? 1 : 0));
 
   // ---- producer: stage one tile (lane 0 of the producer warp) ---------------------------------------
-  auto issue = [&](long long tile, int s) {
-    const long long row0 = (long long)coords[2 * tile], nz0 = (long long)coords[2 * tile + 1];
-    const long long row1 = (long long)coords[2 * tile + 2], nz1 = (long long)coords[2 * tile + 3];
-    Ctl& c = ctls[s];
-    c.row0 = row0; c.nz0 = nz0; c.nrows = (int)(row1 - row0); c.nnz = (int)(nz1 - nz0);
+  // Executed by the whole producer warp: lane i prepares window i (lane 0: row-end offsets, lane 1+I:
+  // stream I), a shuffle prefix sum places the windows in the stage, lane 0 posts the byte count, then
+  // every lane issues its own bulk copy.
+  auto issue = [&](long long row0, long long nz0, long long row1, long long nz1, int s) {
     unsigned char* dst = s_stage + (size_t)s * L::kStageBytes;
-    Window w[NS + 1];
-    w[0] = make_window(row_offsets, sizeof(OffsetT), row0 + 1, row1 - row0, a.num_rows + 1);
+    Window w;
+    w.src = nullptr; w.bulk_bytes = 0; w.lead = 0; w.span = 0; w.tail_src = nullptr; w.tail_bytes = 0;
+    if (lane == 0) w = make_window(row_offsets, sizeof(OffsetT), row0 + 1, row1 - row0, a.num_rows + 1);
     static_for<NS>([&](auto I) {
-      w[I.value + 1] = make_window(G::template stream_ptr<I.value>(p), G::template stream_bytes<I.value>(), nz0,
-                                   nz1 - nz0, a.num_edges);
+      if (lane == I.value + 1)
+        w = make_window(G::template stream_ptr<I.value>(p), G::template stream_bytes<I.value>(), nz0, nz1 - nz0, a.num_edges);
     });
-    uint32_t off[NS + 1], total = 0, cur = 0;
+    uint32_t off = w.span;   // exclusive prefix sum of the spans over lanes 0..NS
 #pragma unroll
-    for (int i = 0; i <= NS; ++i) { off[i] = cur; cur += w[i].span; total += w[i].bulk_bytes; }
-    c.roff_off = off[0] + w[0].lead;
-    static_for<NS>([&](auto I) { c.stream_off[I.value] = off[I.value + 1] + w[I.value + 1].lead; });
+    for (int d = 1; d <= NS; d <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, off, d);
+      if (lane >= d) off += t;
+    }
+    off -= w.span;
+    uint32_t total = w.bulk_bytes;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+    Ctl& c = ctls[s];
+    if (lane == 0) { c.row0 = row0; c.nz0 = nz0; c.nrows = (int)(row1 - row0); c.nnz = (int)(nz1 - nz0); c.roff_off = off + w.lead; }
+    static_for<NS>([&](auto I) { if (lane == I.value + 1) c.stream_off[I.value] = off + w.lead; });
     // the ragged tail (last < 16 bytes of an array) is fetched with plain loads BEFORE the arrive below,
-    // whose release makes it (and the control block) visible to every consumer that acquires the phase
-#pragma unroll
-    for (int i = 0; i <= NS; ++i) {
-      if (w[i].tail_bytes) {
-        const uint32_t so = off[i] + (uint32_t)(w[i].tail_src - w[i].src);
-        for (uint32_t b = 0; b < w[i].tail_bytes; b += 4)
-          *reinterpret_cast<uint32_t*>(dst + so + b) = *reinterpret_cast<const uint32_t*>(w[i].tail_src + b);
-      }
+    // whose release (after the warp barrier) makes it and the control block visible to the consumers
+    if (w.tail_bytes) {
+      const uint32_t so = off + (uint32_t)(w.tail_src - w.src);
+      for (uint32_t b = 0; b < w.tail_bytes; b += 4)
+        *reinterpret_cast<uint32_t*>(dst + so + b) = *reinterpret_cast<const uint32_t*>(w.tail_src + b);
     }
     fence_proxy_async_smem();   // earlier generic accesses to this stage are ordered before the bulk copies
-    mbar_expect_tx(&bars[s], total);
-#pragma unroll
-    for (int i = 0; i <= NS; ++i) {
-      if (w[i].bulk_bytes) bulk_g2s(dst + off[i], w[i].src, w[i].bulk_bytes, &bars[s]);
-    }
+    __syncwarp();
+    if (lane == 0) mbar_expect_tx(&bars[s], total);
+    __syncwarp();
+    if (w.bulk_bytes) bulk_g2s(dst + off, w.src, w.bulk_bytes, &bars[s]);
   };
 
-  if (tid == 0) {
+  if constexpr (!DIRECT) {
+    if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < S; ++s) { mbar_init(&bars[s], 1); mbar_init(&empty[s], 1); }
-    mbar_fence_init();
+      for (int s = 0; s < S; ++s) { mbar_init(&bars[s], 1); mbar_init(&empty[s], Cfg::kWarps); }   // empty: one arrive per consumer warp
+      mbar_fence_init();
+    }
   }
   if (tid < 2 * kAcc) s_carry[tid] = V(0);
   __syncthreads();   // the only barrier that includes the producer warp
 
   // ---- producer warp: runs up to S tiles ahead of the consumers, off their critical path -----------
-  if (warp == Cfg::kWarps) {
-    if (lane == 0) {
+  if (!DIRECT && warp == Cfg::kWarps) {
+    {
       int issued = 0;
       bool pfail = false;
+      // coordinates are read one tile ahead, so their load latency overlaps the wait for a free stage
+      long long c_row = count ? (long long)coords[2 * t_begin] : 0, c_nz = count ? (long long)coords[2 * t_begin + 1] : 0;
+      long long n_row = count ? (long long)coords[2 * t_begin + 2] : 0, n_nz = count ? (long long)coords[2 * t_begin + 3] : 0;
       for (int k = 0; k < count; ++k) {
         const int s = k % S;
-        if (k >= S && !mbar_wait_bounded(&empty[s], (uint32_t)(k / S - 1) & 1u, kWaitPolls)) { pfail = true; break; }
-        issue(t_begin + k, s);
+        long long nn_row = 0, nn_nz = 0;
+        if (k + 1 < count) { nn_row = (long long)coords[2 * (t_begin + k + 2)]; nn_nz = (long long)coords[2 * (t_begin + k + 2) + 1]; }
+        if (k >= S) {
+          const bool ok = mbar_wait_bounded(&empty[s], (uint32_t)(k / S - 1) & 1u, kWaitPolls);
+          if (!__all_sync(0xffffffffu, ok)) { pfail = true; break; }
+        }
+        issue(c_row, c_nz, n_row, n_nz, s);
+        c_row = n_row; c_nz = n_nz; n_row = nn_row; n_nz = nn_nz;
         issued = k + 1;
       }
-      if (pfail) {   // the consumers never released a stage: flag it, let copies in flight land, leave
+      if (pfail && lane == 0) {   // the consumers never released a stage: flag it, let copies in flight land, leave
         atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
         a.header->debug[4] = (uint32_t)issued; a.header->debug[5] = blockIdx.x;
         for (int j = issued > S ? issued - S : 0; j < issued; ++j)
@@ -217,177 +256,171 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   }
 
   // ---- consumers (threads 0 .. BLOCK-1); their barriers are the named barrier 1 ---------------------
+  using TileT = std::conditional_t<DIRECT, DirectTile<G>, SmemTile<G>>;
+  struct TileRef { long long row0, nz0; int nrows, nnz; };
   bool failed = false;
   long long last_row1 = 0;
-  for (int k = 0; k < count; ++k) {
-    const int s = k % S;
-    const uint32_t parity = (uint32_t)(k / S) & 1u;
-    const bool ok = named_bar_and(1, BLOCK, mbar_wait_bounded(&bars[s], parity, kWaitPolls));
-    if (!ok) {
-      if (tid == 0) {
-        atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
-        a.header->debug[0] = (uint32_t)(t_begin + k); a.header->debug[1] = (uint32_t)s; a.header->debug[2] = blockIdx.x;
-      }
-      failed = true;
-      break;
-    }
-    const Ctl& c = ctls[s];
-    const long long row0 = c.row0, nz0 = c.nz0;
-    const int nrows = c.nrows, nnz = c.nnz;
-    const unsigned char* stage = s_stage + (size_t)s * L::kStageBytes;
-    const OffsetT* s_rend = reinterpret_cast<const OffsetT*>(stage + c.roff_off);
-    SmemTile<G> tile;
-    static_for<NS>([&](auto I) { tile.base[I.value] = reinterpret_cast<const char*>(stage + c.stream_off[I.value]); });
-    last_row1 = row0 + nrows;
 
-    // row ends as 32-bit edge indices relative to the tile, with a sentinel behind the last row; on the
-    // way, find out whether any row (or the trailing partial row) of the tile is long
+  // direct mode: tile coordinates are read one tile ahead into registers
+  long long d_row = 0, d_nz = 0, d_row1 = 0, d_nz1 = 0;
+  if constexpr (DIRECT) {
+    if (count) {
+      d_row = (long long)coords[2 * t_begin]; d_nz = (long long)coords[2 * t_begin + 1];
+      d_row1 = (long long)coords[2 * t_begin + 2]; d_nz1 = (long long)coords[2 * t_begin + 3];
+    }
+  }
+
+  // Makes tile k available: waits (bounded) for its stage, or takes its coordinates in direct mode.
+  auto acquire = [&](int k, TileRef& t, TileT& tile, const OffsetT*& rend) -> bool {
+    if constexpr (DIRECT) {
+      t.row0 = d_row; t.nz0 = d_nz; t.nrows = (int)(d_row1 - d_row); t.nnz = (int)(d_nz1 - d_nz);
+      d_row = d_row1; d_nz = d_nz1;
+      if (k + 1 < count) { d_row1 = (long long)coords[2 * (t_begin + k + 2)]; d_nz1 = (long long)coords[2 * (t_begin + k + 2) + 1]; }
+      tile.p = &p; tile.nz0 = t.nz0;
+      rend = row_offsets + t.row0 + 1;
+      named_bar_sync(1, BLOCK);   // the previous tile's readers of the shared arrays are done
+      return true;
+    } else {
+      const int s = k % S;
+      const bool ok = named_bar_and(1, BLOCK, mbar_wait_bounded(&bars[s], (uint32_t)(k / S) & 1u, kWaitPolls));
+      if (!ok) {
+        if (tid == 0) {
+          atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
+          a.header->debug[0] = (uint32_t)(t_begin + k); a.header->debug[1] = (uint32_t)s; a.header->debug[2] = blockIdx.x;
+        }
+        return false;
+      }
+      const Ctl& c = ctls[s];
+      t.row0 = c.row0; t.nz0 = c.nz0; t.nrows = c.nrows; t.nnz = c.nnz;
+      const unsigned char* stage = s_stage + (size_t)s * L::kStageBytes;
+      rend = reinterpret_cast<const OffsetT*>(stage + c.roff_off);
+      static_for<NS>([&](auto I) { tile.base[I.value] = reinterpret_cast<const char*>(stage + c.stream_off[I.value]); });
+      return true;
+    }
+  };
+  // This warp needs nothing more from stage s: the producer refills it once every warp has said so.
+  auto release = [&](int k) {
+    if constexpr (!DIRECT) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[k % S]);
+    }
+  };
+  // Row ends as 32-bit edge indices relative to the tile, with a sentinel behind the last row.  Returns
+  // whether this thread saw a long row (or a long trailing partial row).
+  auto convert = [&](const TileRef& t, const OffsetT* rend, int* srel) -> bool {
     bool my_long = false;
-    for (int r = tid; r < nrows; r += BLOCK) {
-      const long long end_r = (long long)s_rend[r];
-      const long long beg_r = r ? (long long)s_rend[r - 1] : nz0;
-      s_rel[r] = (int)(end_r - nz0);
+    for (int r = tid; r < t.nrows; r += BLOCK) {
+      const long long end_r = (long long)rend[r];
+      const long long beg_r = r ? (long long)rend[r - 1] : t.nz0;
+      srel[r] = (int)(end_r - t.nz0);
       my_long |= (end_r - beg_r) > kShortRowMax;
     }
     if (tid == 0) {
-      s_rel[nrows] = 0x7fffffff;
-      const long long beg_t = nrows ? (long long)s_rend[nrows - 1] : nz0;
-      my_long |= (nz0 + nnz - beg_t) > kShortRowMax;
+      srel[t.nrows] = 0x7fffffff;
+      const long long beg_t = t.nrows ? (long long)rend[t.nrows - 1] : t.nz0;
+      my_long |= (t.nz0 + t.nnz - beg_t) > kShortRowMax;
     }
+    return my_long;
+  };
+  auto store_row = [&](long long row, const V* v) {
+    static_for<G::kNumReducers>([&](auto R) {
+      constexpr int d = G::template red_dim<R.value>();
+      constexpr int o = G::template red_off<R.value>();
+      V* dst = G::template red_out<R.value>(p) + (size_t)row * d;
+#pragma unroll
+      for (int j = 0; j < d; ++j) dst[j] = v[o + j];
+    });
+  };
 
-    // this thread's merge-path span (used by long-row tiles): items [d0, d1), starting at (row xs, edge ys)
-    const int total_items = nrows + nnz;
-    const int d0 = min(tid * IPT, total_items);
-    const int n_items = min(d0 + IPT, total_items) - d0;
-    int xs = 0, ys = 0;
-    bool long_tile = false;
-
-    if constexpr (G::kGatherNeedsRow) {
-      long_tile = named_bar_or(1, BLOCK, my_long);   // [R] s_rel complete, tile classified
-      if (!long_tile) {
-        // ---- short rows, map needs per-row data: one thread per row does gather + map + sum in
-        //      registers (the row's own vertex data is loaded once) and stores the row; local row 0
-        //      continues the CTA's carry, local row `nrows` (partial) becomes the next carry -----------
-        for (int r = tid; r <= nrows; r += BLOCK) {
-          const int lo = r ? s_rel[r - 1] : 0;
-          const int hi = r < nrows ? s_rel[r] : nnz;
-          V sum[kAcc];
+  // ---- phase 1 pieces: lanes on consecutive edges ------------------------------------------------------
+  auto map_load = [&](const TileRef& t, const TileT& tile, typename G::EReg (&er)[IPT]) {
+    auto ttile = tile;
+    ttile.advance(tid);   // element `tid` at offset 0: the unrolled accesses are base + constant
 #pragma unroll
-          for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[(k & 1) * kAcc + j] : V(0);
-          typename G::GRow gr;
-          if (lo < hi) G::gather_row(p, row0 + r, gr);
-          for (int e0 = lo; e0 < hi; e0 += Cfg::kBatch) {
-            typename G::GEdge ge[Cfg::kBatch];
+    for (int i = 0; i < IPT; ++i)
+      if (i * BLOCK + tid < t.nnz) G::load_edge(ttile, i * BLOCK, er[i]);
+  };
+  auto map_gather = [&](const TileRef& t, const typename G::EReg (&er)[IPT], typename G::GEdge (&ge)[IPT],
+                        typename G::GRow (&gr)[G::kGatherNeedsRow ? IPT : 1]) {
 #pragma unroll
-            for (int b = 0; b < Cfg::kBatch; ++b)
-              if (e0 + b < hi) G::gather_edge(p, tile, e0 + b, ge[b]);
-#pragma unroll
-            for (int b = 0; b < Cfg::kBatch; ++b)
-              if (e0 + b < hi) G::map(p, tile, e0 + b, nz0 + e0 + b, gr, ge[b], sum);
-          }
-          if (r < nrows) {
-            static_for<G::kNumReducers>([&](auto R) {
-              constexpr int d = G::template red_dim<R.value>();
-              constexpr int o = G::template red_off<R.value>();
-              V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + r) * d;
-#pragma unroll
-              for (int j = 0; j < d; ++j) dst[j] = sum[o + j];
-            });
-          } else {
-#pragma unroll
-            for (int j = 0; j < kAcc; ++j) s_carry[((k + 1) & 1) * kAcc + j] = sum[j];
-          }
-        }
-        named_bar_sync(1, BLOCK);               // [S] every thread is done reading the staged arrays
-        if (tid == 0) mbar_arrive(&empty[s]);   // the producer may refill this stage
-        continue;
-      }
-      // long rows: each thread walks its merge-path span once and records the row of every edge
-      merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
-      int row = xs, nz = ys, re = s_rel[xs];
-#pragma unroll
-      for (int i = 0; i < IPT; ++i) {
-        if (i < n_items) {
-          if (nz < re) { s_rowid[nz] = (unsigned short)row; ++nz; }
-          else { ++row; re = s_rel[row]; }
-        }
-      }
-      named_bar_sync(1, BLOCK);   // [W] s_rowid complete
-    }
-
-    // ---- phase 1: gather + map of every edge, lanes on consecutive edges; products to shared memory ---
-    {
-      typename G::GEdge ge[IPT];
-      typename G::GRow gr[G::kGatherNeedsRow ? IPT : 1];
-#pragma unroll
-      for (int i = 0; i < IPT; ++i) {
-        const int e = i * BLOCK + tid;
-        if (e < nnz) {
-          if constexpr (G::kGatherNeedsRow) G::gather_row(p, row0 + s_rowid[e], gr[i]);
-          G::gather_edge(p, tile, e, ge[i]);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < IPT; ++i) {
-        const int e = i * BLOCK + tid;
-        if (e < nnz) {
-          V prod[kAcc];
-#pragma unroll
-          for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
-          G::map(p, tile, e, nz0 + e, gr[G::kGatherNeedsRow ? i : 0], ge[i], prod);
-#pragma unroll
-          for (int j = 0; j < kAcc; ++j) s_prod[j * Cfg::kTile + e] = prod[j];
-        }
+    for (int i = 0; i < IPT; ++i) {
+      if (i * BLOCK + tid < t.nnz) {
+        if constexpr (G::kGatherNeedsRow) G::gather_row(p, t.row0 + s_rowid[i * BLOCK + tid], gr[i]);
+#ifndef FLEX_EXP_SKIP_GATHER
+        G::gather_edge(p, er[i], ge[i]);
+#else
+        memset(&ge[i], 0, sizeof(ge[i]));
+#endif
       }
     }
-    if constexpr (G::kGatherNeedsRow) named_bar_sync(1, BLOCK);        // [P] products complete
-    else long_tile = named_bar_or(1, BLOCK, my_long);                   // [P] + s_rel complete, tile classified
-    if (tid == 0) mbar_arrive(&empty[s]);   // the staged arrays are dead: the producer may refill this stage
+  };
+  auto map_products = [&](const TileRef& t, const typename G::EReg (&er)[IPT], const typename G::GEdge (&ge)[IPT],
+                          const typename G::GRow (&gr)[G::kGatherNeedsRow ? IPT : 1], V* sprod) {
+    V* tprod = sprod + tid;
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (i * BLOCK + tid < t.nnz) {
+        V prod[kAcc];
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
+        G::map(p, er[i], t.nz0 + (i * BLOCK + tid), gr[G::kGatherNeedsRow ? i : 0], ge[i], prod);
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) tprod[j * Cfg::kTile + i * BLOCK] = prod[j];
+      }
+    }
+  };
 
-    if (!long_tile) {
-      // ---- phase 2, short rows: one thread per row sums its products and stores the row (coalesced);
-      //      local row 0 continues the CTA's carry, local row `nrows` (partial) becomes the next carry ----
-      for (int r = tid; r <= nrows; r += BLOCK) {
-        const int lo = r ? s_rel[r - 1] : 0;
-        const int hi = r < nrows ? s_rel[r] : nnz;
-        V sum[kAcc];
+  // ---- phase 2, short rows: one thread per row sums its products left to right and stores the row
+  //      (coalesced); local row 0 continues the CTA's carry (buffer kpar), the trailing partial row
+  //      (local row `nrows`) becomes the next carry ---------------------------------------------------------
+  auto reduce_short = [&](const TileRef& t, int kpar, const V* sprod, const int* srel) {
+#ifdef FLEX_EXP_SKIP_REDUCE
+    return;
+#endif
+    for (int r = tid; r <= t.nrows; r += BLOCK) {
+      const int lo = r ? srel[r - 1] : 0;
+      const int hi = r < t.nrows ? srel[r] : t.nnz;
+      V sum[kAcc];
 #pragma unroll
-        for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[(k & 1) * kAcc + j] : V(0);
-        for (int e = lo; e < hi; ++e) {
+      for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[kpar * kAcc + j] : V(0);
+      const V* q = sprod + lo;
+      int n = hi - lo;
+      for (; n >= 4; n -= 4, q += 4) {
 #pragma unroll
-          for (int j = 0; j < kAcc; ++j) sum[j] += s_prod[j * Cfg::kTile + e];
-        }
-        if (r < nrows) {
-          static_for<G::kNumReducers>([&](auto R) {
-            constexpr int d = G::template red_dim<R.value>();
-            constexpr int o = G::template red_off<R.value>();
-            V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + r) * d;
+        for (int u = 0; u < 4; ++u) {
 #pragma unroll
-            for (int j = 0; j < d; ++j) dst[j] = sum[o + j];
-          });
-        } else {
-#pragma unroll
-          for (int j = 0; j < kAcc; ++j) s_carry[((k + 1) & 1) * kAcc + j] = sum[j];
+          for (int j = 0; j < kAcc; ++j) sum[j] += q[j * Cfg::kTile + u];
         }
       }
-      continue;   // the next tile's first barrier orders these reads before anything is overwritten
+      for (; n > 0; --n, ++q) {
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) sum[j] += q[j * Cfg::kTile];
+      }
+      if (r < t.nrows) {
+        store_row(t.row0 + r, sum);
+      } else {
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) s_carry[(kpar ^ 1) * kAcc + j] = sum[j];
+      }
     }
-    if constexpr (!G::kGatherNeedsRow) merge_path_search<int, int>(d0, s_rel, 0, nrows, nnz, xs, ys);
+  };
 
-    // ---- phase 2, long rows: every thread reduces its merge-path span: exactly n_items steps, each
-    //      consuming one edge (accumulate) or one row end (store the row, reset) ------------------------
+  // ---- phase 2, long rows: every thread reduces its merge-path span: exactly n_items steps, each
+  //      consuming one edge (accumulate) or one row end (store the row, reset); the carries are combined
+  //      by a warp-shuffle segmented scan and a cross-warp fold (one barrier inside) -------------------
+  auto reduce_long = [&](const TileRef& t, int kpar, const V* sprod, const int* srel, int xs, int ys, int n_items) {
     V acc[kAcc], first_val[kAcc];
 #pragma unroll
     for (int j = 0; j < kAcc; ++j) { acc[j] = V(0); first_val[j] = V(0); }
     int row = xs;
     {
-      int nz = ys, re = s_rel[xs];
+      int nz = ys, re = srel[xs];
 #pragma unroll
       for (int i = 0; i < IPT; ++i) {
         if (i < n_items) {
           if (nz < re) {
 #pragma unroll
-            for (int j = 0; j < kAcc; ++j) acc[j] += s_prod[j * Cfg::kTile + nz];
+            for (int j = 0; j < kAcc; ++j) acc[j] += sprod[j * Cfg::kTile + nz];
             ++nz;
           } else {
             // the first row a thread closes may have begun in earlier threads: keep it for after the scan
@@ -395,24 +428,17 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 #pragma unroll
               for (int j = 0; j < kAcc; ++j) first_val[j] = acc[j];
             } else {
-              static_for<G::kNumReducers>([&](auto R) {
-                constexpr int d = G::template red_dim<R.value>();
-                constexpr int o = G::template red_off<R.value>();
-                V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + row) * d;
-#pragma unroll
-                for (int j = 0; j < d; ++j) dst[j] = acc[o + j];
-              });
+              store_row(t.row0 + row, acc);
             }
 #pragma unroll
             for (int j = 0; j < kAcc; ++j) acc[j] = V(0);
             ++row;
-            re = s_rel[row];
+            re = srel[row];
           }
         }
       }
     }
-
-    // ---- segmented inclusive scan of the carries (key = row the carry belongs to) -------------------
+    // segmented inclusive scan of the carries (key = row the carry belongs to)
     const int key = row;
     V val[kAcc];
 #pragma unroll
@@ -436,13 +462,11 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 #pragma unroll
     for (int i = 0; i < kAcc; ++i) pv[i] = shfl_up_any(val[i], 1);
     named_bar_sync(1, BLOCK);   // [B] warp aggregates visible
-
-
     // fold: CTA carry (belongs to local row 0) then the aggregates of the warps before this one
     int fk = 0;
     V fv[kAcc];
 #pragma unroll
-    for (int i = 0; i < kAcc; ++i) fv[i] = s_carry[(k & 1) * kAcc + i];
+    for (int i = 0; i < kAcc; ++i) fv[i] = s_carry[kpar * kAcc + i];
     for (int w = 0; w < warp; ++w) {
       const int wk = s_wkey[w];
       if (wk == fk) {
@@ -456,7 +480,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     }
     if (tid == BLOCK - 1) {   // carry into the next tile = inclusive value of the last thread
 #pragma unroll
-      for (int i = 0; i < kAcc; ++i) s_carry[((k + 1) & 1) * kAcc + i] = (fk == key) ? fv[i] + val[i] : val[i];
+      for (int i = 0; i < kAcc; ++i) s_carry[(kpar ^ 1) * kAcc + i] = (fk == key) ? fv[i] + val[i] : val[i];
     }
     if (lane > 0) {
       if (pk == fk) {
@@ -468,15 +492,160 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       }
     }
     if (row > xs) {   // first closed row = what earlier threads / tiles carried + this thread's part
-      static_for<G::kNumReducers>([&](auto R) {
-        constexpr int d = G::template red_dim<R.value>();
-        constexpr int o = G::template red_off<R.value>();
-        V* dst = G::template red_out<R.value>(p) + (size_t)(row0 + xs) * d;
 #pragma unroll
-        for (int j = 0; j < d; ++j) dst[j] = fv[o + j] + first_val[o + j];
-      });
+      for (int i = 0; i < kAcc; ++i) first_val[i] = fv[i] + first_val[i];
+      store_row(t.row0 + xs, first_val);
     }
-    // s_wkey / s_wval / s_prod / s_rel are next written after the next tile's first barrier
+  };
+  auto thread_span = [&](const TileRef& t, const int* srel, int& xs, int& ys, int& n_items) {
+    const int total_items = t.nrows + t.nnz;
+    const int d0 = min(tid * IPT, total_items);
+    n_items = min(d0 + IPT, total_items) - d0;
+    merge_path_search<int, int>(d0, srel, 0, t.nrows, t.nnz, xs, ys);
+  };
+
+  if constexpr (!G::kGatherNeedsRow && !Cfg::kPipeline) {
+    // ---- plain loop: stage -> registers -> gathers -> products -> classify -> reduce --------------------
+    for (int k = 0; k < count; ++k) {
+      TileRef t{0, 0, 0, 0};
+      TileT tile;
+      const OffsetT* rend = nullptr;
+      if (!acquire(k, t, tile, rend)) { failed = true; break; }
+      last_row1 = t.row0 + t.nrows;
+#ifdef FLEX_STREAM_ONLY
+      release(k);
+      continue;
+#endif
+      const bool my_long = convert(t, rend, s_rel);
+      {
+        typename G::EReg er[IPT];
+        typename G::GEdge ge[IPT];
+        typename G::GRow gr[1];
+        map_load(t, tile, er);
+        release(k);
+        map_gather(t, er, ge, gr);
+        map_products(t, er, ge, gr, s_prod);
+      }
+      const bool long_tile = named_bar_or(1, BLOCK, my_long);   // [P] products + s_rel complete, tile classified
+      if (!long_tile) {
+        reduce_short(t, k & 1, s_prod, s_rel);   // the next tile's first barrier orders these reads
+      } else {
+        int xs, ys, n_items;
+        thread_span(t, s_rel, xs, ys, n_items);
+        reduce_long(t, k & 1, s_prod, s_rel, xs, ys, n_items);
+      }
+    }
+  } else if constexpr (!G::kGatherNeedsRow) {
+    // ---- software-pipelined loop: the gathers of tile k are in flight while tile k-1 is reduced.
+    //      s_rel and s_prod are double-buffered by tile parity; one classifying barrier per tile. -------
+    TileRef prev{0, 0, 0, 0};
+    bool prev_long = false;
+    for (int k = 0; k <= count; ++k) {
+      const bool have = k < count;
+      TileRef cur{0, 0, 0, 0};
+      bool my_long = false;
+      typename G::EReg er[IPT];
+      typename G::GEdge ge[IPT];
+      typename G::GRow gr[1];
+      int* srel_k = s_rel + (k & 1) * (Cfg::kTile + 1);
+      V* sprod_k = s_prod + (size_t)(k & 1) * kAcc * Cfg::kTile;
+      if (have) {
+        TileT tile;
+        const OffsetT* rend = nullptr;
+        if (!acquire(k, cur, tile, rend)) { failed = true; break; }
+        last_row1 = cur.row0 + cur.nrows;
+#ifdef FLEX_STREAM_ONLY
+        release(k);
+        continue;
+#endif
+        my_long = convert(cur, rend, srel_k);
+        map_load(cur, tile, er);
+        release(k);
+        map_gather(cur, er, ge, gr);
+      }
+      if (k > 0) {
+        const int* srel_p = s_rel + ((k - 1) & 1) * (Cfg::kTile + 1);
+        const V* sprod_p = s_prod + (size_t)((k - 1) & 1) * kAcc * Cfg::kTile;
+        if (!prev_long) {
+          reduce_short(prev, (k - 1) & 1, sprod_p, srel_p);
+        } else {
+          int xs, ys, n_items;
+          thread_span(prev, srel_p, xs, ys, n_items);
+          reduce_long(prev, (k - 1) & 1, sprod_p, srel_p, xs, ys, n_items);
+        }
+      }
+      if (have) map_products(cur, er, ge, gr, sprod_k);
+      prev_long = named_bar_or(1, BLOCK, my_long);   // [P] products + s_rel of tile k complete, tile classified
+      prev = cur;
+    }
+  } else {
+    // ---- the map needs per-row data (row-identity selectors) ---------------------------------------------
+    for (int k = 0; k < count; ++k) {
+      TileRef t{0, 0, 0, 0};
+      TileT tile;
+      const OffsetT* rend = nullptr;
+      if (!acquire(k, t, tile, rend)) { failed = true; break; }
+      last_row1 = t.row0 + t.nrows;
+      const bool my_long = convert(t, rend, s_rel);
+      const bool long_tile = named_bar_or(1, BLOCK, my_long);   // [R] s_rel complete, tile classified
+      if (!long_tile) {
+        // short rows: one thread per row does gather + map + sum in registers (the row's own vertex data is
+        // loaded once) and stores the row; local row 0 continues the CTA's carry, local row `nrows`
+        // (partial) becomes the next carry
+        for (int r = tid; r <= t.nrows; r += BLOCK) {
+          const int lo = r ? s_rel[r - 1] : 0;
+          const int hi = r < t.nrows ? s_rel[r] : t.nnz;
+          V sum[kAcc];
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[(k & 1) * kAcc + j] : V(0);
+          typename G::GRow grow;
+          if (lo < hi) G::gather_row(p, t.row0 + r, grow);
+          for (int e0 = lo; e0 < hi; e0 += Cfg::kBatch) {
+            typename G::EReg er[Cfg::kBatch];
+            typename G::GEdge ge[Cfg::kBatch];
+#pragma unroll
+            for (int b = 0; b < Cfg::kBatch; ++b)
+              if (e0 + b < hi) { G::load_edge(tile, e0 + b, er[b]); G::gather_edge(p, er[b], ge[b]); }
+#pragma unroll
+            for (int b = 0; b < Cfg::kBatch; ++b)
+              if (e0 + b < hi) G::map(p, er[b], t.nz0 + e0 + b, grow, ge[b], sum);
+          }
+          if (r < t.nrows) {
+            store_row(t.row0 + r, sum);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) s_carry[((k + 1) & 1) * kAcc + j] = sum[j];
+          }
+        }
+        release(k);
+        continue;
+      }
+      // long rows: each thread walks its merge-path span once and records the row of every edge
+      int xs, ys, n_items;
+      thread_span(t, s_rel, xs, ys, n_items);
+      {
+        int row = xs, nz = ys, re = s_rel[xs];
+#pragma unroll
+        for (int i = 0; i < IPT; ++i) {
+          if (i < n_items) {
+            if (nz < re) { s_rowid[nz] = (unsigned short)row; ++nz; }
+            else { ++row; re = s_rel[row]; }
+          }
+        }
+      }
+      named_bar_sync(1, BLOCK);   // [W] s_rowid complete
+      {
+        typename G::EReg er[IPT];
+        typename G::GEdge ge[IPT];
+        typename G::GRow gr[IPT];
+        map_load(t, tile, er);
+        release(k);
+        map_gather(t, er, ge, gr);
+        map_products(t, er, ge, gr, s_prod);
+      }
+      named_bar_sync(1, BLOCK);   // [P] products complete
+      reduce_long(t, k & 1, s_prod, s_rel, xs, ys, n_items);
+    }
   }
 
   // ---- hand the CTA's carry to the last CTA ---------------------------------------------------------

@@ -71,7 +71,9 @@ def test_small_tiles_and_few_ctas(tile_items):
     ir = graphs.spmv_graph()
     for dt in ("float64", "int64"):
         dtype = np.dtype(dt)
-        ext = GraphExtension(ir, tile_items=tile_items, max_ctas=3)
+        probe = GraphExtension(ir)
+        cap = probe.symbols(NP2T[dtype]).graph_info.default_tile_items      # a tile cannot exceed the compiled carve-up
+        ext = GraphExtension(ir, tile_items=min(tile_items, cap), max_ctas=3)
         nnz = 2000 if tile_items < 10 else 60000
         prob = problems.random_problem(ir, 97, 97, nnz, seed=5, dtype=dtype)
         ref, _, sums = ir_eval.run_graph(ir, prob, dtype, num_threads=4, want_abs_sums=True)
