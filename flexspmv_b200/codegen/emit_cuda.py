@@ -279,6 +279,16 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
             w(f"    r.{s_['selector_name']} = fx::ld_vec<V, {dim_of(s_['shape'])}>(t.template stream<{si}, V>(le));")
     w("    (void)t; (void)le; (void)r;")
     w("  }")
+    # L1 prefetch of what gather_edge will read, issued by the producer warp one tile ahead
+    w("  template <class Tile, class IdxT>")
+    w("  __device__ __forceinline__ static void prefetch_edge(const Params& p, const Tile& t, IdxT le) {")
+    for s_ in edge_sel:
+        d = dim_of(s_["shape"])
+        si = stream_of["idx:" + s_["selector_name"]]
+        w(f"    fx::prefetch_l1<V, {d}>(p.{s_['target']} + (long long)(*t.template stream<{si}, int>(le)) * {d});")
+    w("    (void)p; (void)t; (void)le;")
+    w("  }")
+    w(f"  static constexpr bool kHasEdgeGather = {'true' if edge_sel else 'false'};")
     w("  __device__ __forceinline__ static void gather_edge(const Params& p, const EReg& r, GEdge& g) {")
     for s_ in edge_sel:
         d = dim_of(s_["shape"])

@@ -202,6 +202,21 @@ __device__ __forceinline__ Vec<V, D> ldg_vec(const V* p) {   // read-only global
   return r;
 }
 
+// L1 prefetch of one gathered record (every 32-byte sector it touches)
+template <typename V, int D>
+__device__ __forceinline__ void prefetch_l1(const V* p) {
+  const char* c = reinterpret_cast<const char*>(p);
+  constexpr int kBytes = int(sizeof(V)) * D;
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(c));
+  if constexpr (kBytes > 32) {
+#pragma unroll
+    for (int o = 32; o < kBytes; o += 32) asm volatile("prefetch.global.L1 [%0];" ::"l"(c + o));
+  }
+  if constexpr (kBytes > 4 && kBytes <= 32) {   // a record that is not sector-aligned may straddle two sectors
+    if ((reinterpret_cast<uintptr_t>(c) & 31) + kBytes > 32) asm volatile("prefetch.global.L1 [%0];" ::"l"(c + kBytes - 1));
+  }
+}
+
 template <typename V, int D>
 __device__ __forceinline__ Vec<V, D> ld_vec(const V* p) {   // plain load (shared or global)
   Vec<V, D> r;

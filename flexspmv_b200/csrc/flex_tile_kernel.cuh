@@ -24,6 +24,14 @@ struct TileCfg {
   // slower than the plain loop on B200 (58% against 68% of the HBM peak on the 7-point fp64 SpMV: one
   // CTA less per SM for the second s_prod / s_rel buffer), so it is off by default
   static constexpr bool kPipeline = PIPELINE_;
+  // producer-warp L1 prefetch of the records the next tile's gathers will read: measured slower on B200
+  // (62% against 67% of the HBM peak on the 7-point fp64 SpMV, 16% against 21% on the power-law matrix: the
+  // prefetches add L1 traffic and delay the producer's next bulk copies), so it is off unless requested
+#ifdef FLEX_GATHER_PREFETCH
+  static constexpr bool kPrefetchGathers = true;
+#else
+  static constexpr bool kPrefetchGathers = false;
+#endif
   static constexpr int kBlock = BLOCK_;
   static constexpr int kIpt = IPT_;
   static constexpr int kStages = STAGES_;
@@ -215,6 +223,22 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     if (w.bulk_bytes) bulk_g2s(dst + off, w.src, w.bulk_bytes, &bars[s]);
   };
 
+  // Producer warp, one tile ahead of the consumers: once tile j's index arrays have landed in shared memory,
+  // prefetch into L1 every vertex record its gathers will read, so that the consumers' gathers hit L1
+  // instead of paying an L2 round trip in the middle of the tile.
+  auto prefetch_gathers = [&](int j) {
+    if constexpr (G::kHasEdgeGather && S >= 2 && Cfg::kPrefetchGathers) {
+      const int s = j % S;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bars[s], (uint32_t)(j / S) & 1u, kWaitPolls))) return;
+      const Ctl& c = ctls[s];
+      const unsigned char* stage = s_stage + (size_t)s * L::kStageBytes;
+      SmemTile<G> tile;
+      static_for<NS>([&](auto I) { tile.base[I.value] = reinterpret_cast<const char*>(stage + c.stream_off[I.value]); });
+      const int nnz = c.nnz;
+      for (int e = lane; e < nnz; e += 32) G::prefetch_edge(p, tile, e);
+    }
+  };
+
   if constexpr (!DIRECT) {
     if (tid == 0) {
 #pragma unroll
@@ -244,7 +268,9 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         issue(c_row, c_nz, n_row, n_nz, s);
         c_row = n_row; c_nz = n_nz; n_row = nn_row; n_nz = nn_nz;
         issued = k + 1;
+        if (k >= 1) prefetch_gathers(k - 1);   // tile k-1 has (almost certainly) landed: warm L1 for its gathers
       }
+      if (!pfail && count >= 1) prefetch_gathers(count - 1);
       if (pfail && lane == 0) {   // the consumers never released a stage: flag it, let copies in flight land, leave
         atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
         a.header->debug[4] = (uint32_t)issued; a.header->debug[5] = blockIdx.x;
