@@ -62,7 +62,17 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.idx = gpu_index
         self.proc = None
-        self.lines = []
+        self.lines = []      # (arrival time, csv line)
+        self.t_begin = self.t_end = None
+
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
+
+    def under_load(self) -> int:
+        return sum(1 for t, _ in self.lines if self.t_begin is not None and t >= self.t_begin)
 
     def start(self):
         try:
@@ -75,9 +85,9 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self) -> dict:
+    def stop(self, extra_steps: int = 0) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -86,7 +96,12 @@ class ClockSampler:
         except Exception:
             pass
         sm, mx, reasons, power = [], [], set(), []
-        for ln in self.lines:
+        in_timed = 0
+        for t, ln in self.lines:
+            if self.t_begin is None or t < self.t_begin:
+                continue
+            if self.t_end is not None and t <= self.t_end:
+                in_timed += 1
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -98,7 +113,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "samples_in_timed_region": in_timed,
+                "trailing_untimed_steps_sampled": extra_steps, "reasons": sorted(reasons)}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -282,12 +298,14 @@ def run_ours(args) -> None:
             return 1
         return 0
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()          # nvidia-smi needs a moment to start: begin before the warm-up
     for i in range(W):
         op.step()
     barrier()
-    sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.mark_begin()
     launches0 = ext.launches
     extra = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -302,7 +320,23 @@ def run_ours(args) -> None:
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     total_ms = float(ms.item())
-    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        sampler.mark_end()
+    # a timed region of a few tens of milliseconds can fall between two nvidia-smi samples: keep the same
+    # workload running (untimed) until a handful of samples under load exist, and say so in the line
+    extra_steps = 0
+    t_wait = time.time()
+    while True:
+        need = torch.tensor([1 if (rank == 0 and sampler.under_load() < 4 and time.time() - t_wait < 3.0) else 0], device=dev)
+        if world > 1:
+            dist.broadcast(need, 0)
+        if int(need.item()) == 0:
+            break
+        for _ in range(20):
+            op.step()
+        extra_steps += 20
+        torch.cuda.synchronize()
+    clocks = sampler.stop(extra_steps) if rank == 0 else None
     my_launches = ext.launches - launches0 + extra
     launches = torch.tensor([my_launches], dtype=torch.int64, device=dev)
     if world > 1:

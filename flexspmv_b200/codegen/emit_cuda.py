@@ -418,9 +418,13 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     w("    (void)p; (void)r; (void)e; (void)gr; (void)ge; (void)acc;")
     w("  }")
     w("};")
-    edge_regs = sum(dim_of(s_["shape"]) * VBYTES[dtype] // 4 for s_ in ir.selector_register
-                    if s_.get("selector") == 1 and not s_.get("row_identity"))
-    batch = max(2, min(8, 24 // max(edge_regs, 1)))
+    # registers one edge keeps live in the fused thread-per-row loop: its staged record (indices + edge
+    # tensors) and its gathered vertex data; the batch is the largest of 8/4/3/2 edges that stays under ~28
+    words = VBYTES[dtype] // 4
+    per_edge_regs = sum(dim_of(s_["shape"]) * words for s_ in ir.selector_register
+                        if not (s_.get("selector") == 1 and s_.get("row_identity")))
+    per_edge_regs += sum(1 for s_ in ir.selector_register if s_.get("selector") == 1 and not s_.get("row_identity"))
+    batch = next((b_ for b_ in (8, 4, 3, 2) if b_ * max(per_edge_regs, 1) <= 28), 2)
     w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}>;")
     w("}  // namespace")
     w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg)")
