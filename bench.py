@@ -205,7 +205,7 @@ def time_config(name, ir, ext, values, indices, ro, outputs, num_rows, nnz, num_
                                 "edges_per_s": nnz / cold_ms * 1e3, "iters": len(cold)}}
 
 
-def single_gpu_configs(peak: float) -> list:
+def single_gpu_configs(peak: float, only=None) -> list:
     import torch
     from flexspmv_b200 import graphs, problems
     from flexspmv_b200.binding import GraphExtension
@@ -223,7 +223,9 @@ def single_gpu_configs(peak: float) -> list:
     specs = [("config0 2D Poisson 512^2 fp64", "spmv", lambda: problems.poisson2d(512), 8, 200),
              ("config1 spring-mass 1024^2 fp32", "spring_mass", lambda: problems.spring_mass(1024), 4, 200),
              ("config2 shallow-water Rusanov 1024^2 fp64", "rusanov", lambda: problems.shallow_water(1024), 8, 200)]
-    for name, gname, make, vb, iters in specs:
+    for ci, (name, gname, make, vb, iters) in enumerate(specs):
+        if only is not None and ci not in only:
+            continue
         ir = graphs.ALL_GRAPHS[gname]()
         prob = make()
         vals, idxs, ro = upload(ir, prob)
@@ -234,6 +236,8 @@ def single_gpu_configs(peak: float) -> list:
         out.append(time_config(name, ir, GraphExtension(ir), vals, idxs, ro, outs, prob.num_rows, prob.nnz, prob.num_cols,
                                alg, iters, peak, flush))
         del vals, idxs, ro, outs
+    if only is not None and 3 not in only:
+        return out
     # config 3 is generated on the device (268 M non-zeros)
     ir = graphs.spmv_graph()
     ro, cols, vals, x = problems.powerlaw_device(1 << 24, 3, dev)
@@ -267,6 +271,9 @@ def run_ours(args) -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     peak, peak_kind = load_peaks()
+    if args.only_config is not None:      # profiling aid: one single-GPU configuration, nothing else
+        print(json.dumps({"configs": single_gpu_configs(peak, only=[args.only_config])}), flush=True)
+        return
     n = args.grid
     n2 = n * n
     K, W = args.steps, max(args.warmup, 3)
@@ -283,7 +290,7 @@ def run_ours(args) -> None:
     g.manual_seed(4 * 1000 + rank)
     x0 = torch.rand(plan.rows, generator=g, device=dev, dtype=torch.float64) * 2.0 - 1.0
     ext = load_builtin("spmv")
-    op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x0, ext=ext)
+    op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x0, ext=ext, overlap=not args.no_overlap)
     alg_bytes, nnz_total = poisson3d_bytes(n)
 
     def barrier():
@@ -301,8 +308,15 @@ def run_ours(args) -> None:
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()          # nvidia-smi needs a moment to start: begin before the warm-up
-    for i in range(W):
+    for i in range(W + (W % 2)):     # an even number of warm-up steps: the captured pair starts from buffer 0
         op.step()
+    use_graph = world > 1 and not args.no_graph and K % 2 == 0 and K <= 200
+    if use_graph:
+        flag = torch.tensor([1 if op.capture_pair() else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)          # all ranks replay, or none does
+        use_graph = bool(flag.item())
+        if not use_graph:
+            op.graph = None
     barrier()
     if rank == 0:
         sampler.mark_begin()
@@ -311,11 +325,16 @@ def run_ours(args) -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for i in range(K):
-        extra += renorm(W + i)
-        op.step()
+    if use_graph:
+        for i in range(K // 2):
+            op.step_pair()
+    else:
+        for i in range(K):
+            extra += renorm(W + i)
+            op.step()
     e1.record()
     barrier()
+    timed_launches = (K * op.launches_per_step) if use_graph else (ext.launches - launches0 + extra)
     ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -337,8 +356,7 @@ def run_ours(args) -> None:
         extra_steps += 20
         torch.cuda.synchronize()
     clocks = sampler.stop(extra_steps) if rank == 0 else None
-    my_launches = ext.launches - launches0 + extra
-    launches = torch.tensor([my_launches], dtype=torch.int64, device=dev)
+    launches = torch.tensor([timed_launches], dtype=torch.int64, device=dev)
     if world > 1:
         dist.all_reduce(launches)
     ms_per_step = total_ms / K
@@ -384,6 +402,8 @@ def run_ours(args) -> None:
         "config": {"workload": f"config4: 3D Poisson {n}^3 7-point SpMV, fp64 values, int64 row offsets, int32 columns, "
                                f"{nnz_total} non-zeros, x <- A x with one z-plane halo per neighbour per iteration",
                    "partition": f"{world} nnz-balanced z-slab(s), merge-path tile plan cached across iterations",
+                   "halo_overlap": bool(op.overlap), "launches_per_step_per_rank": op.launches_per_step,
+                   "cuda_graph": bool(use_graph),
                    "l2": "inputs larger than L2 (per-GPU matrix slab >= 1.8 GB)", "algorithmic_bytes_per_step": alg_bytes,
                    "halo_bytes_per_neighbour_per_direction": n2 * 8 if world > 1 else 0},
         "edges_per_s": nnz_total / ms_per_step * 1e3,
@@ -428,6 +448,10 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table (N = 1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (N = 1)")
+    ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3],
+                    help="run just this single-GPU configuration (kernel-only timings) and print its entry")
+    ap.add_argument("--no-overlap", action="store_true", help="N > 1: exchange halos before one launch instead of overlapping")
+    ap.add_argument("--no-graph", action="store_true", help="N > 1: enqueue every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -42,7 +42,10 @@ struct TileCfg {
 };
 
 constexpr int kMaxCtas = 2048;            // capacity of the per-CTA carry arrays in the workspace
-constexpr int kShortRowMax = 64;              // tiles whose rows are all at most this long reduce one thread per row
+#ifndef FLEX_SHORT_ROW_MAX
+#define FLEX_SHORT_ROW_MAX 64
+#endif
+constexpr int kShortRowMax = FLEX_SHORT_ROW_MAX;              // tiles whose rows are all at most this long reduce one thread per row
 constexpr uint64_t kWaitPolls = 1000000000ull;  // bound on every mbarrier wait: one second of %globaltimer
 
 template <class G>
@@ -548,7 +551,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         typename G::GEdge ge[IPT];
         typename G::GRow gr[1];
         map_load(t, tile, er);
-        release(k);
+        release(k);     // as early as possible: the refill latency of this stage is what bounds the kernel
         map_gather(t, er, ge, gr);
         map_products(t, er, ge, gr, s_prod);
       }

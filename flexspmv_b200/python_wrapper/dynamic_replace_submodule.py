@@ -1,0 +1,128 @@
+"""Swaps a fused FX sub-module for the CUDA operator.  Same contract as the reference's
+``dynamic_replace_submodule(compiled_eqn, ext, submodule_name)``
+(python_wrapper/dynamic_replace_submodule.py:202-258): find the ``call_module`` node, collect the Selector
+index tensors and the Reducer's row ids from the sub-module, turn the row ids into CSR offsets, and
+install a wrapper whose ``__call__`` marshals the placeholders into the operator's positional order
+(:180-193) and returns the outputs as a list.
+
+What the reference's wrapper does on every call and this one does once: ``.contiguous()`` copies
+(:147-149; here only non-contiguous arguments are copied), device moves of the index buffers, and the
+int64 -> int32 cast of the row offsets (kept int64 when they do not fit int32: the kernels take both).
+What the reference never checks and this one does once at construction: the Reducer's row ids must be
+sorted ascending (its ``_coo_rows_to_csr_ptr`` silently assumes it, :20-41).
+
+Selector / Reducer modules are recognised by duck typing (an ``idx`` tensor; a Reducer also has ``n``), so
+the module works with ``easier``'s classes without importing them.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.nn as nn
+
+
+def coo_rows_to_csr_ptr(row_ids: torch.Tensor, num_rows: Optional[int] = None) -> torch.Tensor:
+    """Sorted COO row ids -> CSR offsets with the leading 0 (int64)."""
+    row_ids = row_ids.to(torch.int64)
+    if num_rows is None:
+        if row_ids.numel() == 0:
+            raise RuntimeError("row_ids is empty; cannot infer num_rows")
+        num_rows = int(row_ids.max().item()) + 1
+    if row_ids.numel() > 1 and bool((row_ids[1:] < row_ids[:-1]).any()):
+        raise ValueError("Reducer row ids must be sorted ascending (edges stored CSR-by-row)")
+    counts = torch.bincount(row_ids, minlength=num_rows)
+    crow = torch.zeros(num_rows + 1, dtype=torch.int64, device=row_ids.device)
+    torch.cumsum(counts, dim=0, out=crow[1:])
+    return crow
+
+
+def _is_selector(m) -> bool:
+    return hasattr(m, "idx") and not hasattr(m, "n")
+
+
+def _is_reducer(m) -> bool:
+    return hasattr(m, "idx") and hasattr(m, "n")
+
+
+class DynamicCudaWrapper(nn.Module):
+    def __init__(self, ext, input_param_names: Sequence[str], non_gather_value_inputs: Sequence[str],
+                 gather_value_inputs: Sequence[str], selector_idx_tensors: Sequence[torch.Tensor],
+                 row_end_offsets: Optional[torch.Tensor]):
+        super().__init__()
+        self._ext = ext
+        self._names = list(input_param_names)
+        self._non_gather, self._gather = list(non_gather_value_inputs), list(gather_value_inputs)
+        self._sel_names: List[str] = []
+        for i, t in enumerate(selector_idx_tensors):
+            t = t.contiguous()
+            if t.dtype != torch.int32:
+                if t.numel() and int(t.max()) >= 2 ** 31:
+                    raise ValueError("selector indices beyond int32 are not supported")
+                t = t.to(torch.int32)
+            self.register_buffer(f"selector_{i}_idx", t, persistent=False)
+            self._sel_names.append(f"selector_{i}_idx")
+        if row_end_offsets is not None:
+            ro = row_end_offsets.contiguous()
+            if int(ro[-1]) < 2 ** 31 and ro.dtype != torch.int32:
+                ro = ro.to(torch.int32)
+        else:
+            ro = None
+        self.register_buffer("row_end_offsets", ro, persistent=False)
+        self._moved_to = None
+
+    def _buffers_on(self, device):
+        if self._moved_to != device:
+            for n in self._sel_names + (["row_end_offsets"] if self.row_end_offsets is not None else []):
+                setattr(self, n, getattr(self, n).to(device))
+            self._moved_to = device
+
+    def __call__(self, *args):
+        amap: Dict[str, torch.Tensor] = {n: (a if a.is_contiguous() else a.contiguous()) for n, a in zip(self._names, args)}
+        device = next(iter(amap.values())).device
+        self._buffers_on(device)
+        ro = self.row_end_offsets
+        gv = self._gather[0] if self._gather else self._non_gather[0]
+        num_cols = int(amap[gv].shape[0])
+        if ro is None:     # map-only graph: the operator still takes a (dummy) offsets tensor
+            ro = torch.tensor([42], dtype=torch.int32, device=device)
+            num_rows = num_cols
+        else:
+            num_rows = int(ro.numel() - 1)
+        call_args = [amap[n] for n in self._non_gather] + [amap[n] for n in self._gather] + \
+                    [getattr(self, n) for n in self._sel_names] + [ro, num_rows, num_cols]
+        outs = self._ext.merged_spmv_launch(*call_args)
+        if outs is None:
+            return []
+        return list(outs) if isinstance(outs, tuple) else [outs]
+
+
+def dynamic_replace_submodule(compiled_eqn: nn.Module, ext, submodule_name: str) -> bool:
+    graph = compiled_eqn.jit_engine.graph
+    for node in graph.nodes:
+        if node.op != "call_module" or node.name != submodule_name:
+            continue
+        gm = compiled_eqn.get_submodule(node.target)
+        names = [n.name for n in gm.graph.nodes if n.op == "placeholder"]
+        selectors, reducer = [], None
+        for qn, m in gm.named_modules():
+            if qn == "":
+                continue
+            if _is_reducer(m):
+                reducer = m
+                break                      # the first Reducer's row ids define the CSR of the whole sub-module
+            if _is_selector(m):
+                selectors.append((qn, m))
+        sel_q = {q for q, _ in selectors}
+        gathers: List[str] = []
+        for n in gm.graph.nodes:
+            if n.op == "call_module" and n.target in sel_q:
+                for a in n.args:
+                    if hasattr(a, "op") and a.op == "placeholder" and a.name not in gathers:
+                        gathers.append(a.name)
+        ro = coo_rows_to_csr_ptr(reducer.idx, int(reducer.n)) if reducer is not None else None
+        wrapper = DynamicCudaWrapper(ext, names, [n for n in names if n not in gathers], gathers,
+                                     [m.idx for _, m in selectors], ro)
+        setattr(compiled_eqn, submodule_name, wrapper)
+        return True
+    return False

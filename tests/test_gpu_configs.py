@@ -1,0 +1,129 @@
+"""The five benchmark configurations on the GPU: against the CPU oracle at sizes the oracle finishes in
+seconds (identical numpy inputs on both sides), against the committed golden fixtures, and at full
+size through size-independent properties (checksum against an independent torch reduction, linearity,
+agreement with torch's own CSR product, run-to-run determinism)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from flexspmv_b200 import graphs, multi_gpu, problems
+from flexspmv_b200.binding import GraphExtension
+from golden_io import golden_files, load
+from oracle import ir_eval
+from parity import TOL, assert_outputs_match, row_error
+from test_gpu_parity import run_gpu
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name,make", [
+    ("config0 poisson2d 128", lambda: ("spmv", problems.poisson2d(128))),
+    ("config0 poisson2d 512 (full size)", lambda: ("spmv", problems.poisson2d(512))),
+    ("config1 spring-mass 160", lambda: ("spring_mass", problems.spring_mass(160))),
+    ("config2 shallow-water 96", lambda: ("rusanov", problems.shallow_water(96))),
+    ("config3 power-law 2^16", lambda: ("spmv", problems.powerlaw(1 << 16, cap=20000))),
+    ("config4 poisson3d 40, int64 offsets", lambda: ("spmv", problems.poisson3d(40))),
+], ids=lambda v: v if isinstance(v, str) else "")
+def test_config_matches_oracle(name, make):
+    gname, prob = make()
+    ir = graphs.ALL_GRAPHS[gname]()
+    dt = next(iter(prob.values.values())).dtype
+    ref, _, sums = ir_eval.run_graph(ir, prob, dt, num_threads=8, want_abs_sums=True)
+    got, _ = run_gpu(GraphExtension(ir), ir, prob, dt)
+    assert_outputs_match(ir, got, ref, sums, dt, what=name)
+
+
+@pytest.mark.parametrize("path", golden_files(), ids=lambda p: os.path.basename(p)[:-4])
+def test_gpu_matches_golden_fixture(path):
+    """The fixtures were produced by the reference's own generated CPU operator."""
+    prob, dt, threads, outs, written = load(path)
+    ir = graphs.ALL_GRAPHS[prob.graph]()
+    _, _, sums = ir_eval.run_graph(ir, prob, dt, num_threads=threads, want_abs_sums=True)
+    got, got_written = run_gpu(GraphExtension(ir), ir, prob, dt)
+    assert_outputs_match(ir, got, outs, sums, dt, what=os.path.basename(path))
+    for k, r in written.items():
+        g = got_written[k].reshape(r.shape)
+        if np.dtype(dt).kind == "i" or prob.graph != "ops_zoo":
+            assert np.array_equal(g, r), f"in-place input {k}"
+
+
+def _spmv(ext, vals, x, cols, ro, n):
+    y = torch.empty(n, dtype=vals.dtype, device=vals.device)
+    ext.launch_into([vals, x], [cols], ro, [y], n, cols.numel(), x.numel())
+    return y
+
+
+def test_config3_full_size_properties():
+    """16.8 M rows, ~260 M non-zeros, rows up to 100 000 long, built on the device."""
+    dev = torch.device("cuda:0")
+    ro, cols, vals, x = problems.powerlaw_device(1 << 24, 3, dev)
+    n = x.numel()
+    ext = GraphExtension(graphs.spmv_graph())
+    y = _spmv(ext, vals, x, cols, ro, n)
+    # checksum of checksums: sum(y) == sum over edges of val * x[col] (independent fp64 reduction)
+    terms = vals.double() * x[cols.long()].double()
+    assert abs(float(y.double().sum()) - float(terms.sum())) <= 1e-5 * float(terms.abs().sum())
+    # per-row agreement with torch's CSR product on the same device arrays
+    A = torch.sparse_csr_tensor(ro.long(), cols.long(), vals.double(), size=(n, n))
+    y_ref = (A @ x.double().unsqueeze(1)).squeeze(1)
+    rid = torch.repeat_interleave(torch.arange(n, device=dev), (ro[1:] - ro[:-1]).long())
+    abs_sum = torch.zeros(n, dtype=torch.float64, device=dev).index_add_(0, rid, terms.abs())
+    err = ((y.double() - y_ref).abs() / abs_sum.clamp_min(1e-300)).max()
+    assert float(err) <= TOL[np.dtype(np.float32)]
+    # linearity: A(2x) == 2 A x exactly in binary floating point, and determinism
+    y2 = _spmv(ext, vals, x * 2.0, cols, ro, n)
+    assert torch.equal(y2, y * 2.0)
+    assert torch.equal(_spmv(ext, vals, x, cols, ro, n), y)
+
+
+def test_config4_slab_properties_int64_offsets():
+    """A 512 x 512 x 24 slab of the 512^3 problem (same plane size and row structure), int64 offsets,
+    built on the device exactly as the benchmark builds each rank's block."""
+    dev = torch.device("cuda:0")
+    n, planes = 512, 24
+    ro, cols, vals = multi_gpu.poisson3d_planes_device(n, 1, 1 + planes, dev, col_shift=0)
+    rows = planes * n * n
+    x = torch.rand((planes + 2) * n * n, dtype=torch.float64, device=dev) * 2 - 1
+    ext = GraphExtension(graphs.spmv_graph())
+    y = _spmv(ext, vals, x, cols, ro, rows)
+    # the 7-point stencil applied with torch slicing on the (z, y, x) grid
+    X = x.view(planes + 2, n, n)
+    C = X[1:-1]
+    ref = 6.0 * C - X[:-2] - X[2:]
+    ref[:, 1:, :] -= C[:, :-1, :]
+    ref[:, :-1, :] -= C[:, 1:, :]
+    ref[:, :, 1:] -= C[:, :, :-1]
+    ref[:, :, :-1] -= C[:, :, 1:]
+    err = (y.view(planes, n, n) - ref).abs().max() / 12.0      # sum |terms| <= 12 for |x| <= 1
+    assert float(err) <= 1e-12
+    ones = torch.ones_like(x)
+    y1 = _spmv(ext, vals, ones, cols, ro, rows)                 # row sums of the Laplacian: 0 inside, >0 on faces
+    assert float(y1.view(planes, n, n)[:, 1:-1, 1:-1].abs().max()) == 0.0
+    assert torch.equal(_spmv(ext, vals, x, cols, ro, rows), y)
+
+
+def test_operator_reuses_and_invalidates_its_plan():
+    """The shim caches the partition per row-offset tensor; a different matrix of the same size must not
+    be served from the old plan."""
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    a = problems.random_problem(ir, 3000, 3000, 50000, seed=1, dtype=np.float64)
+    b = problems.random_problem(ir, 3000, 3000, 50000, seed=2, dtype=np.float64)
+    for prob in (a, b, a):
+        ref, _, sums = ir_eval.run_graph(ir, prob, np.float64, num_threads=8, want_abs_sums=True)
+        got, _ = run_gpu(ext, ir, prob, np.float64)
+        assert row_error(got[0], ref[0], sums[0]) <= 1e-12
+    # in-place edit of the same offsets tensor bumps its version and forces a re-plan
+    dev = torch.device("cuda:0")
+    ro = torch.from_numpy(a.row_offsets).to(dev)
+    vals = torch.from_numpy(a.values["vals"]).to(dev)
+    x = torch.from_numpy(a.values["x"]).to(dev)
+    cols = torch.from_numpy(a.indices["selector"]).to(dev)
+    (y0,) = ext.merged_spmv_launch(vals, x, cols, ro, a.num_rows, a.num_cols)
+    ro.copy_(torch.from_numpy(b.row_offsets).to(dev))
+    (y1,) = ext.merged_spmv_launch(torch.from_numpy(b.values["vals"]).to(dev), torch.from_numpy(b.values["x"]).to(dev),
+                                   torch.from_numpy(b.indices["selector"]).to(dev), ro, b.num_rows, b.num_cols)
+    refb, _, sumsb = ir_eval.run_graph(ir, b, np.float64, num_threads=8, want_abs_sums=True)
+    assert row_error(y1.cpu().numpy(), refb[0], sumsb[0]) <= 1e-12

@@ -110,3 +110,25 @@ def test_device_builder_matches_numpy_generator():
     assert np.array_equal(ro.numpy(), q.row_offsets) and np.array_equal(cols.numpy(), q.indices["selector"])
     assert np.array_equal(vals.numpy(), q.values["vals"])
     assert np.array_equal(multi_gpu.poisson3d_row_offsets(n, "cpu").numpy(), problems.poisson3d(n).row_offsets)
+
+
+def test_boundary_rows_and_sub_csr():
+    """The rows that read a halo are exactly the first / last z-plane of an interior slab; the three
+    sub-matrices tile the block and reproduce its product."""
+    n, n2 = 8, 64
+    first = [0, 3 * n2, 6 * n2, 8 * n2]
+    plans = multi_gpu.make_halo_plans(first, [0, 2 * n2, 5 * n2], [4 * n2 - 1, 7 * n2 - 1, 8 * n2 - 1])
+    x_full = torch.from_numpy(problems.poisson3d(n).values["x"])
+    for plan, (z0, z1) in zip(plans, ((0, 3), (3, 6), (6, 8))):
+        ro, cols, vals = multi_gpu.poisson3d_planes_device(n, z0, z1, "cpu", col_shift=plan.col_shift)
+        lo, hi = multi_gpu.boundary_rows(ro, cols, plan)
+        assert (lo, hi) == (n2 if plan.halo_lo else 0, n2 if plan.halo_hi else 0)
+        x_local = x_full[plan.col_shift:plan.col_shift + plan.local_len]
+        whole = _local_matvec(ro, cols, vals, x_local)
+        got = torch.empty_like(whole)
+        for r0, r1 in ((lo, plan.rows - hi), (0, lo), (plan.rows - hi, plan.rows)):
+            if r1 > r0:
+                sro, scols, svals = multi_gpu.sub_csr(ro, cols, vals, r0, r1)
+                assert int(sro[0]) == 0 and int(sro[-1]) == scols.numel()
+                got[r0:r1] = _local_matvec(sro, scols, svals, x_local)
+        assert torch.equal(got, whole)
