@@ -39,7 +39,10 @@ def test_emitter_is_deterministic_and_resolves_overloads():
     assert "fx::PowHalf{}" in r and "kGatherNeedsRow = true" in r and "kNumReducers = 3, kAccDim = 3" in r
     s = emit_cuda.emit_graph(graphs.spring_mass_graph(), "float32")
     assert "kNumStreams = 3" in s                              # L, k, sel_dst index; sel_src is the row id
-    assert "p.sel_src_idx" not in s.split("struct Gathered")[1]
+    body = s.split("struct GRow")[1]
+    assert "sel_src_idx" not in body and "idx_sel_src" not in body      # the row-identity index array is never read
+    assert "g.sel_src = fx::ldg_vec<V, 2>(p.p + row * 2);" in body      # it is the row the merge path already knows
+    assert "int idx_sel_dst;" in body
     m = emit_cuda.emit_graph(graphs.mixed_dims_graph(), "int64")
     assert "fx::st_vec(p.out_t1 + (long long)e * 2, t1)" in m  # per-edge map output
 
