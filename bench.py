@@ -290,7 +290,7 @@ def run_ours(args) -> None:
     g.manual_seed(4 * 1000 + rank)
     x0 = torch.rand(plan.rows, generator=g, device=dev, dtype=torch.float64) * 2.0 - 1.0
     ext = load_builtin("spmv")
-    op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x0, ext=ext, overlap=not args.no_overlap)
+    op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x0, ext=ext, overlap=args.overlap)
     alg_bytes, nnz_total = poisson3d_bytes(n)
 
     def barrier():
@@ -435,7 +435,15 @@ def run_ours(args) -> None:
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # A captured graph holds NCCL kernels; tearing the communicator down under it has hung at exit.
+        # Everything is measured and printed: drop the graph, meet once more, and leave without the
+        # interpreter's teardown.
+        op.graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -450,7 +458,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (N = 1)")
     ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3],
                     help="run just this single-GPU configuration (kernel-only timings) and print its entry")
-    ap.add_argument("--no-overlap", action="store_true", help="N > 1: exchange halos before one launch instead of overlapping")
+    ap.add_argument("--overlap", action="store_true", help="N > 1: split off the halo-reading rows and overlap the exchange with the interior launch")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: enqueue every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -198,9 +198,10 @@ class PartitionedSpmv:
     """One rank's share of y = A x for a row-block partitioned banded matrix, iterated as
     x <- A x: the local vector is double-buffered ([halo_lo | owned | halo_hi] each) so an
     iteration is "exchange halos of the current buffer, fused SpMV into the owned part of the other
-    buffer".  With ``overlap`` (default when there is more than one rank) the rows are split once into
+    buffer".  With ``overlap`` the rows are split once into
     the few that read a halo (first / last rows of the block) and the interior: the interior launch is
-    enqueued while the NCCL transfers are in flight and the two small boundary launches follow them."""
+    enqueued while the NCCL transfers are in flight and the two small boundary launches follow them
+    (``overlap=True``; off by default, see ``__init__``)."""
 
     def __init__(self, plan: HaloPlan, row_offsets: torch.Tensor, cols_local: torch.Tensor, vals: torch.Tensor,
                  x_owned: torch.Tensor, group=None, ext=None, overlap: Optional[bool] = None):
@@ -213,7 +214,9 @@ class PartitionedSpmv:
         self.cur = 0
         self.buf[0][plan.halo_lo:plan.halo_lo + plan.rows] = x_owned
         self.nnz = int(cols_local.numel())
-        self.overlap = (plan.world > 1) if overlap is None else (overlap and plan.world > 1)
+        # measured on 8 B200s (512^3, 100 steps): 0.479 ms/step without the split, 0.491 ms with it -- the two
+        # boundary launches cost more than the 2 MiB exchange they hide -- so overlapping is opt-in
+        self.overlap = bool(overlap) and plan.world > 1
         self.parts = []          # (row_begin, row_end, ro_sub, cols_sub, vals_sub); interior first
         if self.overlap:
             lo_rows, hi_rows = boundary_rows(row_offsets, cols_local, plan)
