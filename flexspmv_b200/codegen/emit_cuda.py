@@ -33,12 +33,28 @@ def _lit(a) -> str:
     return f"V({repr(a)})"
 
 
+def stage_values(ir: GraphIR) -> bool:
+    """Whether the edge TENSORS (values, attributes) go through the bulk-copy stages like the index arrays and
+    the row-end offsets, or are read straight from global memory with coalesced loads issued together with
+    the gathers (they are not on the index -> gather dependency chain).  Measured on B200: for graphs reduced
+    in two phases (plain SpMV) staging wins, 67 % against 53 % of the HBM peak on the 7-point fp64 SpMV -- a
+    direct value load is a DRAM round trip inside the tile, longer than the L2-hit gather it travels with;
+    for graphs that run fused, one thread per row (row-identity selectors: spring-mass, Rusanov), the direct
+    loads win (33 % against 30 %), because the stage goes back to the producer only at the end of the tile and
+    a smaller stage is refilled sooner.  FLEXSPMV_STAGE_VALUES=0/1 overrides."""
+    import os
+    env = os.environ.get("FLEXSPMV_STAGE_VALUES")
+    if env in ("0", "1"):
+        return env == "1"
+    return not any(s_.get("selector") == 1 and s_.get("row_identity") for s_ in ir.selector_register)
+
+
 def _stream_bytes_per_edge(ir: GraphIR, vb: int) -> Tuple[int, int]:
     """(bytes staged per edge, number of staged streams): every distinct edge tensor plus one int32
     index array per distinct non-row-identity selector."""
     seen, total = set(), 0
     for s in ir.selector_register:
-        if s.get("selector") != 1 and s["target"] not in seen:
+        if stage_values(ir) and s.get("selector") != 1 and s["target"] not in seen:
             seen.add(s["target"])
             total += vb * dim_of(s["shape"])
     for s in ir.selector_register:
@@ -104,8 +120,8 @@ TUNED_CONFIGS = {
     "spmv_f64": (256, 5, 2, 4),          # 7-point fp64 SpMV: 66-69 % of the HBM peak; 3 stages / bigger CTAs / 3 or 5 CTAs all lower
     "spmv_f32": (256, 5, 2, 4),
     "spmv_i64": (256, 5, 2, 4),
-    "spring_mass_f32": (256, 7, 2, 4),   # 31 % (5 items: 30 %, 9 items x 3 CTAs: 24 %)
-    "rusanov_f64": (256, 4, 2, 2),       # 27 % (3 items x 3 CTAs: 23 %)
+    "spring_mass_f32": (256, 8, 2, 4),   # 35 %: 2048-item tiles hold ~228 rows of 8 edges, one per thread (5 items: 30 %)
+    "rusanov_f64": (256, 4, 2, 3),       # 29 %: 1024-item tiles hold 256 rows of 3 edges (3 items: 25 %, 5 items x 2 CTAs: 20 %)
 }
 
 
@@ -136,8 +152,10 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     # ---- streams (staged per-edge arrays) ---------------------------------------------------------
     streams: List[Tuple[str, str, int]] = []      # (param field, element C type, bytes per edge)
     stream_of: Dict[str, int] = {}
+    staged_values = stage_values(ir)
+    inplace_targets = {op_["args"][0] for op_ in ir.map_operations if op_["op"] in ("add_", "copy_", "setitem")}
     for s in ir.selector_register:
-        if s.get("selector") != 1 and s["target"] not in stream_of:
+        if staged_values and s.get("selector") != 1 and s["target"] not in stream_of:
             stream_of[s["target"]] = len(streams)
             streams.append((s["target"], "V", f"int(sizeof(V)) * {dim_of(s['shape'])}"))
     for s in ir.selector_register:
@@ -206,6 +224,9 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     seen = set()
     for s in ir.selector_register:
         if s.get("selector") == 1 and s["target"] not in seen:
+            seen.add(s["target"])
+            w(f"    ok = ok && (reinterpret_cast<uintptr_t>(p.{s['target']}) % fx::VecIO<V, {dim_of(s['shape'])}>::kChunk == 0);")
+        if s.get("selector") != 1 and not staged_values and s["target"] not in seen:
             seen.add(s["target"])
             w(f"    ok = ok && (reinterpret_cast<uintptr_t>(p.{s['target']}) % fx::VecIO<V, {dim_of(s['shape'])}>::kChunk == 0);")
     w("    (void)p; return ok;")
@@ -278,7 +299,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
         w("    int unused;")
     w("  };")
     w("  template <class Tile, class IdxT>")
-    w("  __device__ __forceinline__ static void load_edge(const Tile& t, IdxT le, EReg& r) {")
+    w("  __device__ __forceinline__ static void load_edge(const Params& p, const Tile& t, IdxT le, long long e, EReg& r) {")
     for s_ in edge_sel:
         si = stream_of["idx:" + s_["selector_name"]]
         w(f"    r.idx_{s_['name']} = *t.template stream<{si}, int>(le);")
@@ -286,9 +307,15 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     for s_ in edge_regs_list:
         if s_["selector_name"] not in seen_e:
             seen_e.add(s_["selector_name"])
-            si = stream_of[s_["target"]]
-            w(f"    r.{s_['selector_name']} = fx::ld_vec<V, {dim_of(s_['shape'])}>(t.template stream<{si}, V>(le));")
-    w("    (void)t; (void)le; (void)r;")
+            d_ = dim_of(s_["shape"])
+            if staged_values:
+                si = stream_of[s_["target"]]
+                w(f"    r.{s_['selector_name']} = fx::ld_vec<V, {d_}>(t.template stream<{si}, V>(le));")
+            elif s_["target"] in inplace_targets:   # written through the same pointer by this kernel: no read-only path
+                w(f"    r.{s_['selector_name']} = fx::ld_vec<V, {d_}>(p.{s_['target']} + e * {d_});")
+            else:
+                w(f"    r.{s_['selector_name']} = fx::ldg_vec<V, {d_}>(p.{s_['target']} + e * {d_});")
+    w("    (void)p; (void)t; (void)le; (void)e; (void)r;")
     w("  }")
     # L1 prefetch of what gather_edge will read, issued by the producer warp one tile ahead
     w("  template <class Tile, class IdxT>")

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(BLOCK) flex_edge_kernel(const typename G::Para
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       const long long e = base + (long long)i * BLOCK + tid;
-      if (e < a.num_edges) { G::load_edge(tile, e, er[i]); G::gather_row(p, e, gr[i]); G::gather_edge(p, er[i], g[i]); }
+      if (e < a.num_edges) { G::load_edge(p, tile, e, e, er[i]); G::gather_row(p, e, gr[i]); G::gather_edge(p, er[i], g[i]); }
     }
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {

@@ -367,7 +367,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     ttile.advance(tid);   // element `tid` at offset 0: the unrolled accesses are base + constant
 #pragma unroll
     for (int i = 0; i < IPT; ++i)
-      if (i * BLOCK + tid < t.nnz) G::load_edge(ttile, i * BLOCK, er[i]);
+      if (i * BLOCK + tid < t.nnz) G::load_edge(p, ttile, i * BLOCK, t.nz0 + (i * BLOCK + tid), er[i]);
   };
   auto map_gather = [&](const TileRef& t, const typename G::EReg (&er)[IPT], typename G::GEdge (&ge)[IPT],
                         typename G::GRow (&gr)[G::kGatherNeedsRow ? IPT : 1]) {
@@ -634,7 +634,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
             typename G::GEdge ge[Cfg::kBatch];
 #pragma unroll
             for (int b = 0; b < Cfg::kBatch; ++b)
-              if (e0 + b < hi) { G::load_edge(tile, e0 + b, er[b]); G::gather_edge(p, er[b], ge[b]); }
+              if (e0 + b < hi) { G::load_edge(p, tile, e0 + b, t.nz0 + e0 + b, er[b]); G::gather_edge(p, er[b], ge[b]); }
 #pragma unroll
             for (int b = 0; b < Cfg::kBatch; ++b)
               if (e0 + b < hi) G::map(p, er[b], t.nz0 + e0 + b, grow, ge[b], sum);
