@@ -38,7 +38,9 @@ def test_emitter_is_deterministic_and_resolves_overloads():
     r = emit_cuda.emit_graph(graphs.rusanov_graph(), "float64")
     assert "fx::PowHalf{}" in r and "kGatherNeedsRow = true" in r and "kNumReducers = 3, kAccDim = 3" in r
     s = emit_cuda.emit_graph(graphs.spring_mass_graph(), "float32")
-    assert "kNumStreams = 3" in s                              # L, k, sel_dst index; sel_src is the row id
+    assert "kNumStreams = 1" in s        # only the sel_dst index array is staged: sel_src is the row id, L and k are read directly
+    assert "r.L = fx::ldg_vec<V, 1>(p.L + e * 1);" in s
+    assert "kNumStreams = 2" in emit_cuda.emit_graph(graphs.spmv_graph(), "float64")    # two-phase graphs stage values too
     body = s.split("struct GRow")[1]
     assert "sel_src_idx" not in body and "idx_sel_src" not in body      # the row-identity index array is never read
     assert "g.sel_src = fx::ldg_vec<V, 2>(p.p + row * 2);" in body      # it is the row the merge path already knows
