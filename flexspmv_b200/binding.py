@@ -14,7 +14,7 @@ Differences from the reference binding, all on the host side of the same contrac
   * outputs are ``torch.empty`` (the kernels write every element; the reference needs torch::zeros
     because it accumulates with atomicAdd), scratch comes from torch's caching allocator instead of a
     per-call cudaMalloc/cudaFree (cuda_template/merged_binding_template.cu:42-49);
-  * the merge-path partition is planned once per (row_end_offsets tensor, version) and cached;
+  * the merge-path partition is planned once per (row_end_offsets tensor, version, stream) and cached;
   * int64 ``row_end_offsets`` are accepted as they are (the reference casts to int32);
   * an unsupported dtype raises (the reference prints to stderr and falls off the end of a non-void
     function, cuda_template/merged_binding_template.cu:65-68).
@@ -139,8 +139,11 @@ class GraphExtension:
         return vals
 
     def _workspace(self, syms: _Symbols, desc: Desc, ro: Optional[torch.Tensor], device) -> Tuple[torch.Tensor, int]:
+        # a workspace holds per-launch state (ticket, carries): launches that may overlap on the GPU must not
+        # share one, so the plan is cached per stream as well as per matrix
         key = (id(syms), desc.num_rows, desc.num_edges, desc.offset_bits, desc.tile_items, desc.max_ctas,
-               (ro.data_ptr(), ro._version) if ro is not None else None, device.index)
+               (ro.data_ptr(), ro._version) if ro is not None else None, device.index,
+               torch.cuda.current_stream(device).cuda_stream)
         hit = self._plans.get(key)
         if hit is not None:
             self._plans.move_to_end(key)
