@@ -152,3 +152,26 @@ def test_errors_are_loud():
         ext.merged_spmv_launch(vals[1:], x, idx, ro, 10, 10)              # misaligned streamed array (and short)
     lib = load_library()
     assert lib.flexspmv_partition(None, 32, ctypes.c_int64(1), ctypes.c_int64(1), 4, None, None) != 0
+
+
+def test_c_abi_edge_cases_empty_matrices():
+    """Below the operator's own `ne > 0` check the C ABI accepts matrices without edges (every row sums to
+    0) and without rows (nothing to do)."""
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    dev = torch.device("cuda:0")
+    x = torch.ones(64, dtype=torch.float64, device=dev)
+    vals = torch.zeros(16, dtype=torch.float64, device=dev)       # valid, aligned pointers; no element is read
+    cols = torch.zeros(16, dtype=torch.int32, device=dev)
+    for rows in (1, 37, 5000):
+        ro = torch.zeros(rows + 1, dtype=torch.int32, device=dev)
+        y = torch.full((rows,), float("nan"), dtype=torch.float64, device=dev)
+        ext.launch_into([vals, x], [cols], ro, [y], rows, 0, 64)
+        torch.cuda.synchronize()
+        assert float(y.abs().max()) == 0.0
+    ro = torch.zeros(1, dtype=torch.int32, device=dev)
+    y = torch.full((4,), 7.0, dtype=torch.float64, device=dev)
+    ext.launch_into([vals, x], [cols], ro, [y], 0, 0, 64)          # zero rows, zero edges: no launch at all
+    torch.cuda.synchronize()
+    assert float(y.min()) == 7.0
+    assert ext.device_status(torch.float64) == 0
