@@ -178,8 +178,7 @@ def run_reference(args) -> None:
 # --------------------------------------------------------------------------------------------------
 def time_config(name, ir, ext, values, indices, ro, outputs, num_rows, nnz, num_cols, alg_bytes, iters, peak, flush_buf):
     import torch
-    def launch():
-        ext.launch_into(values, indices, ro, outputs, num_rows, nnz, num_cols)
+    launch = ext.prepare(values, indices, ro, outputs, num_rows, nnz, num_cols).launch
     for _ in range(3):
         launch()
     torch.cuda.synchronize()

@@ -248,6 +248,26 @@ class GraphExtension:
         check(self.lib, st, "launch_into")
         self.launches += 1
 
+    def prepare(self, values: Sequence[torch.Tensor], indices: Sequence[torch.Tensor],
+                row_end_offsets: Optional[torch.Tensor], outputs: Sequence[torch.Tensor],
+                num_rows: int, num_edges: int, num_cols: int = 0) -> "PreparedLaunch":
+        """Binds one fixed set of tensors once (plan, workspace, C argument arrays) so that every later
+        ``launch()`` is a single foreign call on the current stream: the form for time-stepping loops, where
+        the reference wrapper re-marshals every argument on every call
+        (python_wrapper/dynamic_replace_submodule.py:147-199).  The row offsets must not change while the
+        object is in use; the value / index / output tensors may be rewritten in place."""
+        dt = values[0].dtype
+        syms = self.symbols(dt)
+        has_red = self.ir.has_reducer
+        device = values[0].device
+        desc = Desc(num_rows if has_red else 0, num_edges, num_cols,
+                    64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
+                    self.tile_items, self.max_ctas, 0)
+        with torch.cuda.device(device):
+            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device)
+        return PreparedLaunch(self, syms, desc, list(values), list(indices), row_end_offsets if has_red else None,
+                              list(outputs), ws, ws_bytes)
+
     def device_status(self, dtype: torch.dtype, row_end_offsets: Optional[torch.Tensor] = None) -> int:
         """Reads back the status word of the most recently used workspace (synchronises)."""
         if not self._plans:
@@ -258,6 +278,42 @@ class GraphExtension:
         check(self.lib, syms.device_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(out.data_ptr()), _stream_ptr()),
               "device_status")
         return int(out.item())
+
+
+class PreparedLaunch:
+    """One graph bound to one set of device tensors (see ``GraphExtension.prepare``)."""
+
+    def __init__(self, ext: GraphExtension, syms: _Symbols, desc: Desc, values, indices, ro, outputs, ws, ws_bytes):
+        self.ext, self._syms, self._desc = ext, syms, desc
+        self._keep = (values, indices, ro, outputs, ws)       # the raw pointers below borrow these tensors
+        self._device = ws.device.index
+        self._planned = torch.cuda.Event()                    # the plan kernels were enqueued on this stream
+        self._planned.record(torch.cuda.current_stream(ws.device))
+        self._ordered = {torch.cuda.current_stream(ws.device).cuda_stream}
+        vp = (ctypes.c_void_p * max(len(values), 1))(*[t.data_ptr() for t in values])
+        ip = (ctypes.c_void_p * max(len(indices), 1))(*[t.data_ptr() for t in indices])
+        op = (ctypes.c_void_p * max(len(outputs), 1))(*[t.data_ptr() for t in outputs])
+        self._args = (ctypes.byref(desc), vp, ip, ctypes.c_void_p(ro.data_ptr() if ro is not None else 0), op,
+                      ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws_bytes))
+        self._fn = syms.launch
+
+    def launch(self) -> None:
+        """Enqueues the fused pass on the current stream of the tensors' device.  The workspace carries
+        per-launch state, so launches of one prepared object must be stream-ordered with one another:
+        launching from a second stream needs a second prepared object."""
+        if torch.cuda.current_device() != self._device:
+            with torch.cuda.device(self._device):
+                return self.launch()
+        stream = torch.cuda.current_stream()
+        if stream.cuda_stream not in self._ordered:           # first use on another stream: after the plan
+            stream.wait_event(self._planned)
+            self._ordered.add(stream.cuda_stream)
+        st = self._fn(*self._args, ctypes.c_void_p(stream.cuda_stream))
+        if st != 0:
+            check(self.ext.lib, st, "launch")
+        self.ext.launches += 1
+
+    __call__ = launch
 
 
 def load_builtin(name: str, **kw) -> GraphExtension:

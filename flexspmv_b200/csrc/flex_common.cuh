@@ -137,9 +137,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 // 1-D bulk async copy global -> this CTA's shared memory, completion counted on an mbarrier.
 // dst, src 16-byte aligned, bytes a positive multiple of 16.  No multicast qualifier.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+  // The staged arrays are read once per launch: evict_first in L2 leaves the cache to the gathered
+  // records (measured on B200: +11% on a random-column matrix whose x is half the L2, neutral on stencils;
+  // marking the gathers evict_last on top of it was slower).
+  uint64_t pol;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
                    smem_u32(smem_dst)),
-               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
                : "memory");
 }
 // Orders earlier generic-proxy shared-memory accesses before later async-proxy (bulk copy) ones.
@@ -148,6 +153,10 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 template <typename T>
 __device__ __forceinline__ T shfl_up_any(T v, int delta) {
   return __shfl_up_sync(0xffffffffu, v, delta);
+}
+template <typename T>
+__device__ __forceinline__ T shfl_down_any(T v, int delta) {
+  return __shfl_down_sync(0xffffffffu, v, delta);
 }
 
 }  // namespace flex

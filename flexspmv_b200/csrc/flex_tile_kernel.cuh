@@ -95,7 +95,10 @@ struct TileSmemLayout {
   static constexpr int kOffWVal = int(align_up(kOffWKey + 4 * Cfg::kWarps, 16));
   static constexpr int kOffCarry = int(align_up(kOffWVal + sizeof(V) * kAcc * Cfg::kWarps, 16));
   static constexpr int kOffFlag = int(align_up(kOffCarry + sizeof(V) * kAcc * 2, 16));
-  static constexpr int kOffRel = int(align_up(kOffFlag + 16, 16));
+  // rows longer than kShortRowMax inside the current tile: [0..1] counters by tile parity, [2..] local rows
+  static constexpr int kMaxLong = Cfg::kTile / (kShortRowMax + 1) + 2;
+  static constexpr int kOffLong = int(align_up(kOffFlag + 16, 16));
+  static constexpr int kOffRel = int(align_up(kOffLong + 4 * (2 + kMaxLong), 16));
   static constexpr int kBuffers = (!G::kGatherNeedsRow && Cfg::kPipeline) ? 2 : 1;   // s_rel / s_prod double-buffered when tiles are pipelined
   static constexpr int kOffRowId = int(align_up(kOffRel + 4 * (Cfg::kTile + 1) * kBuffers, 16));
   static constexpr int kOffProd = int(align_up(kOffRowId + (G::kGatherNeedsRow ? 2 * Cfg::kTile : 0), 16));
@@ -164,6 +167,8 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   V* s_wval = reinterpret_cast<V*>(smem + L::kOffWVal);
   V* s_carry = reinterpret_cast<V*>(smem + L::kOffCarry);
   int* s_flag = reinterpret_cast<int*>(smem + L::kOffFlag);
+  int* s_nlong = reinterpret_cast<int*>(smem + L::kOffLong);
+  int* s_long = s_nlong + 2;
   int* s_rel = reinterpret_cast<int*>(smem + L::kOffRel);
   unsigned short* s_rowid = reinterpret_cast<unsigned short*>(smem + L::kOffRowId);
   V* s_prod = reinterpret_cast<V*>(smem + L::kOffProd);
@@ -250,6 +255,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     }
   }
   if (tid < 2 * kAcc) s_carry[tid] = V(0);
+  if (tid < 2) s_nlong[tid] = 0;
   __syncthreads();   // the only barrier that includes the producer warp
 
   // ---- producer warp: runs up to S tiles ahead of the consumers, off their critical path -----------
@@ -336,18 +342,25 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   };
   // Row ends as 32-bit edge indices relative to the tile, with a sentinel behind the last row.  Returns
   // whether this thread saw a long row (or a long trailing partial row).
-  auto convert = [&](const TileRef& t, const OffsetT* rend, int* srel) -> bool {
+  // With list >= 0 the long rows are also appended (in any order) to s_long, counted in s_nlong[list].
+  auto convert = [&](const TileRef& t, const OffsetT* rend, int* srel, int list) -> bool {
     bool my_long = false;
     for (int r = tid; r < t.nrows; r += BLOCK) {
       const long long end_r = (long long)rend[r];
       const long long beg_r = r ? (long long)rend[r - 1] : t.nz0;
       srel[r] = (int)(end_r - t.nz0);
-      my_long |= (end_r - beg_r) > kShortRowMax;
+      if ((end_r - beg_r) > kShortRowMax) {
+        my_long = true;
+        if (list >= 0) s_long[atomicAdd(&s_nlong[list], 1)] = r;
+      }
     }
     if (tid == 0) {
       srel[t.nrows] = 0x7fffffff;
       const long long beg_t = t.nrows ? (long long)rend[t.nrows - 1] : t.nz0;
-      my_long |= (t.nz0 + t.nnz - beg_t) > kShortRowMax;
+      if ((t.nz0 + t.nnz - beg_t) > kShortRowMax) {
+        my_long = true;
+        if (list >= 0) s_long[atomicAdd(&s_nlong[list], 1)] = t.nrows;
+      }
     }
     return my_long;
   };
@@ -402,18 +415,53 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   // ---- phase 2, short rows: one thread per row sums its products left to right and stores the row
   //      (coalesced); local row 0 continues the CTA's carry (buffer kpar), the trailing partial row
   //      (local row `nrows`) becomes the next carry ---------------------------------------------------------
-  auto reduce_short = [&](const TileRef& t, int kpar, const V* sprod, const int* srel) {
+  //      With list >= 0 the rows in s_long (longer than kShortRowMax) are left to whole warps: lanes sum
+  //      strided, a shuffle tree combines them.
+  auto reduce_short = [&](const TileRef& t, int kpar, const V* sprod, const int* srel, int list) {
 #ifdef FLEX_EXP_SKIP_REDUCE
     return;
 #endif
+    if (list >= 0) {
+      const int n_long = s_nlong[list];
+      for (int i = warp; i < n_long; i += Cfg::kWarps) {
+        const int r = s_long[i];
+        const int lo = r ? srel[r - 1] : 0;
+        const int hi = r < t.nrows ? srel[r] : t.nnz;
+        V sum[kAcc];
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) sum[j] = V(0);
+        for (int e = lo + lane; e < hi; e += 32) {
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) sum[j] += sprod[j * Cfg::kTile + e];
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) sum[j] += shfl_down_any(sum[j], off);
+        }
+        if (lane == 0) {
+          if (r == 0) {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) sum[j] = s_carry[kpar * kAcc + j] + sum[j];
+          }
+          if (r < t.nrows) {
+            store_row(t.row0 + r, sum);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) s_carry[(kpar ^ 1) * kAcc + j] = sum[j];
+          }
+        }
+      }
+    }
     for (int r = tid; r <= t.nrows; r += BLOCK) {
       const int lo = r ? srel[r - 1] : 0;
       const int hi = r < t.nrows ? srel[r] : t.nnz;
+      int n = hi - lo;
+      if (list >= 0 && n > kShortRowMax) continue;
       V sum[kAcc];
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[kpar * kAcc + j] : V(0);
       const V* q = sprod + lo;
-      int n = hi - lo;
       for (; n >= 4; n -= 4, q += 4) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -545,7 +593,8 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       release(k);
       continue;
 #endif
-      const bool my_long = convert(t, rend, s_rel);
+      if (tid == 0) s_nlong[(k + 1) & 1] = 0;   // the previous tile's list has been consumed (barrier in acquire)
+      const bool my_long = convert(t, rend, s_rel, k & 1);
       {
         typename G::EReg er[IPT];
         typename G::GEdge ge[IPT];
@@ -555,14 +604,16 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         map_gather(t, er, ge, gr);
         map_products(t, er, ge, gr, s_prod);
       }
-      const bool long_tile = named_bar_or(1, BLOCK, my_long);   // [P] products + s_rel complete, tile classified
-      if (!long_tile) {
-        reduce_short(t, k & 1, s_prod, s_rel);   // the next tile's first barrier orders these reads
-      } else {
+      const bool long_tile = named_bar_or(1, BLOCK, my_long);   // [P] products, s_rel and the long-row list complete
+#ifdef FLEX_MERGE_WALK_REDUCE
+      if (long_tile) {
         int xs, ys, n_items;
         thread_span(t, s_rel, xs, ys, n_items);
         reduce_long(t, k & 1, s_prod, s_rel, xs, ys, n_items);
+        continue;
       }
+#endif
+      reduce_short(t, k & 1, s_prod, s_rel, long_tile ? (k & 1) : -1);   // the next tile's first barrier orders these reads
     }
   } else if constexpr (!G::kGatherNeedsRow) {
     // ---- software-pipelined loop: the gathers of tile k are in flight while tile k-1 is reduced.
@@ -587,7 +638,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         release(k);
         continue;
 #endif
-        my_long = convert(cur, rend, srel_k);
+        my_long = convert(cur, rend, srel_k, -1);
         map_load(cur, tile, er);
         release(k);
         map_gather(cur, er, ge, gr);
@@ -596,7 +647,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         const int* srel_p = s_rel + ((k - 1) & 1) * (Cfg::kTile + 1);
         const V* sprod_p = s_prod + (size_t)((k - 1) & 1) * kAcc * Cfg::kTile;
         if (!prev_long) {
-          reduce_short(prev, (k - 1) & 1, sprod_p, srel_p);
+          reduce_short(prev, (k - 1) & 1, sprod_p, srel_p, -1);
         } else {
           int xs, ys, n_items;
           thread_span(prev, srel_p, xs, ys, n_items);
@@ -615,7 +666,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       const OffsetT* rend = nullptr;
       if (!acquire(k, t, tile, rend)) { failed = true; break; }
       last_row1 = t.row0 + t.nrows;
-      const bool my_long = convert(t, rend, s_rel);
+      const bool my_long = convert(t, rend, s_rel, -1);
       const bool long_tile = named_bar_or(1, BLOCK, my_long);   // [R] s_rel complete, tile classified
       if (!long_tile) {
         // short rows: one thread per row does gather + map + sum in registers (the row's own vertex data is

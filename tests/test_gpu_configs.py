@@ -127,3 +127,33 @@ def test_operator_reuses_and_invalidates_its_plan():
                                    torch.from_numpy(b.indices["selector"]).to(dev), ro, b.num_rows, b.num_cols)
     refb, _, sumsb = ir_eval.run_graph(ir, b, np.float64, num_threads=8, want_abs_sums=True)
     assert row_error(y1.cpu().numpy(), refb[0], sumsb[0]) <= 1e-12
+
+
+def test_prepared_launch_matches_operator_and_orders_after_its_plan():
+    """`prepare` binds tensors once; its launches must equal the operator's result, also when the first
+    launch happens on a stream other than the one the plan ran on."""
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    prob = problems.random_problem(ir, 20000, 20000, 300000, seed=21, dtype=np.float64)
+    dev = torch.device("cuda:0")
+    vals = torch.from_numpy(prob.values["vals"]).to(dev)
+    x = torch.from_numpy(prob.values["x"]).to(dev)
+    cols = torch.from_numpy(prob.indices["selector"]).to(dev)
+    ro = torch.from_numpy(prob.row_offsets).to(dev)
+    (want,) = ext.merged_spmv_launch(vals, x, cols, ro, prob.num_rows, prob.num_cols)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        y = torch.full((prob.num_rows,), float("nan"), dtype=torch.float64, device=dev)
+    side.synchronize()
+    other = GraphExtension(ir)                       # fresh plan cache: prepare() plans on the default stream
+    prepared = other.prepare([vals, x], [cols], ro, [y], prob.num_rows, prob.nnz, prob.num_cols)
+    with torch.cuda.stream(side):
+        prepared.launch()
+        prepared.launch()
+    side.synchronize()
+    assert torch.equal(y, want)
+    x.mul_(2.0)                                      # tensors may be rewritten in place between launches
+    prepared.launch()
+    torch.cuda.synchronize()
+    assert torch.equal(y, want * 2.0)
