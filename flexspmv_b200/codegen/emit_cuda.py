@@ -287,9 +287,10 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     # per-edge data that comes out of the staged arrays: copied to registers first, so that the stage can
     # be handed back to the producer before the gathers are even issued
     edge_regs_list = [s_ for s_ in ir.selector_register if s_.get("selector") != 1]
+    idx_names = list(dict.fromkeys(s_["selector_name"] for s_ in edge_sel))   # calls of one Selector share its index
     w("  struct EReg {")
-    for s_ in edge_sel:
-        w(f"    int idx_{s_['name']};")
+    for n_ in idx_names:
+        w(f"    int idx_{n_};")
     seen_e = set()
     for s_ in edge_regs_list:
         if s_["selector_name"] not in seen_e:
@@ -300,9 +301,9 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     w("  };")
     w("  template <class Tile, class IdxT>")
     w("  __device__ __forceinline__ static void load_edge(const Params& p, const Tile& t, IdxT le, long long e, EReg& r) {")
-    for s_ in edge_sel:
-        si = stream_of["idx:" + s_["selector_name"]]
-        w(f"    r.idx_{s_['name']} = *t.template stream<{si}, int>(le);")
+    for n_ in idx_names:
+        si = stream_of["idx:" + n_]
+        w(f"    r.idx_{n_} = *t.template stream<{si}, int>(le);")
     seen_e = set()
     for s_ in edge_regs_list:
         if s_["selector_name"] not in seen_e:
@@ -330,7 +331,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     w("  __device__ __forceinline__ static void gather_edge(const Params& p, const EReg& r, GEdge& g) {")
     for s_ in edge_sel:
         d = dim_of(s_["shape"])
-        w(f"    g.{s_['name']} = fx::ldg_vec<V, {d}>(p.{s_['target']} + (long long)r.idx_{s_['name']} * {d});")
+        w(f"    g.{s_['name']} = fx::ldg_vec<V, {d}>(p.{s_['target']} + (long long)r.idx_{s_['selector_name']} * {d});")
     w("    (void)p; (void)r; (void)g;")
     w("  }")
 
@@ -461,7 +462,8 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     words = VBYTES[dtype] // 4
     per_edge_regs = sum(dim_of(s_["shape"]) * words for s_ in ir.selector_register
                         if not (s_.get("selector") == 1 and s_.get("row_identity")))
-    per_edge_regs += sum(1 for s_ in ir.selector_register if s_.get("selector") == 1 and not s_.get("row_identity"))
+    per_edge_regs += len({s_["selector_name"] for s_ in ir.selector_register
+                          if s_.get("selector") == 1 and not s_.get("row_identity")})
     batch = next((b_ for b_ in (8, 4, 3, 2) if b_ * max(per_edge_regs, 1) <= 28), 2)
     w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}>;")
     w("}  // namespace")

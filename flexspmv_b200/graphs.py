@@ -90,9 +90,10 @@ def placeholder(name: str, shape: Tuple[int, ...]) -> Dict[str, Any]:
             "op": "placeholder", "args": (), "dtype_data": None}
 
 
-def selector_input(name: str, gather_src: str, shape: Tuple[int, ...]) -> Dict[str, Any]:
-    """A Selector module call; ``target`` names the index array, args[0] is the gathered tensor."""
-    return {"name": name, "target": name, "dtype": "int", "shape": tuple(shape),
+def selector_input(name: str, gather_src: str, shape: Tuple[int, ...], module: str | None = None) -> Dict[str, Any]:
+    """A Selector module call; ``target`` names the index array (the Selector module: several calls of one
+    module share it), args[0] is the gathered tensor."""
+    return {"name": name, "target": module or name, "dtype": "int", "shape": tuple(shape),
             "op": "call_module", "args": (NodeRef(gather_src),), "dtype_data": None}
 
 
@@ -101,9 +102,10 @@ def edge_register(name: str, shape: Tuple[int, ...]) -> Dict[str, Any]:
             "selector_name": name, "shape": tuple(shape), "dtype_data": None}
 
 
-def gather_register(name: str, gather_src: str, shape: Tuple[int, ...], row_identity: bool = False) -> Dict[str, Any]:
+def gather_register(name: str, gather_src: str, shape: Tuple[int, ...], row_identity: bool = False,
+                    module: str | None = None) -> Dict[str, Any]:
     d = {"name": name, "target": gather_src, "dtype": "TensorKeyT", "selector": 1,
-         "selector_name": name, "shape": tuple(shape), "dtype_data": None}
+         "selector_name": module or name, "shape": tuple(shape), "dtype_data": None}
     if row_identity:
         d["row_identity"] = True
     return d
@@ -226,6 +228,67 @@ def rusanov_graph() -> GraphIR:
     return _finish("rusanov", inputs, outputs, selreg, m, rusanov_graph.__doc__)
 
 
+def swe_delta_graph() -> GraphIR:
+    """The interior part of ``ShallowWaterEquation.delta`` of the reference's shallow-water model
+    (shallow_water_equation/swe_main.py:86-119): face reconstruction of h, uh, vh from the two cells of
+    every edge, ``phi_f = (1 - alpha) phi[src] + alpha phi[dst]``, face velocities ``uh_f / h_f`` and
+    ``vh_f / h_f``, and the three ``scatter`` reducers over the destination cell:
+      r_h  = sum uh_f sx + vh_f sy
+      r_uh = sum (u_f uh_f + h_f^2/2) sx + u_f vh_f sy
+      r_vh = sum v_f uh_f sx + (v_f vh_f + h_f^2/2) sy
+    as a torch.fx trace of that method lists them: the ``gather_src`` / ``gather_dst`` Selector modules are
+    called three times each (on h, uh, vh) and share one index array per module; edges are sorted by
+    destination cell, so ``gather_dst`` is the row id.  The boundary reducers (``scatter_b``) and the
+    ``-(...)/area`` update are separate, element-wise steps of the model.
+    Operator: merged_spmv_launch(alpha, sx, sy, h, uh, vh, gather_src_idx, gather_dst_idx,
+                                 row_end_offsets, nc, nc) -> (r_h, r_uh, r_vh)"""
+    S1 = (1,)
+    inputs = [placeholder("alpha", S1), placeholder("sx", S1), placeholder("sy", S1),
+              placeholder("h", S1), placeholder("uh", S1), placeholder("vh", S1)]
+    selreg = [edge_register("alpha", S1), edge_register("sx", S1), edge_register("sy", S1)]
+    for i, phi in enumerate(("h", "uh", "vh")):
+        sfx = "" if i == 0 else f"_{i}"
+        inputs.append(selector_input("gather_src" + sfx, phi, S1, module="gather_src"))
+        inputs.append(selector_input("gather_dst" + sfx, phi, S1, module="gather_dst"))
+        selreg.append(gather_register("gather_src" + sfx, phi, S1, module="gather_src"))
+        selreg.append(gather_register("gather_dst" + sfx, phi, S1, row_identity=True, module="gather_dst"))
+    m: List[Dict[str, Any]] = []
+
+    def op(name, kind, *args):
+        m.append(mop(name, kind, S1, *args))
+        return name
+
+    face = {}
+    for i, phi in enumerate(("h", "uh", "vh")):
+        sfx = "" if i == 0 else f"_{i}"
+        oma = op(f"oma_{phi}", "sub", 1.0, "alpha")          # traced once per face_reconstruct call
+        a = op(f"a_{phi}", "mul", oma, "gather_src" + sfx)
+        b = op(f"b_{phi}", "mul", "alpha", "gather_dst" + sfx)
+        face[phi] = op(f"{phi}_f", "add", a, b)
+    u_f = op("u_f", "truediv", face["uh"], face["h"])
+    v_f = op("v_f", "truediv", face["vh"], face["h"])
+    hh = op("hh", "mul", 0.5, face["h"])
+    hsq = op("h_f_square", "mul", hh, face["h"])
+    uhsx = op("uh_f_times_sx", "mul", face["uh"], "sx")
+    vhsy = op("vh_f_times_sy", "mul", face["vh"], "sy")
+    s_h = op("s_h", "add", uhsx, vhsy)
+    r_h = op("r_h", "reducer", s_h)
+    t1 = op("t1", "mul", u_f, face["uh"])
+    t2 = op("t2", "add", t1, hsq)
+    t3 = op("t3", "mul", t2, "sx")
+    t4 = op("t4", "mul", u_f, vhsy)
+    s_uh = op("s_uh", "add", t3, t4)
+    r_uh = op("r_uh", "reducer", s_uh)
+    t5 = op("t5", "mul", v_f, uhsx)
+    t6 = op("t6", "mul", v_f, face["vh"])
+    t7 = op("t7", "add", t6, hsq)
+    t8 = op("t8", "mul", t7, "sy")
+    s_vh = op("s_vh", "add", t5, t8)
+    r_vh = op("r_vh", "reducer", s_vh)
+    outputs = [out(r, "reducer", S1) for r in (r_h, r_uh, r_vh)]
+    return _finish("swe_delta", inputs, outputs, selreg, m, swe_delta_graph.__doc__)
+
+
 def mixed_dims_graph() -> GraphIR:
     """Unit-test graph shaped like the reference's demo model (easier_spmv.py:17-69, generated
     instance include/merged_agent_spmv.cuh:124-149): two selectors on one dim-2 vertex tensor, edge
@@ -305,6 +368,7 @@ ALL_GRAPHS = {
     "spmv": spmv_graph,
     "spring_mass": spring_mass_graph,
     "rusanov": rusanov_graph,
+    "swe_delta": swe_delta_graph,
     "mixed_dims": mixed_dims_graph,
     "ops_zoo": ops_zoo_graph,
     "edge_sum": edge_sum_graph,
@@ -316,6 +380,7 @@ GRAPH_DTYPES = {
     "spmv": ("float32", "float64", "int64"),
     "spring_mass": ("float32", "float64"),
     "rusanov": ("float64", "float32"),
+    "swe_delta": ("float64", "float32"),
     "mixed_dims": ("float32", "float64", "int64"),
     "ops_zoo": ("float32", "float64"),
     "edge_sum": ("float32", "float64", "int64"),

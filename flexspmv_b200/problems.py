@@ -151,6 +151,39 @@ def shallow_water(n: int = 1024, dtype=np.float64) -> Problem:
                    {"config": 2, "grid": n})
 
 
+def swe_mesh(n: int = 1024, dtype=np.float64) -> Problem:
+    """Inputs of the reference shallow-water model's fused ``delta`` graph (graphs.swe_delta_graph) on the
+    triangulated n x n square of ``shallow_water``: one directed edge per interior face and side (src =
+    the neighbour, dst = the cell the flux is scattered to), sorted by dst, so boundary cells have 2
+    edges (1 in two corners) and interior cells 3; face vectors (sx, sy) = outward normal x length as seen
+    from dst, interpolation weight alpha = 0.5 (equal-size cells), h as in ``shallow_water`` and a smooth
+    non-zero momentum field.  Deterministic (no rng).  The reference reads the same arrays from its HDF5
+    mesh files (shallow_water_equation/swe_main.py:19-75)."""
+    base = shallow_water(n, np.float64)
+    cells = base.num_rows
+    nbr = base.indices["sel_nbr"].astype(np.int64)
+    dst = base.indices["sel_self"].astype(np.int64)
+    keep = nbr != dst                       # boundary faces are self-edges there: the model treats them separately
+    src, dst = nbr[keep], dst[keep]
+    face = base.values["face"][keep]
+    ro = np.zeros(cells + 1, dtype=np.int64)
+    np.cumsum(np.bincount(dst, minlength=cells), out=ro[1:])
+    hs = 1.0 / n
+    sq = np.arange(n * n)
+    iy, ix = sq // n, sq % n
+    cx, cy = np.empty(cells), np.empty(cells)
+    cx[0::2], cy[0::2] = (ix + 2.0 / 3.0) * hs, (iy + 1.0 / 3.0) * hs
+    cx[1::2], cy[1::2] = (ix + 1.0 / 3.0) * hs, (iy + 2.0 / 3.0) * hs
+    h = base.values["U"][:, 0]
+    uh = 0.05 * h * np.sin(2 * np.pi * cx) * np.cos(2 * np.pi * cy)
+    vh = -0.05 * h * np.cos(2 * np.pi * cx) * np.sin(2 * np.pi * cy)
+    values = {"alpha": np.full(src.shape[0], 0.5), "sx": face[:, 0] * face[:, 2], "sy": face[:, 1] * face[:, 2],
+              "h": h, "uh": uh, "vh": vh}
+    return Problem("swe_delta", {k: np.ascontiguousarray(v.astype(dtype)) for k, v in values.items()},
+                   {"gather_src": src.astype(np.int32), "gather_dst": dst.astype(np.int32)},
+                   ro.astype(np.int32), cells, cells, {"grid": n})
+
+
 # ----------------------------------------------------------------------------------------------
 # config 3: power-law CSR
 # ----------------------------------------------------------------------------------------------

@@ -156,6 +156,8 @@ FLEXSPMV_DECLARE_GRAPH(spring_mass_f32)
 FLEXSPMV_DECLARE_GRAPH(spring_mass_f64)
 FLEXSPMV_DECLARE_GRAPH(rusanov_f64)
 FLEXSPMV_DECLARE_GRAPH(rusanov_f32)
+FLEXSPMV_DECLARE_GRAPH(swe_delta_f64)
+FLEXSPMV_DECLARE_GRAPH(swe_delta_f32)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_f32)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_f64)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_i64)

@@ -3,7 +3,7 @@ the reference tree into oracle/_ref by oracle/ref_build.py) on small seeded prob
 ships no golden vectors of its own, so these fixtures are what pins the oracle on machines where the
 reference tree is absent.  Each file holds the inputs, the thread count and the reference outputs.
 
-    python tests/golden/make_golden.py      # needs the reference tree (default /root/reference)
+    python tests/golden/make_golden.py [name ...]     # needs the reference tree; no name = all fixtures
 """
 import os
 import sys
@@ -25,6 +25,8 @@ CASES = [
     ("spmv_f64_poisson3d_10", "spmv", np.float64, lambda ir: problems.poisson3d(10, offset_dtype=np.int32), 8),
     ("spring_mass_f32_lattice_20", "spring_mass", np.float32, lambda ir: problems.spring_mass(20), 8),
     ("rusanov_f64_mesh_12", "rusanov", np.float64, lambda ir: problems.shallow_water(12), 6),
+    ("swe_delta_f64_mesh_12", "swe_delta", np.float64, lambda ir: problems.swe_mesh(12), 6),
+    ("swe_delta_f32_cut_rows", "swe_delta", np.float32, lambda ir: problems.random_problem(ir, 200, 200, 4000, 14, np.float32), 5),
     ("mixed_dims_f64", "mixed_dims", np.float64, lambda ir: problems.random_problem(ir, 150, 90, 2500, 9, np.float64), 4),
     ("mixed_dims_i64", "mixed_dims", np.int64, lambda ir: problems.random_problem(ir, 150, 90, 2500, 10, np.int64), 4),
     ("ops_zoo_f64", "ops_zoo", np.float64, lambda ir: problems.random_problem(ir, 120, 80, 2000, 11, np.float64), 4),
@@ -36,7 +38,10 @@ CASES = [
 def main():
     if not ref_build.build_all():
         raise SystemExit("reference tree not found: cannot generate golden fixtures")
+    only = set(sys.argv[1:])
     for name, gname, dt, make, threads in CASES:
+        if only and name not in only:
+            continue
         ir = graphs.ALL_GRAPHS[gname]()
         prob = make(ir)
         outs, written = ref_run.run_graph(ir, prob, dt, num_threads=threads)
