@@ -100,6 +100,67 @@ __global__ void validate_kernel(const OffsetT* __restrict__ row_offsets, long lo
   else if (bad_idx) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_ARG);
 }
 
+// One Runge-Kutta stage of the shallow-water model's per-cell arithmetic, fused: the reducers' sums
+// become the stage's increments d = -(r [+ r_boundary]) / area, the running sum of increments is
+// extended, and either the next stage's state x + c d or (last stage) the step x += w sum is written.
+// Every operation is a separate IEEE operation in the order the model's torch expressions evaluate.
+template <typename V>
+struct SweStageArgs {
+  const V* r[3];        // interior reducer sums (h, uh, vh)
+  const V* rb[2];       // boundary reducer sums (uh, vh)
+  const V* area;
+  V* x[3];              // state (read; written by the last stage)
+  V* acc[3];            // running d1 + d2 + ...
+  V* stage[3];          // state for the next delta evaluation (not written by the last stage)
+  V c, w;
+  long long n;
+  int first, last;
+};
+template <typename V>
+__global__ void __launch_bounds__(256) swe_stage_kernel(const SweStageArgs<V> a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+    const V area = a.area[i];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      V sum = a.r[k][i];
+      if (k > 0) sum = sum + a.rb[k - 1][i];
+      const V d = (-sum) / area;
+      const V acc = a.first ? d : a.acc[k][i] + d;
+      const V x = a.x[k][i];
+      if (a.last) {
+        a.x[k][i] = x + a.w * acc;
+      } else {
+        a.acc[k][i] = acc;
+        a.stage[k][i] = x + a.c * d;
+      }
+    }
+  }
+}
+template <typename V>
+int swe_stage_launch(const void* const* r, const void* const* rb, const void* area, void* const* x, void* const* acc,
+                     void* const* stage, double c, double w, long long n, int first, int last, cudaStream_t st) {
+  SweStageArgs<V> a;
+  for (int k = 0; k < 3; ++k) {
+    a.r[k] = static_cast<const V*>(r[k]);
+    a.x[k] = static_cast<V*>(x[k]);
+    a.acc[k] = static_cast<V*>(acc[k]);
+    a.stage[k] = static_cast<V*>(stage[k]);
+    if (!a.r[k] || !a.x[k] || !a.acc[k] || !a.stage[k]) return FLEXSPMV_ERR_BAD_ARG;
+  }
+  for (int k = 0; k < 2; ++k) {
+    a.rb[k] = static_cast<const V*>(rb[k]);
+    if (!a.rb[k]) return FLEXSPMV_ERR_BAD_ARG;
+  }
+  a.area = static_cast<const V*>(area);
+  a.c = (V)c; a.w = (V)w; a.n = n; a.first = first; a.last = last;
+  if (n == 0) return 0;
+  long long grid = (n + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  swe_stage_kernel<V><<<(unsigned)grid, 256, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace flex
 
 extern "C" {
@@ -173,6 +234,16 @@ int flexspmv_validate_csr(const void* d_row_offsets, int32_t offset_bits, int64_
     flex::validate_kernel<long long><<<(unsigned)grid, block, 0, st>>>(static_cast<const long long*>(d_row_offsets), num_rows,
                                                                        num_edges, d_index, num_vertices, d_status);
   return (int)cudaGetLastError();
+}
+
+int flexspmv_swe_rk_stage(int32_t value_bytes, const void* const* d_r, const void* const* d_rb, const void* d_area,
+                          void* const* d_x, void* const* d_acc, void* const* d_stage, double c, double w, int64_t n,
+                          int32_t first, int32_t last, void* stream) {
+  if (!d_r || !d_rb || !d_area || !d_x || !d_acc || !d_stage || n < 0) return FLEXSPMV_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (value_bytes == 8) return flex::swe_stage_launch<double>(d_r, d_rb, d_area, d_x, d_acc, d_stage, c, w, n, first, last, st);
+  if (value_bytes == 4) return flex::swe_stage_launch<float>(d_r, d_rb, d_area, d_x, d_acc, d_stage, c, w, n, first, last, st);
+  return FLEXSPMV_ERR_BAD_ARG;
 }
 
 }  // extern "C"

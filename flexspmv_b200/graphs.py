@@ -289,6 +289,29 @@ def swe_delta_graph() -> GraphIR:
     return _finish("swe_delta", inputs, outputs, selreg, m, swe_delta_graph.__doc__)
 
 
+def swe_boundary_graph() -> GraphIR:
+    """The boundary part of ``ShallowWaterEquation.delta`` (shallow_water_equation/swe_main.py:96-114):
+    ``gather_b_h_square = 0.5 * gather_b(h)**2`` scattered with ``scatter_b`` once times ``bsx`` and once
+    times ``bsy``.  One "edge" per boundary cell, sorted by cell; ``gather_b`` and ``scatter_b`` use the
+    same index (``bcells``), so the selector is the row id.
+    Operator: merged_spmv_launch(bsx, bsy, h, gather_b_idx, row_end_offsets, nc, nc) -> (rb_uh, rb_vh)"""
+    S1 = (1,)
+    inputs = [placeholder("bsx", S1), placeholder("bsy", S1), placeholder("h", S1),
+              selector_input("gather_b", "h", S1)]
+    selreg = [edge_register("bsx", S1), edge_register("bsy", S1),
+              gather_register("gather_b", "h", S1, row_identity=True)]
+    m = [
+        mop("hb2", "pow", S1, "gather_b", 2),
+        mop("gather_b_h_square", "mul", S1, 0.5, "hb2"),
+        mop("bx", "mul", S1, "gather_b_h_square", "bsx"),
+        mop("rb_uh", "reducer", S1, "bx"),
+        mop("by", "mul", S1, "gather_b_h_square", "bsy"),
+        mop("rb_vh", "reducer", S1, "by"),
+    ]
+    outputs = [out("rb_uh", "reducer", S1), out("rb_vh", "reducer", S1)]
+    return _finish("swe_boundary", inputs, outputs, selreg, m, swe_boundary_graph.__doc__)
+
+
 def mixed_dims_graph() -> GraphIR:
     """Unit-test graph shaped like the reference's demo model (easier_spmv.py:17-69, generated
     instance include/merged_agent_spmv.cuh:124-149): two selectors on one dim-2 vertex tensor, edge
@@ -369,6 +392,7 @@ ALL_GRAPHS = {
     "spring_mass": spring_mass_graph,
     "rusanov": rusanov_graph,
     "swe_delta": swe_delta_graph,
+    "swe_boundary": swe_boundary_graph,
     "mixed_dims": mixed_dims_graph,
     "ops_zoo": ops_zoo_graph,
     "edge_sum": edge_sum_graph,
@@ -381,6 +405,7 @@ GRAPH_DTYPES = {
     "spring_mass": ("float32", "float64"),
     "rusanov": ("float64", "float32"),
     "swe_delta": ("float64", "float32"),
+    "swe_boundary": ("float64", "float32"),
     "mixed_dims": ("float32", "float64", "int64"),
     "ops_zoo": ("float32", "float64"),
     "edge_sum": ("float32", "float64", "int64"),

@@ -184,6 +184,30 @@ def swe_mesh(n: int = 1024, dtype=np.float64) -> Problem:
                    ro.astype(np.int32), cells, cells, {"grid": n})
 
 
+def swe_model_inputs(n: int = 64, dtype=np.float64) -> Dict[str, np.ndarray]:
+    """Every array the reference's ``ShallowWaterEquation`` module loads (shallow_water_equation/
+    swe_main.py:19-81) for the triangulated n x n square: interior edges (src, dst sorted by dst, alpha,
+    sx, sy) as in ``swe_mesh``; boundary cells ``bcells`` (sorted) with the summed outward face vector
+    (bsx, bsy) of their wall faces; cell ``area``; initial h, uh, vh."""
+    interior = swe_mesh(n, dtype)
+    base = shallow_water(n, np.float64)
+    nbr = base.indices["sel_nbr"].astype(np.int64)
+    own = base.indices["sel_self"].astype(np.int64)
+    wall = nbr == own
+    face = base.values["face"][wall]
+    cells = base.num_rows
+    bx = np.bincount(own[wall], weights=face[:, 0] * face[:, 2], minlength=cells)
+    by = np.bincount(own[wall], weights=face[:, 1] * face[:, 2], minlength=cells)
+    bcells = np.flatnonzero(np.bincount(own[wall], minlength=cells))
+    hs = 1.0 / n
+    d = dict(interior.values)
+    d.update({"src": interior.indices["gather_src"], "dst": interior.indices["gather_dst"],
+              "row_offsets": interior.row_offsets, "bcells": bcells.astype(np.int32),
+              "bsx": bx[bcells].astype(dtype), "bsy": by[bcells].astype(dtype),
+              "area": np.full(cells, 0.5 * hs * hs, dtype=dtype)})
+    return d
+
+
 # ----------------------------------------------------------------------------------------------
 # config 3: power-law CSR
 # ----------------------------------------------------------------------------------------------

@@ -98,6 +98,20 @@ int flexspmv_validate_csr(const void *d_row_offsets, int32_t offset_bits, int64_
                           int64_t num_edges, const int32_t *d_index, int64_t num_vertices,
                           int32_t *d_status, void *stream);
 
+/*
+ * One Runge-Kutta stage of the per-cell arithmetic of the reference's shallow-water model
+ * (shallow_water_equation/swe_main.py:100-146), which the reference leaves to torch element-wise
+ * kernels: with r = the three interior reducer sums and rb = the two boundary sums,
+ *   d_k   = -(r_k [+ rb_k]) / area                      (k = h, uh, vh; rb only for uh, vh)
+ *   acc_k = first ? d_k : acc_k + d_k
+ *   last  ? x_k += w * acc_k  :  stage_k = x_k + c * d_k
+ * d_r, d_x, d_acc, d_stage: 3 device pointers each; d_rb: 2; value_bytes 4 | 8; all arrays n long.
+ */
+int flexspmv_swe_rk_stage(int32_t value_bytes, const void *const *d_r, const void *const *d_rb,
+                          const void *d_area, void *const *d_x, void *const *d_acc,
+                          void *const *d_stage, double c, double w, int64_t n, int32_t first,
+                          int32_t last, void *stream);
+
 /* ---- per fused graph ---------------------------------------------------------------------------
  * One set of five symbols per (graph, value type); the per-edge map is compiled into the kernel, so
  * a graph is identified by its symbol prefix.  For graph G and value type T (f32 | f64 | i64):
@@ -158,6 +172,8 @@ FLEXSPMV_DECLARE_GRAPH(rusanov_f64)
 FLEXSPMV_DECLARE_GRAPH(rusanov_f32)
 FLEXSPMV_DECLARE_GRAPH(swe_delta_f64)
 FLEXSPMV_DECLARE_GRAPH(swe_delta_f32)
+FLEXSPMV_DECLARE_GRAPH(swe_boundary_f64)
+FLEXSPMV_DECLARE_GRAPH(swe_boundary_f32)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_f32)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_f64)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_i64)
