@@ -100,6 +100,32 @@ __global__ void validate_kernel(const OffsetT* __restrict__ row_offsets, long lo
   else if (bad_idx) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_ARG);
 }
 
+// Sorted COO row ids -> CSR row offsets with the leading 0: offsets[r] = number of ids < r (a lower bound
+// per row), plus the checks the conversion depends on: ids ascending (else BAD_CSR) and inside
+// [0, num_rows) (else BAD_ARG).
+template <typename IdT, typename OffsetT>
+__global__ void coo_rows_to_csr_kernel(const IdT* __restrict__ ids, long long num_edges, long long num_rows,
+                                       OffsetT* __restrict__ offsets, int* status) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long long r = i; r <= num_rows; r += stride) {
+    long long lo = 0, hi = num_edges;
+    while (lo < hi) {
+      const long long mid = (lo + hi) >> 1;
+      if ((long long)ids[mid] < r) lo = mid + 1; else hi = mid;
+    }
+    offsets[r] = (OffsetT)lo;
+  }
+  bool unsorted = false, out_of_range = false;
+  for (long long e = i; e < num_edges; e += stride) {
+    const long long v = (long long)ids[e];
+    out_of_range |= v < 0 || v >= num_rows;
+    if (e + 1 < num_edges) unsorted |= (long long)ids[e + 1] < v;
+  }
+  if (unsorted) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_CSR);
+  else if (out_of_range) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_ARG);
+}
+
 // One Runge-Kutta stage of the shallow-water model's per-cell arithmetic, fused: the reducers' sums
 // become the stage's increments d = -(r [+ r_boundary]) / area, the running sum of increments is
 // extended, and either the next stage's state x + c d or (last stage) the step x += w sum is written.
@@ -233,6 +259,30 @@ int flexspmv_validate_csr(const void* d_row_offsets, int32_t offset_bits, int64_
   else
     flex::validate_kernel<long long><<<(unsigned)grid, block, 0, st>>>(static_cast<const long long*>(d_row_offsets), num_rows,
                                                                        num_edges, d_index, num_vertices, d_status);
+  return (int)cudaGetLastError();
+}
+
+int flexspmv_coo_rows_to_csr(const void* d_row_ids, int32_t id_bits, int64_t num_edges, int64_t num_rows,
+                             void* d_row_offsets, int32_t offset_bits, int32_t* d_status, void* stream) {
+  if (!d_row_offsets || !d_status || num_edges < 0 || num_rows < 0 || (num_edges > 0 && !d_row_ids)) return FLEXSPMV_ERR_BAD_ARG;
+  if ((id_bits != 32 && id_bits != 64) || (offset_bits != 32 && offset_bits != 64)) return FLEXSPMV_ERR_BAD_ARG;
+  if (offset_bits == 32 && num_edges > 0x7fffffffLL) return FLEXSPMV_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(d_status, 0, sizeof(int32_t), st);
+  if (e != cudaSuccess) return (int)e;
+  const int block = 256;
+  const long long work = (num_rows + 1) > num_edges ? (num_rows + 1) : num_edges;
+  long long grid = (work + block - 1) / block;
+  if (grid > 148 * 16) grid = 148 * 16;
+  const unsigned g = (unsigned)grid;
+  if (id_bits == 32 && offset_bits == 32)
+    flex::coo_rows_to_csr_kernel<int, int><<<g, block, 0, st>>>(static_cast<const int*>(d_row_ids), num_edges, num_rows, static_cast<int*>(d_row_offsets), d_status);
+  else if (id_bits == 32)
+    flex::coo_rows_to_csr_kernel<int, long long><<<g, block, 0, st>>>(static_cast<const int*>(d_row_ids), num_edges, num_rows, static_cast<long long*>(d_row_offsets), d_status);
+  else if (offset_bits == 32)
+    flex::coo_rows_to_csr_kernel<long long, int><<<g, block, 0, st>>>(static_cast<const long long*>(d_row_ids), num_edges, num_rows, static_cast<int*>(d_row_offsets), d_status);
+  else
+    flex::coo_rows_to_csr_kernel<long long, long long><<<g, block, 0, st>>>(static_cast<const long long*>(d_row_ids), num_edges, num_rows, static_cast<long long*>(d_row_offsets), d_status);
   return (int)cudaGetLastError();
 }
 

@@ -23,12 +23,35 @@ import torch.nn as nn
 
 
 def coo_rows_to_csr_ptr(row_ids: torch.Tensor, num_rows: Optional[int] = None) -> torch.Tensor:
-    """Sorted COO row ids -> CSR offsets with the leading 0 (int64)."""
-    row_ids = row_ids.to(torch.int64)
+    """Sorted COO row ids -> CSR offsets with the leading 0 (int64).  CUDA ids are converted by the
+    library's ``flexspmv_coo_rows_to_csr`` (one launch, checks that the ids are ascending and in range);
+    ids on the host go through bincount + cumsum as in the reference (:20-41), with the same check."""
+    if row_ids.dtype not in (torch.int32, torch.int64):
+        row_ids = row_ids.to(torch.int64)
     if num_rows is None:
         if row_ids.numel() == 0:
             raise RuntimeError("row_ids is empty; cannot infer num_rows")
         num_rows = int(row_ids.max().item()) + 1
+    if row_ids.is_cuda:
+        import ctypes
+        from ..binding import check, load_library
+        lib = load_library()
+        ids = row_ids.contiguous()
+        crow = torch.empty(num_rows + 1, dtype=torch.int64, device=ids.device)
+        status = torch.empty(1, dtype=torch.int32, device=ids.device)
+        with torch.cuda.device(ids.device):
+            lib.flexspmv_coo_rows_to_csr.restype = ctypes.c_int
+            st = lib.flexspmv_coo_rows_to_csr(ctypes.c_void_p(ids.data_ptr()), 64 if ids.dtype == torch.int64 else 32,
+                                              ctypes.c_int64(ids.numel()), ctypes.c_int64(num_rows),
+                                              ctypes.c_void_p(crow.data_ptr()), 64, ctypes.c_void_p(status.data_ptr()),
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        check(lib, st, "coo_rows_to_csr")
+        code = int(status.item())
+        if code == -5:      # FLEXSPMV_ERR_BAD_CSR
+            raise ValueError("Reducer row ids must be sorted ascending (edges stored CSR-by-row)")
+        check(lib, code, "coo_rows_to_csr")
+        return crow
+    row_ids = row_ids.to(torch.int64)
     if row_ids.numel() > 1 and bool((row_ids[1:] < row_ids[:-1]).any()):
         raise ValueError("Reducer row ids must be sorted ascending (edges stored CSR-by-row)")
     counts = torch.bincount(row_ids, minlength=num_rows)

@@ -99,6 +99,17 @@ int flexspmv_validate_csr(const void *d_row_offsets, int32_t offset_bits, int64_
                           int32_t *d_status, void *stream);
 
 /*
+ * Sorted COO row ids (the Reducer's index, int32 or int64) -> CSR row offsets with the leading 0
+ * (num_rows + 1 entries, int32 or int64): what _coo_rows_to_csr_ptr computes with bincount + cumsum
+ * (python_wrapper/dynamic_replace_submodule.py:20-41), on the device in one launch.  Unlike the
+ * reference it checks its precondition: *d_status (device int32) becomes FLEXSPMV_ERR_BAD_CSR when
+ * the ids are not ascending, FLEXSPMV_ERR_BAD_ARG when one lies outside [0, num_rows), else 0.
+ */
+int flexspmv_coo_rows_to_csr(const void *d_row_ids, int32_t id_bits, int64_t num_edges,
+                             int64_t num_rows, void *d_row_offsets, int32_t offset_bits,
+                             int32_t *d_status, void *stream);
+
+/*
  * One Runge-Kutta stage of the per-cell arithmetic of the reference's shallow-water model
  * (shallow_water_equation/swe_main.py:100-146), which the reference leaves to torch element-wise
  * kernels: with r = the three interior reducer sums and rb = the two boundary sums,

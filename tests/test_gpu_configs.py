@@ -22,6 +22,8 @@ pytestmark = pytest.mark.gpu
     ("config0 poisson2d 128", lambda: ("spmv", problems.poisson2d(128))),
     ("config0 poisson2d 512 (full size)", lambda: ("spmv", problems.poisson2d(512))),
     ("config1 spring-mass 160", lambda: ("spring_mass", problems.spring_mass(160))),
+    ("config1 spring-mass 1024 (full size)", lambda: ("spring_mass", problems.spring_mass(1024))),
+    ("config2 shallow-water 1024 (full size)", lambda: ("rusanov", problems.shallow_water(1024))),
     ("config2 shallow-water 96", lambda: ("rusanov", problems.shallow_water(96))),
     ("reference shallow-water model, fused delta graph, mesh 96", lambda: ("swe_delta", problems.swe_mesh(96))),
     ("config3 power-law 2^16", lambda: ("spmv", problems.powerlaw(1 << 16, cap=20000))),

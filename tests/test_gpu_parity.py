@@ -175,3 +175,21 @@ def test_c_abi_edge_cases_empty_matrices():
     torch.cuda.synchronize()
     assert float(y.min()) == 7.0
     assert ext.device_status(torch.float64) == 0
+
+
+def test_coo_rows_to_csr_bit_exact_and_checked():
+    """Device COO -> CSR offsets against numpy (int32 and int64 ids, empty rows, empty input); unsorted ids
+    and ids outside [0, rows) are reported, not silently mis-converted."""
+    from flexspmv_b200.python_wrapper.dynamic_replace_submodule import coo_rows_to_csr_ptr
+    rng = np.random.default_rng(4)
+    for rows, edges in [(1, 1), (1000, 0), (5000, 123457), (17, 100000), (300000, 4000)]:
+        ids = np.sort(rng.integers(0, rows, edges))
+        want = np.searchsorted(ids, np.arange(rows + 1), side="left").astype(np.int64)
+        for dt in (np.int32, np.int64):
+            got = coo_rows_to_csr_ptr(torch.from_numpy(ids.astype(dt)).cuda(), rows)
+            assert got.dtype == torch.int64 and np.array_equal(got.cpu().numpy(), want)
+    bad = torch.tensor([0, 2, 1, 3], dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError):
+        coo_rows_to_csr_ptr(bad, 4)
+    with pytest.raises(RuntimeError):
+        coo_rows_to_csr_ptr(torch.tensor([0, 1, 9], dtype=torch.int64, device="cuda"), 4)
