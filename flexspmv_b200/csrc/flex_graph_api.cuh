@@ -108,15 +108,25 @@ struct GraphApi {
     static_assert(L::kTotal <= 227 * 1024, "tile kernel needs more shared memory than one sm_100a CTA can have");
     auto kernel = flex_tile_kernel<G, OffsetT, Cfg>;
     constexpr int kThreads = Cfg::kBlock + (G::kDirectLoads ? 0 : 32);   // staged mode adds the producer warp
-    static int resident = 0;
-    static std::once_flag once;
-    static cudaError_t init_err = cudaSuccess;
-    std::call_once(once, [&] {
-      init_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-      if (init_err == cudaSuccess)
-        init_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kThreads, L::kTotal);
-    });
-    if (init_err != cudaSuccess) { (void)cudaGetLastError(); return (int)init_err; }
+    // the shared-memory opt-in and the occupancy are per device: looked up once for each device of the process
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int resident_of[kMaxDevices] = {};      // 0: not initialised yet
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return FLEXSPMV_ERR_BAD_ARG;
+    int resident = 0;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      if (resident_of[dev] == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+        int r = 0;
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, kernel, kThreads, L::kTotal);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
+        resident_of[dev] = r < 1 ? -1 : r;
+      }
+      resident = resident_of[dev];
+    }
     if (resident < 1) return FLEXSPMV_ERR_TOO_LARGE;
     const long long tiles = h.num_tiles;
     if (tiles == 0) return 0;

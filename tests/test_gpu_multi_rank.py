@@ -81,3 +81,26 @@ def test_two_ranks_match_one_gpu(overlap, tmp_path):
     # blocks (and so the CTA boundaries) differ: agreement to the fp64 parity tolerance, not bit for bit
     scale = float(ref.abs().max())
     assert float((got - ref).abs().max()) <= 1e-12 * scale * iters
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_two_devices():
+    """The library's per-device state (shared-memory opt-in of the kernels, SM count, plan cache) must not be
+    tied to the first device a process used."""
+    from flexspmv_b200 import graphs, problems
+    from flexspmv_b200.binding import GraphExtension
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    prob = problems.random_problem(ir, 5000, 5000, 80000, seed=31, dtype=np.float64)
+    results = []
+    for d in (0, 1, 0):
+        dev = torch.device("cuda", d)
+        vals = torch.from_numpy(prob.values["vals"]).to(dev)
+        x = torch.from_numpy(prob.values["x"]).to(dev)
+        cols = torch.from_numpy(prob.indices["selector"]).to(dev)
+        ro = torch.from_numpy(prob.row_offsets).to(dev)
+        (y,) = ext.merged_spmv_launch(vals, x, cols, ro, prob.num_rows, prob.num_cols)
+        torch.cuda.synchronize(dev)
+        assert y.device == dev
+        results.append(y.cpu())
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
