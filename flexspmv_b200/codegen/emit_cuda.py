@@ -140,7 +140,9 @@ def _override(symbol: str):
 def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, static_scratch_bytes: int = 0) -> str:
     cty, sfx = CTYPE[dtype]
     symbol = symbol or f"{ir.name}_{sfx}"
-    block, ipt, stages, min_ctas = config or _override(symbol) or TUNED_CONFIGS.get(symbol) or choose_config(ir, dtype)
+    cfg = tuple(config or _override(symbol) or TUNED_CONFIGS.get(symbol) or choose_config(ir, dtype))
+    block, ipt, stages, min_ctas = cfg[:4]
+    pipeline = len(cfg) > 4 and bool(cfg[4])     # fifth field: software-pipelined tiles (TileCfg::kPipeline)
     non_gather, gathers, index_names = operator_signature(ir)
     value_names = non_gather + gathers
     in_dims = {i["name"]: dim_of(i["shape"]) for i in ir.inputs if i["dtype"] != "int"}
@@ -465,7 +467,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     per_edge_regs += len({s_["selector_name"] for s_ in ir.selector_register
                           if s_.get("selector") == 1 and not s_.get("row_identity")})
     batch = next((b_ for b_ in (8, 4, 3, 2) if b_ * max(per_edge_regs, 1) <= 28), 2)
-    w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}>;")
+    w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}, {'true' if pipeline else 'false'}>;")
     w("}  // namespace")
     w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg)")
     if static_scratch_bytes:

@@ -98,8 +98,8 @@ struct TileSmemLayout {
   // rows longer than kShortRowMax inside the current tile: [0..1] counters by tile parity, [2..] local rows
   static constexpr int kMaxLong = Cfg::kTile / (kShortRowMax + 1) + 2;
   static constexpr int kOffLong = int(align_up(kOffFlag + 16, 16));
-  static constexpr int kOffRel = int(align_up(kOffLong + 4 * (2 + kMaxLong), 16));
-  static constexpr int kBuffers = (!G::kGatherNeedsRow && Cfg::kPipeline) ? 2 : 1;   // s_rel / s_prod double-buffered when tiles are pipelined
+  static constexpr int kBuffers = (!G::kGatherNeedsRow && Cfg::kPipeline) ? 2 : 1;   // s_rel / s_prod / long-row list double-buffered when tiles are pipelined
+  static constexpr int kOffRel = int(align_up(kOffLong + 4 * (4 + kMaxLong * kBuffers), 16));
   static constexpr int kOffRowId = int(align_up(kOffRel + 4 * (Cfg::kTile + 1) * kBuffers, 16));
   static constexpr int kOffProd = int(align_up(kOffRowId + (G::kGatherNeedsRow ? 2 * Cfg::kTile : 0), 16));
   static constexpr int kOffStages = int(align_up(kOffProd + sizeof(V) * kAcc * Cfg::kTile * kBuffers, 128));
@@ -168,7 +168,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   V* s_carry = reinterpret_cast<V*>(smem + L::kOffCarry);
   int* s_flag = reinterpret_cast<int*>(smem + L::kOffFlag);
   int* s_nlong = reinterpret_cast<int*>(smem + L::kOffLong);
-  int* s_long = s_nlong + 2;
+  int* s_long = s_nlong + 4;
   int* s_rel = reinterpret_cast<int*>(smem + L::kOffRel);
   unsigned short* s_rowid = reinterpret_cast<unsigned short*>(smem + L::kOffRowId);
   V* s_prod = reinterpret_cast<V*>(smem + L::kOffProd);
@@ -255,7 +255,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     }
   }
   if (tid < 2 * kAcc) s_carry[tid] = V(0);
-  if (tid < 2) s_nlong[tid] = 0;
+  if (tid < 4) s_nlong[tid] = 0;
   __syncthreads();   // the only barrier that includes the producer warp
 
   // ---- producer warp: runs up to S tiles ahead of the consumers, off their critical path -----------
@@ -342,8 +342,10 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   };
   // Row ends as 32-bit edge indices relative to the tile, with a sentinel behind the last row.  Returns
   // whether this thread saw a long row (or a long trailing partial row).
-  // With list >= 0 the long rows are also appended (in any order) to s_long, counted in s_nlong[list].
-  auto convert = [&](const TileRef& t, const OffsetT* rend, int* srel, int list) -> bool {
+  // With list >= 0 the long rows are also appended (in any order) to buffer lbuf of s_long, counted in
+  // s_nlong[list].
+  auto convert = [&](const TileRef& t, const OffsetT* rend, int* srel, int list, int lbuf = 0) -> bool {
+    int* rows_long = s_long + lbuf * L::kMaxLong;
     bool my_long = false;
     for (int r = tid; r < t.nrows; r += BLOCK) {
       const long long end_r = (long long)rend[r];
@@ -351,7 +353,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       srel[r] = (int)(end_r - t.nz0);
       if ((end_r - beg_r) > kShortRowMax) {
         my_long = true;
-        if (list >= 0) s_long[atomicAdd(&s_nlong[list], 1)] = r;
+        if (list >= 0) rows_long[atomicAdd(&s_nlong[list], 1)] = r;
       }
     }
     if (tid == 0) {
@@ -359,7 +361,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       const long long beg_t = t.nrows ? (long long)rend[t.nrows - 1] : t.nz0;
       if ((t.nz0 + t.nnz - beg_t) > kShortRowMax) {
         my_long = true;
-        if (list >= 0) s_long[atomicAdd(&s_nlong[list], 1)] = t.nrows;
+        if (list >= 0) rows_long[atomicAdd(&s_nlong[list], 1)] = t.nrows;
       }
     }
     return my_long;
@@ -417,14 +419,15 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   //      (local row `nrows`) becomes the next carry ---------------------------------------------------------
   //      With list >= 0 the rows in s_long (longer than kShortRowMax) are left to whole warps: lanes sum
   //      strided, a shuffle tree combines them.
-  auto reduce_short = [&](const TileRef& t, int kpar, const V* sprod, const int* srel, int list) {
+  auto reduce_short = [&](const TileRef& t, int kpar, const V* sprod, const int* srel, int list, int lbuf = 0) {
+    const int* rows_long = s_long + lbuf * L::kMaxLong;
 #ifdef FLEX_EXP_SKIP_REDUCE
     return;
 #endif
     if (list >= 0) {
       const int n_long = s_nlong[list];
       for (int i = warp; i < n_long; i += Cfg::kWarps) {
-        const int r = s_long[i];
+        const int r = rows_long[i];
         const int lo = r ? srel[r - 1] : 0;
         const int hi = r < t.nrows ? srel[r] : t.nnz;
         V sum[kAcc];
@@ -638,7 +641,10 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         release(k);
         continue;
 #endif
-        my_long = convert(cur, rend, srel_k, -1);
+        // long-row counters rotate over three slots: k % 3 is filled now, (k - 1) % 3 is read by the reduction
+        // below, (k + 1) % 3 was last read before the barrier in acquire and is cleared for the next tile
+        if (tid == 0) s_nlong[(k + 1) % 3] = 0;
+        my_long = convert(cur, rend, srel_k, k % 3, k & 1);
         map_load(cur, tile, er);
         release(k);
         map_gather(cur, er, ge, gr);
@@ -646,16 +652,10 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       if (k > 0) {
         const int* srel_p = s_rel + ((k - 1) & 1) * (Cfg::kTile + 1);
         const V* sprod_p = s_prod + (size_t)((k - 1) & 1) * kAcc * Cfg::kTile;
-        if (!prev_long) {
-          reduce_short(prev, (k - 1) & 1, sprod_p, srel_p, -1);
-        } else {
-          int xs, ys, n_items;
-          thread_span(prev, srel_p, xs, ys, n_items);
-          reduce_long(prev, (k - 1) & 1, sprod_p, srel_p, xs, ys, n_items);
-        }
+        reduce_short(prev, (k - 1) & 1, sprod_p, srel_p, prev_long ? (k - 1) % 3 : -1, (k - 1) & 1);
       }
       if (have) map_products(cur, er, ge, gr, sprod_k);
-      prev_long = named_bar_or(1, BLOCK, my_long);   // [P] products + s_rel of tile k complete, tile classified
+      prev_long = named_bar_or(1, BLOCK, my_long);   // [P] products, s_rel and long-row list of tile k complete
       prev = cur;
     }
   } else {
