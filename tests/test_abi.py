@@ -71,3 +71,31 @@ def test_missing_library_fails_loudly(tmp_path):
     from flexspmv_b200.binding import FlexSpmvError, load_library
     with pytest.raises(FlexSpmvError):
         load_library(str(tmp_path / "nope.so"))
+
+
+def test_header_is_plain_c_and_links(tmp_path):
+    """include/flexspmv.h must be usable from a C translation unit (the drop-in boundary is a C ABI): a C99
+    program that includes it and calls a host-only entry point compiles with -pedantic, links against the
+    library and runs without a GPU."""
+    import shutil
+    import subprocess
+    from flexspmv_b200.binding import DEFAULT_LIB
+    gcc = shutil.which("gcc") or "/usr/bin/gcc"
+    src = tmp_path / "use_abi.c"
+    src.write_text(
+        '#include <stdio.h>\n#include "flexspmv.h"\n'
+        "int main(void) {\n"
+        "  flexspmv_desc d = {1000, 7000, 1000, 32, 0, 0, 0};\n"
+        "  size_t bytes = 0;\n"
+        "  flexspmv_graph_info gi;\n"
+        "  if (flexspmv_spmv_f64_info(&gi) != 0 || gi.has_reducer != 1) return 2;\n"
+        "  if (flexspmv_spmv_f64_workspace_bytes(&d, &bytes) != 0 || bytes == 0) return 3;\n"
+        '  printf("%d %zu %s\\n", flexspmv_abi_version(), bytes, flexspmv_error_string(FLEXSPMV_ERR_TIMEOUT));\n'
+        "  return 0;\n}\n")
+    exe = tmp_path / "use_abi"
+    lib_dir = os.path.dirname(DEFAULT_LIB)
+    inc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", inc, str(src), "-o", str(exe),
+                    "-L", lib_dir, "-lflexspmv_b200", f"-Wl,-rpath,{lib_dir}"], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert int(out[0]) >= 1 and int(out[1]) > 0
