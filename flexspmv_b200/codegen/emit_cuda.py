@@ -41,12 +41,16 @@ def stage_values(ir: GraphIR) -> bool:
     direct value load is a DRAM round trip inside the tile, longer than the L2-hit gather it travels with;
     for graphs that run fused, one thread per row (row-identity selectors: spring-mass, Rusanov), the direct
     loads win (33 % against 30 %), because the stage goes back to the producer only at the end of the tile and
-    a smaller stage is refilled sooner.  FLEXSPMV_STAGE_VALUES=0/1 overrides."""
+    a smaller stage is refilled sooner -- unless the graph reads three or more separate edge tensors per edge
+    (the shallow-water model's alpha, sx, sy: 38.8 % staged against 35.3 % direct), where one staged window per
+    tensor replaces three uncoalesced-per-thread loads.  FLEXSPMV_STAGE_VALUES=0/1 overrides."""
     import os
     env = os.environ.get("FLEXSPMV_STAGE_VALUES")
     if env in ("0", "1"):
         return env == "1"
-    return not any(s_.get("selector") == 1 and s_.get("row_identity") for s_ in ir.selector_register)
+    fused = any(s_.get("selector") == 1 and s_.get("row_identity") for s_ in ir.selector_register)
+    edge_tensors = {s_["target"] for s_ in ir.selector_register if s_.get("selector") != 1}
+    return (not fused) or len(edge_tensors) >= 3
 
 
 def _stream_bytes_per_edge(ir: GraphIR, vb: int) -> Tuple[int, int]:
@@ -115,19 +119,24 @@ def choose_config(ir: GraphIR, dtype: str) -> Tuple[int, int, int, int]:
 
 
 # Tile configurations measured on B200 for the built-in benchmark graphs (block, items per thread, stages,
-# min CTAs per SM); graphs not listed use the heuristic of choose_config.
+# min CTAs per SM[, pipelined tiles, edges per register batch of the fused row mode]); graphs not listed use the
+# heuristic of choose_config.  In the fused row mode one more resident CTA beats a wider register batch: the
+# other warps hide the gather latency better than more loads in flight per thread do.
 TUNED_CONFIGS = {
-    "spmv_f64": (256, 5, 2, 4),          # 7-point fp64 SpMV: 66-69 % of the HBM peak; 3 stages / bigger CTAs / 3 or 5 CTAs all lower
+    "spmv_f64": (256, 5, 2, 4),          # 7-point fp64 SpMV: 70 % of the HBM peak; 3 stages / bigger CTAs / 3 or 5 CTAs all lower
     "spmv_f32": (256, 5, 2, 4),
     "spmv_i64": (256, 5, 2, 4),
-    "spring_mass_f32": (256, 8, 2, 4),   # 35 %: 2048-item tiles hold ~228 rows of 8 edges, one per thread (5 items: 30 %)
-    "rusanov_f64": (256, 4, 2, 3),       # 29 %: 1024-item tiles hold 256 rows of 3 edges (3 items: 25 %, 5 items x 2 CTAs: 20 %)
+    # warm / L2-flushed % of the HBM peak:
+    "spring_mass_f32": (256, 8, 2, 4, 0, 2),   # 35.5 / 31.2: 2048-item tiles hold ~228 rows of 8 edges, one per thread (batch 4: 34.9 / 31.2, batch 1 x 5 CTAs: 36.1 / 29.2, batch 8: 25)
+    "rusanov_f64": (256, 4, 2, 3, 0, 1),       # 33.1 / 30.9: 1024-item tiles hold 256 rows of 3 edges (batch 2: 29.4 / 27.6, batch 3: 27.3 / 25.9, batch 1 x 4 CTAs: 30.3 / 28.7)
+    "swe_delta_f64": (256, 3, 2, 3, 0, 1),     # 52.7 / 45.3 with staged edge tensors ((256,4,2,3) batch 1: 48.7 / 39.8, direct: 35.3 / 32.2; heuristic (256,3,2,4) batch 2: 33.8 / 31.5)
 }
 
 
 def _override(symbol: str):
     """Tuning hook: FLEXSPMV_CFG_OVERRIDE="spmv_f64=256,7,2,3;rusanov_f64=128,5,3,4" replaces the
-    heuristic tile configuration (block, items per thread, stages, min CTAs per SM) at build time."""
+    heuristic tile configuration (block, items per thread, stages, min CTAs per SM[, pipelined tiles 0|1[, edges per
+    register batch of the fused row mode]]) at build time."""
     import os
     for part in os.environ.get("FLEXSPMV_CFG_OVERRIDE", "").split(";"):
         if "=" in part:
@@ -143,6 +152,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     cfg = tuple(config or _override(symbol) or TUNED_CONFIGS.get(symbol) or choose_config(ir, dtype))
     block, ipt, stages, min_ctas = cfg[:4]
     pipeline = len(cfg) > 4 and bool(cfg[4])     # fifth field: software-pipelined tiles (TileCfg::kPipeline)
+    batch_override = cfg[5] if len(cfg) > 5 else 0   # sixth field: edges per register batch in the fused row mode
     non_gather, gathers, index_names = operator_signature(ir)
     value_names = non_gather + gathers
     in_dims = {i["name"]: dim_of(i["shape"]) for i in ir.inputs if i["dtype"] != "int"}
@@ -467,6 +477,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     per_edge_regs += len({s_["selector_name"] for s_ in ir.selector_register
                           if s_.get("selector") == 1 and not s_.get("row_identity")})
     batch = next((b_ for b_ in (8, 4, 3, 2) if b_ * max(per_edge_regs, 1) <= 28), 2)
+    batch = batch_override or batch
     w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}, {'true' if pipeline else 'false'}>;")
     w("}  // namespace")
     w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg)")
