@@ -219,10 +219,14 @@ def single_gpu_configs(peak: float, only=None) -> list:
         ro = torch.from_numpy(np.ascontiguousarray(prob.row_offsets)).to(dev)
         return vals, idxs, ro
 
-    specs = [("config0 2D Poisson 512^2 fp64", "spmv", lambda: problems.poisson2d(512), 8, 200),
-             ("config1 spring-mass 1024^2 fp32", "spring_mass", lambda: problems.spring_mass(1024), 4, 200),
-             ("config2 shallow-water Rusanov 1024^2 fp64", "rusanov", lambda: problems.shallow_water(1024), 8, 200)]
-    for ci, (name, gname, make, vb, iters) in enumerate(specs):
+    # (id for --only-config, name, graph, inputs, value bytes, iterations); id 5 is not a BASELINE config: the fused
+    # `delta` graph of the reference's own shallow-water model on the config-2 mesh
+    specs = [(0, "config0 2D Poisson 512^2 fp64", "spmv", lambda: problems.poisson2d(512), 8, 200),
+             (1, "config1 spring-mass 1024^2 fp32", "spring_mass", lambda: problems.spring_mass(1024), 4, 200),
+             (2, "config2 shallow-water Rusanov 1024^2 fp64", "rusanov", lambda: problems.shallow_water(1024), 8, 200),
+             (5, "reference shallow-water model, fused delta graph, 1024^2 mesh fp64", "swe_delta",
+              lambda: problems.swe_mesh(1024), 8, 200)]
+    for ci, name, gname, make, vb, iters in specs:
         if only is not None and ci not in only:
             continue
         ir = graphs.ALL_GRAPHS[gname]()
@@ -474,7 +478,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table (N = 1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (N = 1)")
-    ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3],
+    ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3, 5],
                     help="run just this single-GPU configuration (kernel-only timings) and print its entry")
     ap.add_argument("--overlap", action="store_true", help="N > 1: split off the halo-reading rows and overlap the exchange with the interior launch")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: enqueue every step from Python instead of replaying a CUDA graph")
