@@ -1,12 +1,18 @@
 // Hand-written sm_100a kernel for fused graphs WITH a reduce-by-row: persistent CTAs walk contiguous
-// runs of merge-path tiles; each tile's row-end offsets, index arrays and per-edge tensors are staged
-// into shared memory by 1-D bulk async copies (TMA, mbarrier complete_tx) issued STAGES tiles ahead;
-// every thread owns IPT consecutive merge items, gathers its vertex data, evaluates the generated map
-// in registers, and the per-row partial sums are combined by a warp-shuffle segmented scan, a small
-// cross-warp fold and a carry that travels from tile to tile inside the CTA.  Rows that end inside a
-// tile are staged in shared memory and written once, coalesced; the only cross-CTA state is one
-// carry per CTA, folded in by the last CTA to finish (ticket counter), in CTA order.  No atomics on
-// the output, no pre-zeroed output, run-to-run deterministic.
+// runs of merge-path tiles; each tile's row-end offsets, index arrays and (two-phase graphs) per-edge
+// tensors are staged into shared memory by 1-D bulk async copies (TMA, mbarrier complete_tx) that a
+// producer warp issues STAGES tiles ahead.
+//   Two-phase graphs (plain SpMV and every graph whose map needs no per-row data): phase 1, lanes on
+//   consecutive edges -- each thread copies IPT edges from the stage to registers, hands the stage back,
+//   gathers, runs the generated map and writes the products to shared memory; phase 2, one thread per
+//   row sums its products and stores the row; rows longer than kShortRowMax are summed by whole warps.
+//   Row-mode graphs (a selector equals the row id: spring-mass, fluxes): in tiles without long rows one
+//   thread per row loads the row's own record once, gathers and maps its edges in register batches and
+//   stores the row; tiles with long rows record the row of every edge, run the two phases and combine
+//   the per-thread partial sums with a warp-shuffle segmented scan and a cross-warp fold.
+// The carry of a row that spans tiles travels inside the CTA in shared memory; the only cross-CTA state
+// is one carry per CTA, folded in by the last CTA to finish (ticket counter), in CTA order.  No atomics
+// on the output, no pre-zeroed output, run-to-run deterministic.
 //
 // Replaces (reference, paths inside the FlexSpmv project): SpmvKernel
 // include/merged_spmv_kernels.cuh:110-128 and AgentFlexSpmv::ConsumeTile / reduce<>
