@@ -108,9 +108,9 @@ def choose_config(ir: GraphIR, dtype: str) -> Tuple[int, int, int, int]:
     shared-memory carve-up still lets that many CTAs share the 228 KB of one SM."""
     block, stages = 256, 2
     for ctas in (4, 3, 2):
-        budget = (227 * 1024) // ctas - 1024
+        limit = (227 * 1024) // ctas - 1024
         for ipt in (5, 3):
-            if smem_bytes(ir, dtype, block, ipt, stages) <= budget:
+            if smem_bytes(ir, dtype, block, ipt, stages) <= limit:
                 return block, ipt, stages, ctas
     ipt = 1
     while block > 64 and smem_bytes(ir, dtype, block, ipt, stages) > 110 * 1024:

@@ -13,9 +13,9 @@ x86-64 host) behind a three-line ``extern "C"`` trampoline written here.  The re
 binding (merged_binding_cpu.cpp) is a thin shim over the same function and is not needed.
 
 No reference source text is copied into the repository: the generated header lives in a temporary
-directory and only the compiled object is kept.  Requires the reference tree (default
-/root/reference, override with FLEXSPMV_REFERENCE_DIR); when it is absent this script does nothing
-and the prebuilt objects already in oracle/_ref are used.
+directory and only the compiled object is kept.  Requires the reference tree (its location is REF_DIR
+below, FLEXSPMV_REFERENCE_DIR overrides it); when it is absent this script does nothing and the prebuilt
+objects already in oracle/_ref are used.
 """
 from __future__ import annotations
 
