@@ -184,3 +184,32 @@ def test_shallow_water_model_step_matches_model_oracle():
             got = mesh[name].cpu().numpy()
             scale = max(float(np.abs(want).max()), 1e-300)
             assert float(np.abs(got - want).max()) <= 1e-12 * scale, (name, use_graph)
+
+
+def test_more_than_two_to_the_31_nonzeros():
+    """A 688^3 7-point Laplacian has 2.27e9 non-zeros: edge positions no longer fit 32 bits (the reference's
+    OffsetT is int only).  Checked against the stencil applied with torch slicing."""
+    dev = torch.device("cuda:0")
+    if torch.cuda.get_device_properties(dev).total_memory < 120 * 2 ** 30:
+        pytest.skip("needs a 180 GB device")
+    n = 688
+    ro, cols, vals = multi_gpu.poisson3d_planes_device(n, 0, n, dev)
+    assert int(ro[-1]) > 2 ** 31 and ro.dtype == torch.int64
+    rows = n ** 3
+    x = torch.rand(rows, dtype=torch.float64, device=dev) * 2 - 1
+    ext = GraphExtension(graphs.spmv_graph())
+    y = _spmv(ext, vals, x, cols, ro, rows)
+    del vals, cols, ro
+    X = x.view(n, n, n)
+    ref = 6.0 * X
+    ref[1:] -= X[:-1]
+    ref[:-1] -= X[1:]
+    ref[:, 1:] -= X[:, :-1]
+    ref[:, :-1] -= X[:, 1:]
+    ref[:, :, 1:] -= X[:, :, :-1]
+    ref[:, :, :-1] -= X[:, :, 1:]
+    err = float((y.view(n, n, n) - ref).abs().max()) / 12.0
+    assert err <= 1e-12
+    assert ext.device_status(torch.float64) == 0
+    del x, y, ref, X
+    torch.cuda.empty_cache()
