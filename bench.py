@@ -239,6 +239,26 @@ def single_gpu_configs(peak: float, only=None) -> list:
         out.append(time_config(name, ir, GraphExtension(ir), vals, idxs, ro, outs, prob.num_rows, prob.nnz, prob.num_cols,
                                alg, iters, peak, flush))
         del vals, idxs, ro, outs
+    # ids 6, 7 (not BASELINE configs): the aggregator / map-only flavour (flex_edge_kernel) on 2^27 edges whose
+    # selector walks a 2^24-vertex tensor in order (8 edges per vertex): a per-edge product + global sum, fp32,
+    # and a gather written in place through an input pointer, fp64
+    E, NV = 1 << 27, 1 << 24
+    for ci, name, gname, dt, vb in ((6, "aggregator graph edge_sum (per-edge product + global sum), 2^27 edges fp32", "edge_sum", torch.float32, 4),
+                                    (7, "map-only graph edge_copy (gather written in place), 2^27 edges fp64", "edge_copy", torch.float64, 8)):
+        if only is not None and ci not in only:
+            continue
+        ir = graphs.ALL_GRAPHS[gname]()
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(60 + ci)
+        edge = torch.rand(E, 2, generator=gen, device=dev, dtype=dt)
+        vert = torch.rand(NV, 2, generator=gen, device=dev, dtype=dt)
+        sel = (torch.arange(E, device=dev, dtype=torch.int64) // (E // NV)).to(torch.int32)
+        dummy = torch.tensor([42], dtype=torch.int32, device=dev)
+        outs = [torch.empty(E, 2, device=dev, dtype=dt), torch.empty(2, device=dev, dtype=dt)] if gname == "edge_sum" else []
+        alg = problems.algorithmic_bytes(ir, 0, E, NV, vb, 4)
+        out.append(time_config(name, ir, GraphExtension(ir), [edge, vert], [sel], dummy, outs, 0, E, NV, alg, 20, peak, flush))
+        del edge, vert, sel, outs
+        torch.cuda.empty_cache()
     if only is not None and 3 not in only:
         return out
     # config 3 is generated on the device (268 M non-zeros)
@@ -478,7 +498,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table (N = 1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (N = 1)")
-    ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3, 5],
+    ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3, 5, 6, 7],
                     help="run just this single-GPU configuration (kernel-only timings) and print its entry")
     ap.add_argument("--overlap", action="store_true", help="N > 1: split off the halo-reading rows and overlap the exchange with the interior launch")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: enqueue every step from Python instead of replaying a CUDA graph")
