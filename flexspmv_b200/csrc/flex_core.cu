@@ -241,6 +241,30 @@ int flexspmv_row_blocks(const void* d_row_offsets, int32_t offset_bits, int64_t 
   return (int)cudaGetLastError();
 }
 
+int flexspmv_halo_plan(const int64_t* first_row, const int64_t* min_col, const int64_t* max_col, int32_t world,
+                       flexspmv_halo_plan_t* plans) {
+  if (!first_row || !min_col || !max_col || !plans || world < 1) return FLEXSPMV_ERR_BAD_ARG;
+  for (int r = 0; r < world; ++r) {
+    if (first_row[r + 1] < first_row[r]) return FLEXSPMV_ERR_BAD_ARG;
+    flexspmv_halo_plan_t& p = plans[r];
+    p.row_begin = first_row[r]; p.row_end = first_row[r + 1];
+    p.halo_lo = p.row_begin > min_col[r] ? p.row_begin - min_col[r] : 0;
+    p.halo_hi = max_col[r] + 1 > p.row_end ? max_col[r] + 1 - p.row_end : 0;
+    p.send_lo = p.send_hi = 0;
+  }
+  for (int r = 0; r < world; ++r) {
+    if (plans[r].halo_lo) {
+      if (r == 0 || plans[r].halo_lo > plans[r - 1].row_end - plans[r - 1].row_begin) return FLEXSPMV_ERR_TOO_LARGE;
+      plans[r - 1].send_hi = plans[r].halo_lo;
+    }
+    if (plans[r].halo_hi) {
+      if (r == world - 1 || plans[r].halo_hi > plans[r + 1].row_end - plans[r + 1].row_begin) return FLEXSPMV_ERR_TOO_LARGE;
+      plans[r + 1].send_lo = plans[r].halo_hi;
+    }
+  }
+  return 0;
+}
+
 int flexspmv_validate_csr(const void* d_row_offsets, int32_t offset_bits, int64_t num_rows, int64_t num_edges,
                           const int32_t* d_index, int64_t num_vertices, int32_t* d_status, void* stream) {
   if (!d_row_offsets || !d_status || num_rows < 0 || num_edges < 0) return FLEXSPMV_ERR_BAD_ARG;

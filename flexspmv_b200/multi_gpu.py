@@ -13,6 +13,7 @@ send/recv pairs per rank, no gather lists.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
@@ -25,7 +26,6 @@ def balanced_row_blocks(row_offsets: torch.Tensor, parts: int, snap: int = 1) ->
     ``flexspmv_row_blocks`` is used."""
     n = row_offsets.numel() - 1
     if row_offsets.is_cuda:
-        import ctypes
         from .binding import check, load_library
         lib = load_library()
         out = torch.empty(parts + 1, dtype=torch.int64, device=row_offsets.device)
@@ -77,26 +77,26 @@ class HaloPlan:
         return self.row_begin - self.halo_lo
 
 
+class _CHaloPlan(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int64) for n in ("row_begin", "row_end", "halo_lo", "halo_hi", "send_lo", "send_hi")]
+
+
 def make_halo_plans(first_row: List[int], min_col: List[int], max_col: List[int]) -> List[HaloPlan]:
     """first_row: world+1 block boundaries; min_col/max_col: smallest / largest global column
-    referenced by each block's rows (for an empty block pass row_begin / row_begin-1)."""
+    referenced by each block's rows (for an empty block pass row_begin / row_begin-1).  The integer logic
+    is the library's host-only ``flexspmv_halo_plan``."""
+    from .binding import check, load_library
     world = len(first_row) - 1
-    plans = []
-    for r in range(world):
-        rb, re = first_row[r], first_row[r + 1]
-        lo = max(0, rb - min_col[r])
-        hi = max(0, max_col[r] - re + 1)
-        plans.append(HaloPlan(r, world, rb, re, lo, hi, 0, 0))
-    for r in range(world):
-        if plans[r].halo_lo:
-            if r == 0 or plans[r].halo_lo > plans[r - 1].rows:
-                raise NotImplementedError("halo reaches beyond the neighbouring block (matrix is not banded enough)")
-            plans[r - 1].send_hi = plans[r].halo_lo
-        if plans[r].halo_hi:
-            if r == world - 1 or plans[r].halo_hi > plans[r + 1].rows:
-                raise NotImplementedError("halo reaches beyond the neighbouring block (matrix is not banded enough)")
-            plans[r + 1].send_lo = plans[r].halo_hi
-    return plans
+    lib = load_library()
+    arr = lambda v: (ctypes.c_int64 * len(v))(*[int(x) for x in v])
+    out = (_CHaloPlan * world)()
+    lib.flexspmv_halo_plan.restype = ctypes.c_int
+    st = lib.flexspmv_halo_plan(arr(first_row), arr(min_col), arr(max_col), ctypes.c_int32(world), out)
+    if st == -4:     # FLEXSPMV_ERR_TOO_LARGE
+        raise NotImplementedError("halo reaches beyond the neighbouring block (matrix is not banded enough)")
+    check(lib, st, "halo_plan")
+    return [HaloPlan(r, world, p.row_begin, p.row_end, p.halo_lo, p.halo_hi, p.send_lo, p.send_hi)
+            for r, p in enumerate(out)]
 
 
 def exchange_halos(x_local: torch.Tensor, plan: HaloPlan, group=None) -> None:

@@ -89,6 +89,24 @@ int flexspmv_row_blocks(const void *d_row_offsets, int32_t offset_bits, int64_t 
                         int32_t parts, int64_t snap, int64_t *d_first_row, void *stream);
 
 /*
+ * Halo plan of a 1-D row-block partition (host only, pure integers): given the world + 1 block
+ * boundaries and, per block, the smallest and largest global column its rows reference (for an empty
+ * block: row_begin and row_begin - 1), computes for every rank how many vector entries it needs from
+ * the block below / above (halo_lo / halo_hi) and how many of its own head / tail entries the
+ * neighbours need (send_lo / send_hi).  The local vector of a rank is laid out
+ * [halo_lo | owned rows | halo_hi]; global column - (row_begin - halo_lo) indexes it.
+ * FLEXSPMV_ERR_TOO_LARGE when a halo reaches beyond the neighbouring block (matrix not banded enough
+ * for a nearest-neighbour exchange).  No counterpart in the reference (it has no multi-GPU code).
+ */
+typedef struct flexspmv_halo_plan_t {
+  int64_t row_begin, row_end;
+  int64_t halo_lo, halo_hi;
+  int64_t send_lo, send_hi;
+} flexspmv_halo_plan_t;
+int flexspmv_halo_plan(const int64_t *first_row, const int64_t *min_col, const int64_t *max_col,
+                       int32_t world, flexspmv_halo_plan_t *plans);
+
+/*
  * Debug validator: checks on the device that row offsets start at 0, are non-decreasing and end at
  * num_edges, and (when d_index != NULL) that every index lies in [0, num_vertices).  Writes 0 or a
  * FLEXSPMV_ERR_* to the int32 *d_status (device).  No reference counterpart (the reference never
