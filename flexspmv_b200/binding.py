@@ -90,6 +90,7 @@ class _Symbols:
             f.restype = ctypes.c_int
             return f
         self.info, self.workspace_bytes, self.plan = fn("info"), fn("workspace_bytes"), fn("plan")
+        self.plan_windows = fn("plan_windows")
         self.launch, self.device_status = fn("launch"), fn("device_status")
         gi = GraphInfo()
         check(lib, self.info(ctypes.byref(gi)), f"{sym}_info")
@@ -103,8 +104,18 @@ class GraphExtension:
     PLAN_CACHE_ENTRIES = 8
 
     def __init__(self, ir: GraphIR, lib_path: Optional[str] = None, symbol_prefix: Optional[str] = None,
-                 tile_items: int = 0, max_ctas: int = 0):
+                 tile_items: int = 0, max_ctas: int = 0, gather_windows: Optional[bool] = None):
+        """``gather_windows``: plan column segments per tile so that the kernel gathers from shared memory
+        (include/flexspmv.h, FLEXSPMV_FLAG_GATHER_WINDOWS), for graphs that support it; None = off unless the
+        environment variable FLEXSPMV_GATHER_WINDOWS is 1.  Costs 2 bytes of workspace per edge and a longer
+        first call per matrix; results are bit-identical.  Measured on B200: faster on small stencil matrices
+        that are latency-bound (2-D Poisson 512^2: 14.4 us against 16.5 us per launch), slower on large ones
+        (3-D Poisson: 62 % against 71 % of the HBM peak -- the kernel is bound by shared-memory / L1 data-pipe
+        wavefronts there, and a gather from shared memory costs more of them than an L1-cached global gather)."""
         self.ir = ir
+        if gather_windows is None:
+            gather_windows = os.environ.get("FLEXSPMV_GATHER_WINDOWS", "0") == "1"
+        self.gather_windows = bool(gather_windows)
         self.lib = load_library(lib_path)
         self.prefix = symbol_prefix or ir.name
         self.tile_items, self.max_ctas = int(tile_items), int(max_ctas)
@@ -138,12 +149,26 @@ class GraphExtension:
             raise TypeError(f"merged_spmv_launch() got unexpected keyword arguments {sorted(extra)}")
         return vals
 
-    def _workspace(self, syms: _Symbols, desc: Desc, ro: Optional[torch.Tensor], device) -> Tuple[torch.Tensor, int]:
+    def _flags(self, syms: _Symbols) -> int:
+        return 1 if (self.gather_windows and (syms.graph_info.reserved & 1)) else 0
+
+    def _desc(self, syms: _Symbols, values, row_end_offsets, num_rows: int, num_edges: int, num_cols: int) -> Desc:
+        has_red = self.ir.has_reducer
+        flags = self._flags(syms)
+        if flags:      # the windows are bounded by the gathered array's length: take it from the tensor itself
+            num_cols = int(values[len(self.non_gather)].shape[0])
+        return Desc(num_rows if has_red else 0, num_edges, num_cols,
+                    64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
+                    self.tile_items, self.max_ctas, flags)
+
+    def _workspace(self, syms: _Symbols, desc: Desc, ro: Optional[torch.Tensor], device,
+                   indices: Sequence[torch.Tensor] = ()) -> Tuple[torch.Tensor, int]:
         # a workspace holds per-launch state (ticket, carries): launches that may overlap on the GPU must not
         # share one, so the plan is cached per stream as well as per matrix
         key = (id(syms), desc.num_rows, desc.num_edges, desc.offset_bits, desc.tile_items, desc.max_ctas,
                (ro.data_ptr(), ro._version) if ro is not None else None, device.index,
-               torch.cuda.current_stream(device).cuda_stream)
+               torch.cuda.current_stream(device).cuda_stream,
+               tuple((t.data_ptr(), t._version) for t in indices) if desc.reserved else None)
         hit = self._plans.get(key)
         if hit is not None:
             self._plans.move_to_end(key)
@@ -154,9 +179,14 @@ class GraphExtension:
         check(self.lib, syms.plan(ctypes.byref(desc), ctypes.c_void_p(ro.data_ptr() if ro is not None else 0),
                                   ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(nbytes.value), _stream_ptr()),
               "plan")
+        if desc.reserved:      # gather windows: the second planning step reads the index array
+            ip = (ctypes.c_void_p * max(len(indices), 1))(*[t.data_ptr() for t in indices])
+            check(self.lib, syms.plan_windows(ctypes.byref(desc), ip, ctypes.c_void_p(ws.data_ptr()),
+                                              ctypes.c_size_t(nbytes.value), _stream_ptr()), "plan_windows")
+            self.launches += 2
         self.launches += 2 if ro is not None else 1
         # keep the row-offset tensor alive so its address cannot be recycled under a cached plan
-        self._plans[key] = (ws, nbytes.value, ro)
+        self._plans[key] = (ws, nbytes.value, ro, tuple(indices) if desc.reserved else None)
         while len(self._plans) > self.PLAN_CACHE_ENTRIES:
             self._plans.popitem(last=False)
         return ws, nbytes.value
@@ -194,9 +224,7 @@ class GraphExtension:
             if row_end_offsets.numel() != num_rows + 1:
                 raise FlexSpmvError("row_end_offsets must have length num_rows + 1")
         device = dispatch.device
-        desc = Desc(num_rows if has_red else 0, ne, num_cols,
-                    64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
-                    self.tile_items, self.max_ctas, 0)
+        desc = self._desc(syms, values, row_end_offsets, num_rows, ne, num_cols)
         outputs: List[torch.Tensor] = []
         for o in self.ir.outputs:
             d = dim_of(o["shape"])
@@ -209,7 +237,7 @@ class GraphExtension:
                 shape = (ne,) if d == 1 else (ne, d)
             outputs.append(torch.empty(shape, dtype=dt, device=device))
         with torch.cuda.device(device):
-            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device)
+            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
             vp = (ctypes.c_void_p * max(nv, 1))(*[t.data_ptr() for t in values])
             ip = (ctypes.c_void_p * max(ni, 1))(*[t.data_ptr() for t in indices])
             op = (ctypes.c_void_p * max(len(outputs), 1))(*[t.data_ptr() for t in outputs])
@@ -234,11 +262,9 @@ class GraphExtension:
         syms = self.symbols(dt)
         has_red = self.ir.has_reducer
         device = values[0].device
-        desc = Desc(num_rows if has_red else 0, num_edges, num_cols,
-                    64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
-                    self.tile_items, self.max_ctas, 0)
+        desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols)
         with torch.cuda.device(device):
-            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device)
+            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
             vp = (ctypes.c_void_p * max(len(values), 1))(*[t.data_ptr() for t in values])
             ip = (ctypes.c_void_p * max(len(indices), 1))(*[t.data_ptr() for t in indices])
             op = (ctypes.c_void_p * max(len(outputs), 1))(*[t.data_ptr() for t in outputs])
@@ -260,11 +286,9 @@ class GraphExtension:
         syms = self.symbols(dt)
         has_red = self.ir.has_reducer
         device = values[0].device
-        desc = Desc(num_rows if has_red else 0, num_edges, num_cols,
-                    64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
-                    self.tile_items, self.max_ctas, 0)
+        desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols)
         with torch.cuda.device(device):
-            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device)
+            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
         return PreparedLaunch(self, syms, desc, list(values), list(indices), row_end_offsets if has_red else None,
                               list(outputs), ws, ws_bytes)
 

@@ -133,6 +133,11 @@ TUNED_CONFIGS = {
 }
 
 
+# Tile configurations of the gather-window variant (its stages also hold the window area).
+TUNED_WIN_CONFIGS = {
+}
+
+
 def _override(symbol: str):
     """Tuning hook: FLEXSPMV_CFG_OVERRIDE="spmv_f64=256,7,2,3;rusanov_f64=128,5,3,4" replaces the
     heuristic tile configuration (block, items per thread, stages, min CTAs per SM[, pipelined tiles 0|1[, edges per
@@ -153,6 +158,8 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     block, ipt, stages, min_ctas = cfg[:4]
     pipeline = len(cfg) > 4 and bool(cfg[4])     # fifth field: software-pipelined tiles (TileCfg::kPipeline)
     batch_override = cfg[5] if len(cfg) > 5 else 0   # sixth field: edges per register batch in the fused row mode
+    import os
+    win_bytes = int(os.environ.get("FLEXSPMV_WIN_BYTES", 1024 * VBYTES[dtype]))
     non_gather, gathers, index_names = operator_signature(ir)
     value_names = non_gather + gathers
     in_dims = {i["name"]: dim_of(i["shape"]) for i in ir.inputs if i["dtype"] != "int"}
@@ -316,6 +323,10 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     for n_ in idx_names:
         si = stream_of["idx:" + n_]
         w(f"    r.idx_{n_} = *t.template stream<{si}, int>(le);")
+    w("    load_edge_vals(p, t, le, e, r);")
+    w("  }")
+    w("  template <class Tile, class IdxT>")
+    w("  __device__ __forceinline__ static void load_edge_vals(const Params& p, const Tile& t, IdxT le, long long e, EReg& r) {")
     seen_e = set()
     for s_ in edge_regs_list:
         if s_["selector_name"] not in seen_e:
@@ -346,6 +357,25 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
         w(f"    g.{s_['name']} = fx::ldg_vec<V, {d}>(p.{s_['target']} + (long long)r.idx_{s_['selector_name']} * {d});")
     w("    (void)p; (void)r; (void)g;")
     w("  }")
+    # gather windows: a two-phase graph with exactly one index array and one gathered tensor whose record is a
+    # power of two bytes can take its gathers from segments of that tensor staged in shared memory
+    win_ok = has_reducer and not needs_row and staged_values and len(idx_names) == 1 and len(edge_sel) == 1 \
+        and not direct_loads(ir, dtype)
+    if win_ok:
+        gs = edge_sel[0]
+        rec = dim_of(gs["shape"]) * VBYTES[dtype]
+        win_ok = rec in (4, 8, 16, 32) and gs["target"] not in inplace_targets
+    w(f"  static constexpr bool kWindowGather = {'true' if win_ok else 'false'};")
+    if win_ok:
+        gs = edge_sel[0]
+        d = dim_of(gs["shape"])
+        w(f"  static constexpr int kIdxStream = {stream_of['idx:' + idx_names[0]]};")
+        w(f"  static constexpr int kGatherRecBytes = {d} * int(sizeof(V));")
+        w(f"  static constexpr int kWinBytes = {win_bytes};      // window area per stage")
+        w(f"  __host__ __device__ static const void* gather_base(const Params& p) {{ return p.{gs["target"]}; }}")
+        w("  __device__ __forceinline__ static void gather_edge_win(const unsigned char* xw, unsigned pos, GEdge& g) {")
+        w(f"    g.{gs['name']} = fx::ld_vec<V, {d}>(reinterpret_cast<const V*>(xw) + pos * {d});")
+        w("  }")
 
     # ---- map ----------------------------------------------------------------------------------------
     env: Dict[str, Var] = {}
@@ -479,8 +509,10 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     batch = next((b_ for b_ in (8, 4, 3, 2) if b_ * max(per_edge_regs, 1) <= 28), 2)
     batch = batch_override or batch
     w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}, {'true' if pipeline else 'false'}>;")
+    wb_, wi_, ws_, wm_ = tuple(_override(symbol + "_win") or TUNED_WIN_CONFIGS.get(symbol) or (block, ipt, stages, min_ctas))[:4]
+    w(f"using CfgWin = flex::TileCfg<{wb_}, {wi_}, {ws_}, {wm_}, {batch}, false>;   // the gather-window variant of the kernel")
     w("}  // namespace")
-    w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg)")
+    w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg, CfgWin)")
     if static_scratch_bytes:
         w(f"FLEXSPMV_DEFINE_STATIC_SCRATCH_LAUNCH({symbol}, Graph, Cfg, {int(static_scratch_bytes)})")
     return "\n".join(L) + "\n"

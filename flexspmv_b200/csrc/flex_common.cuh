@@ -39,10 +39,31 @@ struct WorkspaceHeader {
   uint64_t carry_val_offset;
   uint64_t total_bytes;
   uint32_t debug[8];       // where a bounded wait gave up: {tile, stage, ...}
-  char pad[256 - 4 * 4 - 3 * 8 - 2 * 4 - 4 * 8 - 8 * 4];
+  uint64_t win_table_offset;   // gather windows (0: not planned): per-tile segment table ...
+  uint64_t win_index_offset;   // ... and per-edge 16-bit positions inside the tile's window area
+  int32_t win_ready;           // 1 once the window plan has filled them
+  int32_t reserved0;
+  char pad[256 - 4 * 4 - 3 * 8 - 2 * 4 - 4 * 8 - 8 * 4 - 2 * 8 - 2 * 4];
 };
 static_assert(sizeof(WorkspaceHeader) == 256, "header is one 256-byte block");
 constexpr uint32_t kMagic = 0x464c5831u;  // "FLX1"
+
+// ---- gather windows ---------------------------------------------------------------------------------
+// On matrices whose tiles touch only a few contiguous column ranges (stencils, banded meshes) the plan can
+// record, per tile, up to kWinMaxSegs column segments that cover every column of the tile and, per edge, the
+// 16-bit position of its column inside the concatenation of those segments.  The tile kernel then stages the
+// segments of the gathered vector into shared memory with bulk copies (like every other stream) and gathers
+// from there, and it streams the 2-byte positions instead of the 4-byte column indices.
+// Table entry of one tile: ints [0] = number of segments (0: the tile keeps its global gathers),
+// [2 + 2j] = first column, [3 + 2j] = length of segment j.  In the window area segment j starts at the next
+// 16-byte boundary after segment j-1 plus `lead_j = (first_j * record_bytes) & 15` (its source is 16-byte
+// aligned that way when the gathered array is), so the layout is a function of the table entry alone.
+constexpr int kWinMaxSegs = 12;
+constexpr int kWinEntryInts = 28;          // 112 bytes per tile
+__host__ __device__ __forceinline__ uint32_t win_lead(int first, int rec_bytes) { return ((uint32_t)first * (uint32_t)rec_bytes) & 15u; }
+__host__ __device__ __forceinline__ uint32_t win_span(int first, int len, int rec_bytes) {
+  return (win_lead(first, rec_bytes) + (uint32_t)len * (uint32_t)rec_bytes + 15u) & ~15u;
+}
 
 __host__ __device__ constexpr uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 

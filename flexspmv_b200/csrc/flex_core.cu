@@ -55,6 +55,13 @@ int partition_launch(const void* d_row_offsets, int offset_bits, long long num_r
 __global__ void header_init_kernel(WorkspaceHeader* dst, const WorkspaceHeader h) {
   if (threadIdx.x == 0 && blockIdx.x == 0) *dst = h;
 }
+__global__ void window_ready_kernel(WorkspaceHeader* h) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) h->win_ready = 1;
+}
+int window_ready_launch(void* ws, cudaStream_t st) {
+  window_ready_kernel<<<1, 32, 0, st>>>(static_cast<WorkspaceHeader*>(ws));
+  return (int)cudaGetLastError();
+}
 int header_init_launch(void* ws, const WorkspaceHeader& h, cudaStream_t stream) {
   header_init_kernel<<<1, 32, 0, stream>>>(static_cast<WorkspaceHeader*>(ws), h);
   return (int)cudaGetLastError();
@@ -98,6 +105,130 @@ __global__ void validate_kernel(const OffsetT* __restrict__ row_offsets, long lo
     for (long long e = i; e < num_edges; e += stride) bad_idx |= (index[e] < 0) || ((long long)index[e] >= num_vertices);
   if (bad_csr) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_CSR);
   else if (bad_idx) atomicCAS(status, 0, FLEXSPMV_ERR_BAD_ARG);
+}
+
+// ---- gather-window plan (see flex_common.cuh) ----------------------------------------------------------
+// One CTA per tile (grid-stride).  Columns are bucketed by 16; the distinct buckets go into a small hash
+// table (a tile that touches more than kWinMaxBuckets of them keeps its global gathers: random columns
+// leave after the first pass), are rank-sorted, and runs of adjacent buckets become segments whose exact
+// column bounds come from a second pass over the edges.
+constexpr int kWinMaxBuckets = 160;
+constexpr int kWinHashSlots = 1024;
+template <typename OffsetT>
+__global__ void __launch_bounds__(256) window_plan_kernel(const OffsetT* __restrict__ coords, long long num_tiles,
+                                                          const int* __restrict__ idx, int rec_bytes, int win_bytes,
+                                                          int* __restrict__ table, unsigned short* __restrict__ local_idx) {
+  __shared__ int s_hash[kWinHashSlots];
+  __shared__ int s_bk[kWinMaxBuckets], s_sorted[kWinMaxBuckets];
+  __shared__ int s_cnt, s_nseg;
+  __shared__ int s_b0[kWinMaxSegs + 1], s_lo[kWinMaxSegs], s_hi[kWinMaxSegs], s_eoff[kWinMaxSegs];
+  const int tid = threadIdx.x;
+  for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const long long nz0 = (long long)coords[2 * t + 1], nz1 = (long long)coords[2 * t + 3];
+    const int n = (int)(nz1 - nz0);
+    for (int i = tid; i < kWinHashSlots; i += blockDim.x) s_hash[i] = -1;
+    if (tid == 0) { s_cnt = 0; s_nseg = 0; }
+    __syncthreads();
+    for (int e = tid; e < n; e += blockDim.x) {
+      const int b = idx[nz0 + e] >> 4;
+      unsigned h = ((unsigned)b * 2654435761u >> 20) & (kWinHashSlots - 1);
+      for (int probe = 0; probe < kWinHashSlots; ++probe) {
+        if (s_cnt > kWinMaxBuckets) break;                      // already known not to be windowable
+        const int old = atomicCAS(&s_hash[h], -1, b);
+        if (old == -1) {
+          const int pos = atomicAdd(&s_cnt, 1);
+          if (pos < kWinMaxBuckets) s_bk[pos] = b;
+          break;
+        }
+        if (old == b) break;
+        h = (h + 1) & (kWinHashSlots - 1);
+      }
+    }
+    __syncthreads();
+    const int nb = s_cnt;
+    bool ok = nb <= kWinMaxBuckets && n > 0;
+    if (ok) {
+      for (int i = tid; i < nb; i += blockDim.x) {              // rank sort of the distinct buckets
+        const int v = s_bk[i];
+        int rank = 0;
+        for (int j = 0; j < nb; ++j) rank += s_bk[j] < v;
+        s_sorted[rank] = v;
+      }
+    }
+    __syncthreads();
+    if (ok && tid == 0) {
+      int ns = 0;
+      for (int i = 0; i < nb; ++i) {
+        if (i == 0 || s_sorted[i] - s_sorted[i - 1] > 2) {      // a gap of more than one empty bucket starts a segment
+          if (ns < kWinMaxSegs) { s_b0[ns] = s_sorted[i]; s_lo[ns] = 0x7fffffff; s_hi[ns] = -1; }
+          ++ns;
+        }
+      }
+      s_nseg = ns;
+    }
+    __syncthreads();
+    const int ns = s_nseg;
+    ok = ok && ns <= kWinMaxSegs;
+    if (ok) {
+      for (int e = tid; e < n; e += blockDim.x) {
+        const int c = idx[nz0 + e], b = c >> 4;
+        int k = 0;
+        for (int j = 1; j < ns; ++j) k += s_b0[j] <= b;
+        atomicMin(&s_lo[k], c);
+        atomicMax(&s_hi[k], c);
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      unsigned off = 0;
+      if (ok) {
+        for (int k = 0; k < ns; ++k) {
+          const int len = s_hi[k] - s_lo[k] + 1;
+          s_eoff[k] = (int)((off + win_lead(s_lo[k], rec_bytes)) / (unsigned)rec_bytes);
+          off += win_span(s_lo[k], len, rec_bytes);
+        }
+        ok = off <= (unsigned)win_bytes && off / (unsigned)rec_bytes <= 65535u;
+      }
+      int* ent = table + t * kWinEntryInts;
+      ent[0] = ok ? ns : 0;
+      ent[1] = (int)off;
+      for (int k = 0; k < kWinMaxSegs; ++k) {
+        ent[2 + 2 * k] = (ok && k < ns) ? s_lo[k] : 0;
+        ent[3 + 2 * k] = (ok && k < ns) ? s_hi[k] - s_lo[k] + 1 : 0;
+      }
+      s_nseg = ok ? ns : 0;
+    }
+    __syncthreads();
+    const int ns2 = s_nseg;
+    for (int e = tid; e < n; e += blockDim.x) {
+      unsigned short pos = 0;
+      if (ns2 > 0) {
+        const int c = idx[nz0 + e], b = c >> 4;
+        int k = 0;
+        for (int j = 1; j < ns2; ++j) k += s_b0[j] <= b;
+        pos = (unsigned short)(s_eoff[k] + (c - s_lo[k]));
+      }
+      local_idx[nz0 + e] = pos;
+    }
+    __syncthreads();
+  }
+}
+
+int window_plan_launch(const void* d_coords, int offset_bits, long long num_tiles, const int* d_idx, int rec_bytes,
+                       int win_bytes, void* d_table, void* d_local_idx, cudaStream_t st) {
+  if (num_tiles <= 0) return 0;
+  long long grid = num_tiles;
+  const long long cap = (long long)device_sm_count() * 8;
+  if (grid > cap) grid = cap;
+  if (offset_bits == 64)
+    window_plan_kernel<long long><<<(unsigned)grid, 256, 0, st>>>(static_cast<const long long*>(d_coords), num_tiles, d_idx,
+                                                                  rec_bytes, win_bytes, static_cast<int*>(d_table),
+                                                                  static_cast<unsigned short*>(d_local_idx));
+  else
+    window_plan_kernel<int><<<(unsigned)grid, 256, 0, st>>>(static_cast<const int*>(d_coords), num_tiles, d_idx, rec_bytes,
+                                                            win_bytes, static_cast<int*>(d_table),
+                                                            static_cast<unsigned short*>(d_local_idx));
+  return (int)cudaGetLastError();
 }
 
 // Sorted COO row ids -> CSR row offsets with the leading 0: offsets[r] = number of ids < r (a lower bound

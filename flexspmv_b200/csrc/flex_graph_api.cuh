@@ -19,10 +19,13 @@ int partition_launch(const void* d_row_offsets, int offset_bits, long long num_r
                      int tile_items, void* d_coords, cudaStream_t stream);
 int device_sm_count();
 int header_init_launch(void* ws, const WorkspaceHeader& h, cudaStream_t stream);
+int window_plan_launch(const void* d_coords, int offset_bits, long long num_tiles, const int* d_idx, int rec_bytes,
+                       int win_bytes, void* d_table, void* d_local_idx, cudaStream_t st);
+int window_ready_launch(void* ws, cudaStream_t st);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <class G, class Cfg>
+template <class G, class Cfg, class CfgWin = Cfg>
 struct GraphApi {
   using V = typename G::V;
   static constexpr int kEdgeBlock = 256, kEdgeIpt = 4;
@@ -32,7 +35,14 @@ struct GraphApi {
   // on the shallow-water model graph: 40.7 % -> 48.7 % of the HBM peak).  One row less per tile avoids it.
   static constexpr int kDefaultTile = Cfg::kTile - (G::kHasReducer && G::kGatherNeedsRow ? Cfg::kIpt : 0);
 
+  // Gather windows are used when the graph supports them and the caller asked for them in the descriptor.
+  static bool use_win(const flexspmv_desc* d) {
+    if constexpr (G::kHasReducer) return G::kWindowGather && (d->reserved & FLEXSPMV_FLAG_GATHER_WINDOWS) != 0;
+    return false;
+  }
+  static int compiled_tile(const flexspmv_desc* d) { return use_win(d) ? CfgWin::kTile : Cfg::kTile; }
   static int tile_items(const flexspmv_desc* d) {
+    if (d->tile_items <= 0 && use_win(d)) return CfgWin::kTile;
     // the tile kernel's shared-memory carve-up is compiled for Cfg::kTile items; a smaller tile is
     // allowed (tests exercise odd sizes), a larger one is not
     if (d->tile_items <= 0) return kDefaultTile;
@@ -46,7 +56,7 @@ struct GraphApi {
     if (!d) return FLEXSPMV_ERR_BAD_ARG;
     if (d->num_rows < 0 || d->num_edges < 0) return FLEXSPMV_ERR_BAD_ARG;
     if (G::kHasReducer && d->offset_bits != 32 && d->offset_bits != 64) return FLEXSPMV_ERR_BAD_ARG;
-    if (G::kHasReducer && d->tile_items > Cfg::kTile) return FLEXSPMV_ERR_TOO_LARGE;
+    if (G::kHasReducer && d->tile_items > compiled_tile(d)) return FLEXSPMV_ERR_TOO_LARGE;
     if (G::kHasReducer && d->offset_bits == 32 && d->num_rows + d->num_edges >= (1ll << 31)) return FLEXSPMV_ERR_TOO_LARGE;
     return 0;
   }
@@ -63,6 +73,12 @@ struct GraphApi {
     h.carry_val_offset = align_up(h.carry_row_offset + (uint64_t)kMaxCtas * 8u, 256);
     const int width = G::kHasReducer ? G::kAccDim : (G::kAggDim > 0 ? G::kAggDim : 1);
     h.total_bytes = align_up(h.carry_val_offset + (uint64_t)kMaxCtas * width * sizeof(V), 256);
+    h.win_table_offset = h.win_index_offset = 0;
+    if (use_win(d)) {
+      h.win_table_offset = h.total_bytes;
+      h.win_index_offset = align_up(h.win_table_offset + (uint64_t)tiles * kWinEntryInts * 4u, 256);
+      h.total_bytes = align_up(h.win_index_offset + (uint64_t)d->num_edges * 2u, 256);
+    }
   }
 
   static int info(flexspmv_graph_info* o) {
@@ -73,7 +89,9 @@ struct GraphApi {
     o->stages = Cfg::kStages;
     o->smem_bytes = 0;
     if constexpr (G::kHasReducer) o->smem_bytes = TileSmemLayout<G, long long, Cfg>::kTotal;
-    o->acc_dim = G::kHasReducer ? G::kAccDim : G::kAggDim; o->reserved = 0;
+    o->acc_dim = G::kHasReducer ? G::kAccDim : G::kAggDim;
+    o->reserved = 0;
+    if constexpr (G::kHasReducer) o->reserved = G::kWindowGather ? 1 : 0;   // bit 0: the graph can use gather windows
     return 0;
   }
 
@@ -106,13 +124,13 @@ struct GraphApi {
     return 0;
   }
 
-  template <typename OffsetT>
+  template <typename OffsetT, class C = Cfg, bool WIN = false>
   static int launch_tiles(const flexspmv_desc* d, const typename G::Params& p, const void* row_offsets, void* ws,
                           const WorkspaceHeader& h, cudaStream_t st) {
-    using L = TileSmemLayout<G, OffsetT, Cfg>;
+    using L = TileSmemLayout<G, OffsetT, C, WIN>;
     static_assert(L::kTotal <= 227 * 1024, "tile kernel needs more shared memory than one sm_100a CTA can have");
-    auto kernel = flex_tile_kernel<G, OffsetT, Cfg>;
-    constexpr int kThreads = Cfg::kBlock + (G::kDirectLoads ? 0 : 32);   // staged mode adds the producer warp
+    auto kernel = flex_tile_kernel<G, OffsetT, C, WIN>;
+    constexpr int kThreads = C::kBlock + (G::kDirectLoads ? 0 : 32);   // staged mode adds the producer warp
     // the shared-memory opt-in and the occupancy are per device: looked up once for each device of the process
     constexpr int kMaxDevices = 64;
     static std::mutex mu;
@@ -144,8 +162,36 @@ struct GraphApi {
     a.carry_row = reinterpret_cast<long long*>(static_cast<char*>(ws) + h.carry_row_offset);
     a.carry_val = static_cast<char*>(ws) + h.carry_val_offset;
     a.num_rows = d->num_rows; a.num_edges = d->num_edges; a.num_tiles = tiles;
+    a.win_table = nullptr; a.win_index = nullptr; a.num_vertices = d->num_vertices;
+    if constexpr (WIN) {
+      if (d->num_vertices <= 0) return FLEXSPMV_ERR_BAD_ARG;
+      if (!aligned16(G::gather_base(p))) return FLEXSPMV_ERR_ALIGN;   // window sources are 16-byte aligned only then
+      a.win_table = reinterpret_cast<const int*>(static_cast<char*>(ws) + h.win_table_offset);
+      a.win_index = reinterpret_cast<const unsigned short*>(static_cast<char*>(ws) + h.win_index_offset);
+    }
     kernel<<<(unsigned)grid, kThreads, L::kTotal, st>>>(p, a);
     return (int)cudaGetLastError();
+  }
+
+  // Second planning step for descriptors with FLEXSPMV_FLAG_GATHER_WINDOWS (after plan, same workspace): reads the
+  // index array of the graph's one gather and fills the per-tile segment table and the per-edge positions.
+  // Until it has run, a launch treats every tile as having no windows.
+  static int plan_windows(const flexspmv_desc* d, const void* const* indices, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (int e = check_desc(d)) return e;
+    if (!use_win(d)) return 0;          // nothing to do for graphs / descriptors without windows
+    if constexpr (G::kHasReducer && G::kWindowGather) {
+      if (!ws) return FLEXSPMV_ERR_WORKSPACE;
+      if (!indices || !indices[0]) return FLEXSPMV_ERR_BAD_ARG;
+      WorkspaceHeader h{};
+      layout(d, h);
+      if (ws_bytes < h.total_bytes) return FLEXSPMV_ERR_WORKSPACE;
+      char* base = static_cast<char*>(ws);
+      if (int e = window_plan_launch(base + h.coords_offset, d->offset_bits, num_tiles(d), static_cast<const int*>(indices[0]),
+                                     G::kGatherRecBytes, G::kWinBytes, base + h.win_table_offset, base + h.win_index_offset, st))
+        return e;
+      return window_ready_launch(ws, st);
+    }
+    return 0;
   }
 
   static int launch(const flexspmv_desc* d, const void* const* values, const void* const* indices,
@@ -165,6 +211,12 @@ struct GraphApi {
     if constexpr (G::kHasReducer) {
       if (!row_offsets) return FLEXSPMV_ERR_BAD_ARG;
       if (!aligned16(row_offsets)) return FLEXSPMV_ERR_ALIGN;
+      if constexpr (G::kWindowGather) {
+        if (use_win(d)) {
+          if (d->offset_bits == 64) return launch_tiles<long long, CfgWin, true>(d, p, row_offsets, ws, h, st);
+          return launch_tiles<int, CfgWin, true>(d, p, row_offsets, ws, h, st);
+        }
+      }
       if (d->offset_bits == 64) return launch_tiles<long long>(d, p, row_offsets, ws, h, st);
       return launch_tiles<int>(d, p, row_offsets, ws, h, st);
     } else {
@@ -192,21 +244,24 @@ struct GraphApi {
 
 }  // namespace flex
 
-#define FLEXSPMV_DEFINE_GRAPH(SYM, GRAPH, CFG)                                                                  \
+#define FLEXSPMV_DEFINE_GRAPH(SYM, GRAPH, CFG, CFGWIN)                                                          \
   extern "C" {                                                                                                  \
-  int flexspmv_##SYM##_info(flexspmv_graph_info* info) { return flex::GraphApi<GRAPH, CFG>::info(info); }       \
+  int flexspmv_##SYM##_info(flexspmv_graph_info* info) { return flex::GraphApi<GRAPH, CFG, CFGWIN>::info(info); } \
   int flexspmv_##SYM##_workspace_bytes(const flexspmv_desc* d, size_t* b) {                                     \
-    return flex::GraphApi<GRAPH, CFG>::workspace_bytes(d, b);                                                   \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN>::workspace_bytes(d, b);                                           \
   }                                                                                                             \
   int flexspmv_##SYM##_plan(const flexspmv_desc* d, const void* ro, void* ws, size_t wb, void* st) {            \
-    return flex::GraphApi<GRAPH, CFG>::plan(d, ro, ws, wb, static_cast<cudaStream_t>(st));                      \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN>::plan(d, ro, ws, wb, static_cast<cudaStream_t>(st));              \
+  }                                                                                                             \
+  int flexspmv_##SYM##_plan_windows(const flexspmv_desc* d, const void* const* ix, void* ws, size_t wb, void* st) { \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN>::plan_windows(d, ix, ws, wb, static_cast<cudaStream_t>(st));      \
   }                                                                                                             \
   int flexspmv_##SYM##_launch(const flexspmv_desc* d, const void* const* v, const void* const* ix,              \
                               const void* ro, void* const* o, void* ws, size_t wb, void* st) {                  \
-    return flex::GraphApi<GRAPH, CFG>::launch(d, v, ix, ro, o, ws, wb, static_cast<cudaStream_t>(st));          \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN>::launch(d, v, ix, ro, o, ws, wb, static_cast<cudaStream_t>(st));  \
   }                                                                                                             \
   int flexspmv_##SYM##_device_status(const void* ws, int32_t* out, void* st) {                                  \
-    return flex::GraphApi<GRAPH, CFG>::device_status(ws, out, static_cast<cudaStream_t>(st));                   \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN>::device_status(ws, out, static_cast<cudaStream_t>(st));           \
   }                                                                                                             \
   }
 

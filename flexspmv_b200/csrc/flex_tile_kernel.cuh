@@ -79,18 +79,25 @@ struct DirectTile {
   }
 };
 
-template <class G, typename OffsetT, class Cfg>
+template <class G, bool WIN> struct WinBytesOf { static constexpr int value = 0; };
+template <class G> struct WinBytesOf<G, true> { static constexpr int value = G::kWinBytes; };
+
+template <class G, typename OffsetT, class Cfg, bool WIN = false>
 struct TileSmemLayout {
   using V = typename G::V;
   static constexpr int kAcc = G::kAccDim;
   static constexpr int kBytesPerEdge = G::kStreamBytesPerEdge;
   static constexpr int kPerItem = (int(sizeof(OffsetT)) > kBytesPerEdge) ? int(sizeof(OffsetT)) : kBytesPerEdge;
   // each staged window may grow by < 32 bytes from aligning both ends to 16
-  static constexpr int kStageBytes =
+  static constexpr int kStreamBytes =
       G::kDirectLoads ? 0 : int(align_up(uint64_t(Cfg::kTile) * kPerItem + 32u * (G::kNumStreams + 1) + 16, 128));
+  // gather windows (WIN): the segments of the gathered vector follow the streams in every stage
+  static constexpr int kWinBytes = int(align_up(uint64_t(WinBytesOf<G, WIN>::value), 128));
+  static constexpr int kStageBytes = kStreamBytes + kWinBytes;
   struct Ctl {
     long long row0, nz0;
     int nrows, nnz;
+    int win;            // the tile gathers from the window area and its index stream holds 16-bit positions
     uint32_t roff_off;
     uint32_t stream_off[G::kNumStreams > 0 ? G::kNumStreams : 1];
   };
@@ -121,6 +128,9 @@ struct TileKernelArgs {
   long long num_rows;
   long long num_edges;
   long long num_tiles;
+  const int* win_table;                // gather windows (WIN kernels): per-tile segment table,
+  const unsigned short* win_index;     // per-edge positions inside the window area,
+  long long num_vertices;              // rows of the gathered array
 };
 
 // One staged window: `count` elements of `eb` bytes starting at element `first` of an array of
@@ -132,7 +142,7 @@ struct Window {
   uint32_t lead;       // bytes between src and the first wanted element
   uint32_t span;       // smem bytes reserved (multiple of 16)
   const char* tail_src;
-  uint32_t tail_bytes; // multiple of 4
+  uint32_t tail_bytes; // multiple of the element size
 };
 __device__ __forceinline__ Window make_window(const void* gbase, uint32_t eb, long long first, long long count,
                                               long long total) {
@@ -154,11 +164,12 @@ __device__ __forceinline__ Window make_window(const void* gbase, uint32_t eb, lo
   return w;
 }
 
-template <class G, typename OffsetT, class Cfg>
+template <class G, typename OffsetT, class Cfg, bool WIN = false>
 __global__ void __launch_bounds__(Cfg::kBlock + (G::kDirectLoads ? 0 : 32), Cfg::kMinCtas)
 flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   using V = typename G::V;
-  using L = TileSmemLayout<G, OffsetT, Cfg>;
+  using L = TileSmemLayout<G, OffsetT, Cfg, WIN>;
+  static_assert(!WIN || (!G::kDirectLoads && !G::kGatherNeedsRow && !Cfg::kPipeline), "gather windows: staged two-phase loop only");
   using Ctl = typename L::Ctl;
   constexpr int kAcc = G::kAccDim;
   constexpr int NS = G::kNumStreams;
@@ -192,6 +203,9 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     return;
   }
 
+  const bool win_ready = WIN && a.header->win_ready == 1;   // until the window plan has run every tile gathers globally
+  (void)win_ready;
+
   // contiguous run of tiles of this CTA
   const long long q = a.num_tiles / gridDim.x, rem = a.num_tiles % gridDim.x;
   const long long t_begin = (long long)blockIdx.x * q + ((long long)blockIdx.x < rem ? blockIdx.x : rem);
@@ -201,34 +215,64 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   // Executed by the whole producer warp: lane i prepares window i (lane 0: row-end offsets, lane 1+I:
   // stream I), a shuffle prefix sum places the windows in the stage, lane 0 posts the byte count, then
   // every lane issues its own bulk copy.
-  auto issue = [&](long long row0, long long nz0, long long row1, long long nz1, int s) {
+  // Table entry of a tile's gather windows, one piece per lane: the segment count in every lane, segment j in
+  // lane 16 + j (read one tile ahead, like the coordinates).
+  struct WinEnt { int nseg, first, len; };
+  auto load_win_entry = [&](long long tile_id) -> WinEnt {
+    WinEnt e{0, 0, 0};
+    if constexpr (WIN) {
+      static_assert(NS + 1 <= 16 && kWinMaxSegs <= 16, "lanes 0..NS stage the streams, lanes 16.. the window segments");
+      if (win_ready) {
+        const int* ent = a.win_table + tile_id * kWinEntryInts;
+        e.nseg = ent[0];
+        if (lane >= 16 && lane - 16 < kWinMaxSegs) { e.first = ent[2 + 2 * (lane - 16)]; e.len = ent[3 + 2 * (lane - 16)]; }
+      }
+    }
+    (void)tile_id;
+    return e;
+  };
+  auto issue = [&](long long row0, long long nz0, long long row1, long long nz1, int s, const WinEnt& we) {
     unsigned char* dst = s_stage + (size_t)s * L::kStageBytes;
     Window w;
     w.src = nullptr; w.bulk_bytes = 0; w.lead = 0; w.span = 0; w.tail_src = nullptr; w.tail_bytes = 0;
+    const int nseg = we.nseg;
+    if constexpr (WIN) {
+      if (lane >= 16 && lane - 16 < nseg) w = make_window(G::gather_base(p), G::kGatherRecBytes, we.first, we.len, a.num_vertices);
+    }
     if (lane == 0) w = make_window(row_offsets, sizeof(OffsetT), row0 + 1, row1 - row0, a.num_rows + 1);
     static_for<NS>([&](auto I) {
-      if (lane == I.value + 1)
-        w = make_window(G::template stream_ptr<I.value>(p), G::template stream_bytes<I.value>(), nz0, nz1 - nz0, a.num_edges);
+      if (lane == I.value + 1) {
+        bool local = false;
+        if constexpr (WIN) local = (I.value == G::kIdxStream) && nseg > 0;
+        if (local) w = make_window(a.win_index, 2, nz0, nz1 - nz0, a.num_edges);
+        else w = make_window(G::template stream_ptr<I.value>(p), G::template stream_bytes<I.value>(), nz0, nz1 - nz0, a.num_edges);
+      }
     });
-    uint32_t off = w.span;   // exclusive prefix sum of the spans over lanes 0..NS
+    uint32_t off = w.span;   // exclusive prefix sum of the spans over lanes 0..NS (streams) and 16.. (segments)
 #pragma unroll
-    for (int d = 1; d <= NS; d <<= 1) {
+    for (int d = 1; d <= (WIN ? 8 : NS); d <<= 1) {
       const uint32_t t = __shfl_up_sync(0xffffffffu, off, d);
-      if (lane >= d) off += t;
+      if ((lane & 15) >= d) off += t;
     }
     off -= w.span;
+    if constexpr (WIN) { if (lane >= 16) off += L::kStreamBytes; }
     uint32_t total = w.bulk_bytes;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
     Ctl& c = ctls[s];
-    if (lane == 0) { c.row0 = row0; c.nz0 = nz0; c.nrows = (int)(row1 - row0); c.nnz = (int)(nz1 - nz0); c.roff_off = off + w.lead; }
+    if (lane == 0) { c.row0 = row0; c.nz0 = nz0; c.nrows = (int)(row1 - row0); c.nnz = (int)(nz1 - nz0); c.roff_off = off + w.lead; c.win = nseg > 0; }
     static_for<NS>([&](auto I) { if (lane == I.value + 1) c.stream_off[I.value] = off + w.lead; });
     // the ragged tail (last < 16 bytes of an array) is fetched with plain loads BEFORE the arrive below,
     // whose release (after the warp barrier) makes it and the control block visible to the consumers
     if (w.tail_bytes) {
       const uint32_t so = off + (uint32_t)(w.tail_src - w.src);
-      for (uint32_t b = 0; b < w.tail_bytes; b += 4)
-        *reinterpret_cast<uint32_t*>(dst + so + b) = *reinterpret_cast<const uint32_t*>(w.tail_src + b);
+      if (((uint32_t)reinterpret_cast<uintptr_t>(w.tail_src) | w.tail_bytes) & 3u) {   // 2-byte elements (window positions)
+        for (uint32_t b = 0; b < w.tail_bytes; b += 2)
+          *reinterpret_cast<uint16_t*>(dst + so + b) = *reinterpret_cast<const uint16_t*>(w.tail_src + b);
+      } else {
+        for (uint32_t b = 0; b < w.tail_bytes; b += 4)
+          *reinterpret_cast<uint32_t*>(dst + so + b) = *reinterpret_cast<const uint32_t*>(w.tail_src + b);
+      }
     }
     fence_proxy_async_smem();   // earlier generic accesses to this stage are ordered before the bulk copies
     __syncwarp();
@@ -272,16 +316,18 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       // coordinates are read one tile ahead, so their load latency overlaps the wait for a free stage
       long long c_row = count ? (long long)coords[2 * t_begin] : 0, c_nz = count ? (long long)coords[2 * t_begin + 1] : 0;
       long long n_row = count ? (long long)coords[2 * t_begin + 2] : 0, n_nz = count ? (long long)coords[2 * t_begin + 3] : 0;
+      WinEnt c_we = count ? load_win_entry(t_begin) : WinEnt{0, 0, 0};
       for (int k = 0; k < count; ++k) {
         const int s = k % S;
         long long nn_row = 0, nn_nz = 0;
         if (k + 1 < count) { nn_row = (long long)coords[2 * (t_begin + k + 2)]; nn_nz = (long long)coords[2 * (t_begin + k + 2) + 1]; }
+        const WinEnt n_we = (k + 1 < count) ? load_win_entry(t_begin + k + 1) : WinEnt{0, 0, 0};
         if (k >= S) {
           const bool ok = mbar_wait_bounded(&empty[s], (uint32_t)(k / S - 1) & 1u, kWaitPolls);
           if (!__all_sync(0xffffffffu, ok)) { pfail = true; break; }
         }
-        issue(c_row, c_nz, n_row, n_nz, s);
-        c_row = n_row; c_nz = n_nz; n_row = nn_row; n_nz = nn_nz;
+        issue(c_row, c_nz, n_row, n_nz, s, c_we);
+        c_row = n_row; c_nz = n_nz; n_row = nn_row; n_nz = nn_nz; c_we = n_we;
         issued = k + 1;
         if (k >= 1) prefetch_gathers(k - 1);   // tile k-1 has (almost certainly) landed: warm L1 for its gathers
       }
@@ -298,7 +344,8 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 
   // ---- consumers (threads 0 .. BLOCK-1); their barriers are the named barrier 1 ---------------------
   using TileT = std::conditional_t<DIRECT, DirectTile<G>, SmemTile<G>>;
-  struct TileRef { long long row0, nz0; int nrows, nnz; };
+  struct TileRef { long long row0, nz0; int nrows, nnz; int win; };
+  const unsigned char* xwin = nullptr;   // WIN: the current tile's window area
   bool failed = false;
   long long last_row1 = 0;
 
@@ -314,7 +361,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   // Makes tile k available: waits (bounded) for its stage, or takes its coordinates in direct mode.
   auto acquire = [&](int k, TileRef& t, TileT& tile, const OffsetT*& rend) -> bool {
     if constexpr (DIRECT) {
-      t.row0 = d_row; t.nz0 = d_nz; t.nrows = (int)(d_row1 - d_row); t.nnz = (int)(d_nz1 - d_nz);
+      t.row0 = d_row; t.nz0 = d_nz; t.nrows = (int)(d_row1 - d_row); t.nnz = (int)(d_nz1 - d_nz); t.win = 0;
       d_row = d_row1; d_nz = d_nz1;
       if (k + 1 < count) { d_row1 = (long long)coords[2 * (t_begin + k + 2)]; d_nz1 = (long long)coords[2 * (t_begin + k + 2) + 1]; }
       tile.p = &p; tile.nz0 = t.nz0;
@@ -332,8 +379,9 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         return false;
       }
       const Ctl& c = ctls[s];
-      t.row0 = c.row0; t.nz0 = c.nz0; t.nrows = c.nrows; t.nnz = c.nnz;
+      t.row0 = c.row0; t.nz0 = c.nz0; t.nrows = c.nrows; t.nnz = c.nnz; t.win = c.win;
       const unsigned char* stage = s_stage + (size_t)s * L::kStageBytes;
+      xwin = stage + L::kStreamBytes;
       rend = reinterpret_cast<const OffsetT*>(stage + c.roff_off);
       static_for<NS>([&](auto I) { tile.base[I.value] = reinterpret_cast<const char*>(stage + c.stream_off[I.value]); });
       return true;
@@ -417,6 +465,25 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 #pragma unroll
         for (int j = 0; j < kAcc; ++j) tprod[j * Cfg::kTile + i * BLOCK] = prod[j];
       }
+    }
+  };
+
+  // ---- phase 1 of a tile with gather windows: 16-bit positions instead of column indices, gathers from the
+  //      window area of the stage (so the stage goes back to the producer after the gathers, not before) ----
+  auto map_load_gather_win = [&](const TileRef& t, const TileT& tile, typename G::EReg (&er)[IPT], typename G::GEdge (&ge)[IPT]) {
+    if constexpr (WIN) {
+      auto ttile = tile;
+      ttile.advance(tid);
+      unsigned short pos[IPT];
+#pragma unroll
+      for (int i = 0; i < IPT; ++i)
+        if (i * BLOCK + tid < t.nnz) {
+          G::load_edge_vals(p, ttile, i * BLOCK, t.nz0 + (i * BLOCK + tid), er[i]);   // the index stream holds 16-bit positions here
+          pos[i] = reinterpret_cast<const unsigned short*>(tile.base[G::kIdxStream])[i * BLOCK + tid];
+        }
+#pragma unroll
+      for (int i = 0; i < IPT; ++i)
+        if (i * BLOCK + tid < t.nnz) G::gather_edge_win(xwin, pos[i], ge[i]);
     }
   };
 
@@ -593,7 +660,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   if constexpr (!G::kGatherNeedsRow && !Cfg::kPipeline) {
     // ---- plain loop: stage -> registers -> gathers -> products -> classify -> reduce --------------------
     for (int k = 0; k < count; ++k) {
-      TileRef t{0, 0, 0, 0};
+      TileRef t{0, 0, 0, 0, 0};
       TileT tile;
       const OffsetT* rend = nullptr;
       if (!acquire(k, t, tile, rend)) { failed = true; break; }
@@ -608,9 +675,14 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         typename G::EReg er[IPT];
         typename G::GEdge ge[IPT];
         typename G::GRow gr[1];
-        map_load(t, tile, er);
-        release(k);     // as early as possible: the refill latency of this stage is what bounds the kernel
-        map_gather(t, er, ge, gr);
+        if (WIN && t.win) {
+          map_load_gather_win(t, tile, er, ge);
+          release(k);
+        } else {
+          map_load(t, tile, er);
+          release(k);     // as early as possible: the refill latency of this stage is what bounds the kernel
+          map_gather(t, er, ge, gr);
+        }
         map_products(t, er, ge, gr, s_prod);
       }
       const bool long_tile = named_bar_or(1, BLOCK, my_long);   // [P] products, s_rel and the long-row list complete
@@ -627,11 +699,11 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   } else if constexpr (!G::kGatherNeedsRow) {
     // ---- software-pipelined loop: the gathers of tile k are in flight while tile k-1 is reduced.
     //      s_rel and s_prod are double-buffered by tile parity; one classifying barrier per tile. -------
-    TileRef prev{0, 0, 0, 0};
+    TileRef prev{0, 0, 0, 0, 0};
     bool prev_long = false;
     for (int k = 0; k <= count; ++k) {
       const bool have = k < count;
-      TileRef cur{0, 0, 0, 0};
+      TileRef cur{0, 0, 0, 0, 0};
       bool my_long = false;
       typename G::EReg er[IPT];
       typename G::GEdge ge[IPT];
@@ -667,7 +739,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   } else {
     // ---- the map needs per-row data (row-identity selectors) ---------------------------------------------
     for (int k = 0; k < count; ++k) {
-      TileRef t{0, 0, 0, 0};
+      TileRef t{0, 0, 0, 0, 0};
       TileT tile;
       const OffsetT* rend = nullptr;
       if (!acquire(k, t, tile, rend)) { failed = true; break; }

@@ -55,8 +55,22 @@ typedef struct flexspmv_desc {
   int32_t offset_bits;   /* 32 or 64: width of the row-offset entries                               */
   int32_t tile_items;    /* merge items (rows + edges) per tile; 0 = the graph's compiled default   */
   int32_t max_ctas;      /* cap on persistent CTAs; 0 = SM count x resident CTAs per SM             */
-  int32_t reserved;
+  int32_t reserved;      /* flags: 0 or FLEXSPMV_FLAG_GATHER_WINDOWS (field name kept from ABI 1)     */
 } flexspmv_desc;
+
+/*
+ * Gather windows (no reference counterpart; graphs whose flexspmv_graph_info.reserved has bit 0 set).
+ * With this flag in the descriptor -- the same descriptor for workspace_bytes, plan, plan_windows and
+ * launch -- the workspace also holds, per tile, up to 12 column segments that cover every column the
+ * tile gathers from and, per edge, the 16-bit position of its column in those segments (2 bytes per
+ * edge of extra workspace).  The kernel then stages the segments of the gathered array with bulk
+ * copies and gathers from shared memory, and it streams the positions instead of the 4-byte column
+ * indices.  Pays on stencil / banded matrices that are applied many times; tiles that touch too many
+ * separate column ranges (random columns) keep their global gathers.  The gathered array must be
+ * 16-byte aligned and num_vertices must be its number of rows.  Results are bit-identical to the
+ * plain path.
+ */
+#define FLEXSPMV_FLAG_GATHER_WINDOWS 1
 
 /* ---- library-wide ----------------------------------------------------------------------------- */
 
@@ -151,6 +165,9 @@ int flexspmv_swe_rk_stage(int32_t value_bytes, const void *const *d_r, const voi
  *   flexspmv_G_T_plan            partitions the problem into the workspace (cacheable while the row
  *                                offsets do not change; replaces the per-call search kernel,
  *                                include/merged_spmv.cuh:98-119)
+ *   flexspmv_G_T_plan_windows    second planning step of descriptors with FLEXSPMV_FLAG_GATHER_WINDOWS,
+ *                                after plan on the same workspace; takes the index arrays of launch.
+ *                                A no-op (returns 0) for other descriptors and graphs.
  *   flexspmv_G_T_launch          one fused pass (replaces SpmvKernel + AgentFlexSpmv::ConsumeTile,
  *                                include/merged_spmv_kernels.cuh:110-128,
  *                                cuda_template/reducer/merged_agent_spmv_template.cuh:350-445, and
@@ -185,6 +202,8 @@ typedef struct flexspmv_graph_info {
   int flexspmv_##G##_workspace_bytes(const flexspmv_desc *desc, size_t *bytes);                     \
   int flexspmv_##G##_plan(const flexspmv_desc *desc, const void *d_row_offsets, void *d_workspace,  \
                           size_t workspace_bytes, void *stream);                                    \
+  int flexspmv_##G##_plan_windows(const flexspmv_desc *desc, const void *const *indices,            \
+                                  void *d_workspace, size_t workspace_bytes, void *stream);         \
   int flexspmv_##G##_launch(const flexspmv_desc *desc, const void *const *values,                   \
                             const void *const *indices, const void *d_row_offsets,                  \
                             void *const *outputs, void *d_workspace, size_t workspace_bytes,        \

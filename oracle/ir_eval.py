@@ -95,6 +95,47 @@ def tile_coordinates(row_offsets: np.ndarray, tile_items: int) -> np.ndarray:
     return out
 
 
+def gather_window_plan(coords: np.ndarray, idx: np.ndarray, rec_bytes: int, win_bytes: int,
+                       max_segs: int = 12, max_buckets: int = 160):
+    """Restatement of the gather-window plan (this package's own format, no reference counterpart): per tile
+    the columns are bucketed by 16, runs of buckets with at most one empty bucket between them become
+    segments with exact column bounds, laid out consecutively at 16-byte boundaries (each shifted by
+    ``(first * rec_bytes) & 15``); a tile with more than ``max_buckets`` buckets, more than ``max_segs``
+    segments or more than ``win_bytes`` of window area gets none.  Returns (table (tiles, 2 + 2*max_segs) with
+    [count, bytes, first0, len0, ...], positions (nnz,) uint16)."""
+    tiles = coords.shape[0] - 1
+    table = np.zeros((tiles, 2 + 2 * max_segs), np.int64)
+    pos = np.zeros(idx.shape[0], np.uint16)
+    for t in range(tiles):
+        nz0, nz1 = int(coords[t, 1]), int(coords[t + 1, 1])
+        c = idx[nz0:nz1].astype(np.int64)
+        if c.size == 0:
+            continue
+        b = np.unique(c >> 4)
+        if b.size > max_buckets:
+            continue
+        heads = np.concatenate([[True], np.diff(b) > 2])
+        b0 = b[heads]
+        if b0.size > max_segs:
+            continue
+        k = np.searchsorted(b0, c >> 4, side="right") - 1
+        lo = np.array([c[k == j].min() for j in range(b0.size)])
+        hi = np.array([c[k == j].max() for j in range(b0.size)])
+        off, eoff = 0, []
+        for j in range(b0.size):
+            lead = (int(lo[j]) * rec_bytes) & 15
+            eoff.append((off + lead) // rec_bytes)
+            off += (lead + int(hi[j] - lo[j] + 1) * rec_bytes + 15) & ~15
+        table[t, 1] = off
+        if off > win_bytes or off // rec_bytes > 65535:
+            continue
+        table[t, 0] = b0.size
+        table[t, 2:2 + 2 * b0.size:2] = lo
+        table[t, 3:3 + 2 * b0.size:2] = hi - lo + 1
+        pos[nz0:nz1] = (np.array(eoff)[k] + (c - lo[k])).astype(np.uint16)
+    return table, pos
+
+
 def nnz_balanced_row_blocks(row_offsets: np.ndarray, parts: int, snap: int = 1) -> np.ndarray:
     ro = np.ascontiguousarray(row_offsets.astype(np.int64))
     out = np.empty(parts + 1, np.int64)

@@ -86,7 +86,7 @@ def test_classify_op_follows_the_reference_table():
 def test_generate_sources_from_ir(tmp_path):
     paths = merged_gen_gpu.generate_cuda_code_from_ir(graphs.spring_mass_graph(), ("float32",), str(tmp_path))
     text = open(paths[0]).read()
-    assert "FLEXSPMV_DEFINE_GRAPH(spring_mass_f32, Graph, Cfg)" in text and "kGatherNeedsRow = true" in text
+    assert "FLEXSPMV_DEFINE_GRAPH(spring_mass_f32, Graph, Cfg, CfgWin)" in text and "kGatherNeedsRow = true" in text
 
 
 def test_coo_rows_to_csr_ptr():

@@ -193,3 +193,70 @@ def test_coo_rows_to_csr_bit_exact_and_checked():
         coo_rows_to_csr_ptr(bad, 4)
     with pytest.raises(RuntimeError):
         coo_rows_to_csr_ptr(torch.tensor([0, 1, 9], dtype=torch.int64, device="cuda"), 4)
+
+
+@pytest.mark.parametrize("gname,dt", [("spmv", "float64"), ("spmv", "float32"), ("spmv", "int64"), ("ops_zoo", "float64")])
+def test_gather_windows_are_bit_identical_to_global_gathers(gname, dt):
+    """Banded matrices (every tile gets windows), random columns (no tile does), and a mix; int32 and int64
+    offsets; gathered arrays whose length is not a multiple of 16 bytes."""
+    ir = graphs.ALL_GRAPHS[gname]()
+    dtype = np.dtype(dt)
+    plain = GraphExtension(ir, gather_windows=False)
+    win = GraphExtension(ir, gather_windows=True)
+    assert win._flags(win.symbols(NP2T[dtype])) == 1
+    probs = []
+    if gname == "spmv":
+        for mk in (lambda: problems.poisson2d(97), lambda: problems.poisson3d(23), lambda: problems.poisson3d(31, offset_dtype=np.int32)):
+            p = mk()
+            p.values = {k: (v * 3).astype(dtype) if dtype.kind == "i" else v.astype(dtype) for k, v in p.values.items()}
+            probs.append(p)
+    rng = np.random.default_rng(17)
+    for nr, nnz, band in [(4001, 60000, 40), (4001, 60000, 0), (777, 30011, 3), (50, 20000, 0)]:
+        p = problems.random_problem(ir, nr, nr, nnz, seed=nr + nnz + band, dtype=dtype)
+        if band:       # columns within +-band of the row, plus a second band far away for every third edge
+            rows = np.repeat(np.arange(nr), np.diff(p.row_offsets))
+            off = rng.integers(-band, band + 1, nnz)
+            far = (np.arange(nnz) % 3 == 0) * (nr // 2)
+            key = next(iter(p.indices))
+            p.indices[key] = np.clip(rows + off + far, 0, nr - 1).astype(np.int32)
+        probs.append(p)
+    for p in probs:
+        a, _ = run_gpu(plain, ir, p, dtype)
+        b, _ = run_gpu(win, ir, p, dtype)
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y, equal_nan=True)
+    assert win.device_status(NP2T[dtype]) == 0
+
+
+def test_gather_window_plan_bit_exact():
+    """The per-tile segment table and the per-edge 16-bit positions against their numpy restatement."""
+    from flexspmv_b200.binding import Desc
+    lib = load_library()
+    for prob, bits in ((problems.poisson3d(23, offset_dtype=np.int32), 32), (problems.poisson3d(17), 64),
+                       (problems.random_problem(graphs.spmv_graph(), 300, 300, 9000, 5, np.float64), 32)):
+        ro = prob.row_offsets.astype(np.int32 if bits == 32 else np.int64)
+        cols = prob.indices["selector"]
+        desc = Desc(prob.num_rows, prob.nnz, prob.num_cols, bits, 0, 0, 1)
+        nbytes = ctypes.c_size_t()
+        for f in (lib.flexspmv_spmv_f64_workspace_bytes, lib.flexspmv_spmv_f64_plan, lib.flexspmv_spmv_f64_plan_windows):
+            f.restype = ctypes.c_int
+        assert lib.flexspmv_spmv_f64_workspace_bytes(ctypes.byref(desc), ctypes.byref(nbytes)) == 0
+        ws = torch.zeros(nbytes.value, dtype=torch.uint8, device="cuda")
+        ro_t, cols_t = torch.from_numpy(ro).cuda(), torch.from_numpy(cols).cuda()
+        assert lib.flexspmv_spmv_f64_plan(ctypes.byref(desc), ctypes.c_void_p(ro_t.data_ptr()), ctypes.c_void_p(ws.data_ptr()),
+                                          ctypes.c_size_t(nbytes.value), None) == 0
+        ip = (ctypes.c_void_p * 1)(cols_t.data_ptr())
+        assert lib.flexspmv_spmv_f64_plan_windows(ctypes.byref(desc), ip, ctypes.c_void_p(ws.data_ptr()),
+                                                  ctypes.c_size_t(nbytes.value), None) == 0
+        torch.cuda.synchronize()
+        raw = ws.cpu().numpy()
+        # workspace header: tile_items is the int32 at byte 40, the window table / index offsets the int64 at 112 / 120
+        tile_items = int(raw[:256].view(np.int32)[10])
+        coords = ir_eval.tile_coordinates(ro, tile_items)
+        tiles = coords.shape[0] - 1
+        t_off, i_off = (int(v) for v in raw[112:128].view(np.int64))
+        table = raw[t_off:t_off + tiles * 112].view(np.int32).reshape(tiles, 28)[:, :26]
+        pos = raw[i_off:i_off + 2 * prob.nnz].view(np.uint16)
+        want_table, want_pos = ir_eval.gather_window_plan(coords, cols, 8, 8192)
+        assert np.array_equal(table, want_table)
+        assert np.array_equal(pos, want_pos)
