@@ -94,7 +94,7 @@ struct TileSmemLayout {
   // gather windows (WIN): the segments of the gathered vector follow the streams in every stage
   static constexpr int kWinBytes = int(align_up(uint64_t(WinBytesOf<G, WIN>::value), 128));
   static constexpr int kStageBytes = kStreamBytes + kWinBytes;
-  struct Ctl {
+  struct alignas(16) Ctl {   // read by every consumer thread of every tile: whole 16-byte words (see acquire)
     long long row0, nz0;
     int nrows, nnz;
     int win;            // the tile gathers from the window area and its index stream holds 16-bit positions
@@ -378,7 +378,16 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         }
         return false;
       }
-      const Ctl& c = ctls[s];
+      // one 16-byte shared load per 16 bytes of the control block instead of one load per field: the kernel
+      // is bound by shared-memory wavefronts, and every thread of every tile reads this
+      Ctl c;
+      {
+        constexpr int kWords = int(sizeof(Ctl) / 16);
+        const int4* src = reinterpret_cast<const int4*>(&ctls[s]);
+        int4* dst16 = reinterpret_cast<int4*>(&c);
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) dst16[i] = src[i];
+      }
       t.row0 = c.row0; t.nz0 = c.nz0; t.nrows = c.nrows; t.nnz = c.nnz; t.win = c.win;
       const unsigned char* stage = s_stage + (size_t)s * L::kStageBytes;
       xwin = stage + L::kStreamBytes;
