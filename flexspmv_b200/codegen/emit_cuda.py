@@ -341,6 +341,18 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
                 w(f"    r.{s_['selector_name']} = fx::ldg_vec<V, {d_}>(p.{s_['target']} + e * {d_});")
     w("    (void)p; (void)t; (void)le; (void)e; (void)r;")
     w("  }")
+    # edge tensors that are NOT staged are read straight from global memory by the consumers; the producer warp
+    # prefetches the tile's part of them into L2 when it stages the tile, STAGES tiles ahead of their use
+    w("  __device__ __forceinline__ static void prefetch_direct(const Params& p, long long nz0, long long nz1, int lane) {")
+    seen_e = set()
+    for s_ in edge_regs_list:
+        if s_["selector_name"] not in seen_e and not staged_values:
+            seen_e.add(s_["selector_name"])
+            d_ = dim_of(s_["shape"])
+            w(f"    fx::prefetch_l2_range(p.{s_['target']} + nz0 * {d_}, p.{s_['target']} + nz1 * {d_}, lane);")
+    w("    (void)p; (void)nz0; (void)nz1; (void)lane;")
+    w("  }")
+    w(f"  static constexpr bool kHasDirectEdgeTensors = {'true' if (edge_regs_list and not staged_values) else 'false'};")
     # L1 prefetch of what gather_edge will read, issued by the producer warp one tile ahead
     w("  template <class Tile, class IdxT>")
     w("  __device__ __forceinline__ static void prefetch_edge(const Params& p, const Tile& t, IdxT le) {")

@@ -217,6 +217,12 @@ __device__ __forceinline__ void prefetch_l1(const V* p) {
   }
 }
 
+// L2 prefetch of the byte range [b, e) by one warp (one request per 128-byte line)
+__device__ __forceinline__ void prefetch_l2_range(const void* b, const void* e, int lane) {
+  const char* q = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(b) & ~(uintptr_t)127) + lane * 128;
+  for (; q < reinterpret_cast<const char*>(e); q += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
+}
+
 template <typename V, int D>
 __device__ __forceinline__ Vec<V, D> ld_vec(const V* p) {   // plain load (shared or global)
   Vec<V, D> r;

@@ -279,6 +279,9 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     if (lane == 0) mbar_expect_tx(&bars[s], total);
     __syncwarp();
     if (w.bulk_bytes) bulk_g2s(dst + off, w.src, w.bulk_bytes, &bars[s]);
+#ifdef FLEX_PREFETCH_DIRECT
+    if constexpr (G::kHasDirectEdgeTensors) G::prefetch_direct(p, nz0, nz1, lane);
+#endif
   };
 
   // Producer warp, one tile ahead of the consumers: once tile j's index arrays have landed in shared memory,
