@@ -68,7 +68,7 @@ typedef struct flexspmv_desc {
  * indices.  Pays on stencil / banded matrices that are applied many times; tiles that touch too many
  * separate column ranges (random columns) keep their global gathers.  The gathered array must be
  * 16-byte aligned and num_vertices must be its number of rows.  Results are bit-identical to the
- * plain path.
+ * plain path run with the same tile size and CTA count.
  */
 #define FLEXSPMV_FLAG_GATHER_WINDOWS 1
 

@@ -201,8 +201,10 @@ def test_gather_windows_are_bit_identical_to_global_gathers(gname, dt):
     offsets; gathered arrays whose length is not a multiple of 16 bytes."""
     ir = graphs.ALL_GRAPHS[gname]()
     dtype = np.dtype(dt)
-    plain = GraphExtension(ir, gather_windows=False)
-    win = GraphExtension(ir, gather_windows=True)
+    # same tile size and CTA count on both sides: which partial sums meet at a tile or CTA boundary is part of
+    # the rounding, and the two kernels have different numbers of resident CTAs
+    plain = GraphExtension(ir, gather_windows=False, max_ctas=296)
+    win = GraphExtension(ir, gather_windows=True, max_ctas=296)
     assert win._flags(win.symbols(NP2T[dtype])) == 1
     probs = []
     if gname == "spmv":
