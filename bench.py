@@ -34,6 +34,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "fused SpMV effective GB/s"
+DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.045
 UNIT = "GB/s"
 
 
@@ -459,13 +460,14 @@ def run_ours(args) -> None:
                             "launch_ms": ms_per_step, "algorithmic_bytes_per_launch": alg_bytes,
                             "tile": {"block": info.block_threads, "items_per_thread": info.items_per_thread,
                                      "stages": info.stages, "smem_bytes": info.smem_bytes}}
-        traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(traffic_file):
-            with open(traffic_file) as f:
-                t = json.load(f)
-            if "dram_bytes_per_algorithmic_byte" in t:
-                line["roofline"]["traffic"] = t["dram_bytes_per_algorithmic_byte"] * alg_bytes
-                line["roofline"]["traffic_source"] = t.get("source")
+        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on the 192^3 grid (761,757,704
+        # algorithmic bytes: 742.8 MB read + 53.4 MB written = 1.045 x; a later capture that ended before all of y
+        # was written back read 718.3 + 24.3 MB); traffic grows in proportion to the grid, so it is scaled to this
+        # launch by the algorithmic bytes
+        line["roofline"]["traffic"] = DRAM_BYTES_PER_ALGORITHMIC_BYTE * alg_bytes
+        line["roofline"]["traffic_source"] = ("ncu --set full, flex_tile_kernel<spmv_f64, int64 offsets>, 3D Poisson 192^3: "
+                                              "742.8 MB read + 53.4 MB written for 761.8 MB of algorithmic bytes, scaled by "
+                                              "algorithmic bytes (profiles/flex_tile_kernel_spmv_f64_poisson3d.md)")
         del op, ro, cols, vals, x0, xbuf
         torch.cuda.empty_cache()
         if not args.no_configs:
