@@ -55,6 +55,9 @@ int partition_launch(const void* d_row_offsets, int offset_bits, long long num_r
 __global__ void header_init_kernel(WorkspaceHeader* dst, const WorkspaceHeader h) {
   if (threadIdx.x == 0 && blockIdx.x == 0) *dst = h;
 }
+__global__ void debug_withhold_kernel(WorkspaceHeader* h, uint32_t first_tile_plus_one) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) h->debug[7] = first_tile_plus_one;
+}
 __global__ void window_ready_kernel(WorkspaceHeader* h) {
   if (threadIdx.x == 0 && blockIdx.x == 0) h->win_ready = 1;
 }
@@ -369,6 +372,13 @@ int flexspmv_row_blocks(const void* d_row_offsets, int32_t offset_bits, int64_t 
     flex::row_blocks_kernel<long long><<<grid, block, 0, st>>>(static_cast<const long long*>(d_row_offsets), num_rows, parts,
                                                                snap, reinterpret_cast<long long*>(d_first_row));
   flex::row_blocks_fix_kernel<<<1, 32, 0, st>>>(reinterpret_cast<long long*>(d_first_row), parts);
+  return (int)cudaGetLastError();
+}
+
+int flexspmv_debug_withhold_stage(void* d_workspace, uint32_t first_tile_plus_one, void* stream) {
+  if (!d_workspace) return FLEXSPMV_ERR_WORKSPACE;
+  flex::debug_withhold_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<flex::WorkspaceHeader*>(d_workspace),
+                                                                               first_tile_plus_one);
   return (int)cudaGetLastError();
 }
 

@@ -320,7 +320,11 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       long long c_row = count ? (long long)coords[2 * t_begin] : 0, c_nz = count ? (long long)coords[2 * t_begin + 1] : 0;
       long long n_row = count ? (long long)coords[2 * t_begin + 2] : 0, n_nz = count ? (long long)coords[2 * t_begin + 3] : 0;
       WinEnt c_we = count ? load_win_entry(t_begin) : WinEnt{0, 0, 0};
+      // testing aid (flexspmv_debug_withhold_stage): the stage of tile `withhold - 1` and of every later tile is
+      // never filled, so that the consumers' bounded wait runs out and the error path can be exercised
+      const unsigned long long withhold = a.header->debug[7];
       for (int k = 0; k < count; ++k) {
+        if (withhold && (unsigned long long)(t_begin + k) + 1ull >= withhold) break;
         const int s = k % S;
         long long nn_row = 0, nn_nz = 0;
         if (k + 1 < count) { nn_row = (long long)coords[2 * (t_begin + k + 2)]; nn_nz = (long long)coords[2 * (t_begin + k + 2) + 1]; }

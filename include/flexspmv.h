@@ -103,6 +103,15 @@ int flexspmv_row_blocks(const void *d_row_offsets, int32_t offset_bits, int64_t 
                         int32_t parts, int64_t snap, int64_t *d_first_row, void *stream);
 
 /*
+ * Testing aid for the bounded device-side waits: after this call, launches on the planned workspace never
+ * fill the stage of tile `first_tile_plus_one - 1` nor of any later tile (0 switches the aid off; plan
+ * resets it).  The consumers of such a tile wait for their bounded time (one second), the kernel sets
+ * FLEXSPMV_ERR_TIMEOUT in the workspace status (read it with *_device_status) and returns; rows of the
+ * withheld tiles are not written.  No reference counterpart (its kernels have no waits).
+ */
+int flexspmv_debug_withhold_stage(void *d_workspace, uint32_t first_tile_plus_one, void *stream);
+
+/*
  * Halo plan of a 1-D row-block partition (host only, pure integers): given the world + 1 block
  * boundaries and, per block, the smallest and largest global column its rows reference (for an empty
  * block: row_begin and row_begin - 1), computes for every rank how many vector entries it needs from

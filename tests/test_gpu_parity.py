@@ -262,3 +262,54 @@ def test_gather_window_plan_bit_exact():
         want_table, want_pos = ir_eval.gather_window_plan(coords, cols, 8, 8192)
         assert np.array_equal(table, want_table)
         assert np.array_equal(pos, want_pos)
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """A stage that is never filled (testing aid flexspmv_debug_withhold_stage) makes the consumers' one-second
+    wait run out: the launch returns, the workspace status says FLEXSPMV_ERR_TIMEOUT, rows of the tiles before
+    the withheld one are correct, and after a fresh plan the same workspace gives the full result again."""
+    from flexspmv_b200.binding import Desc
+    lib = load_library()
+    ir = graphs.spmv_graph()
+    prob = problems.random_problem(ir, 4000, 4000, 60000, seed=77, dtype=np.float64)
+    ref, _, sums = ir_eval.run_graph(ir, prob, np.float64, num_threads=4, want_abs_sums=True)
+    dev = torch.device("cuda:0")
+    vals, x = (torch.from_numpy(prob.values[k]).to(dev) for k in ("vals", "x"))
+    cols = torch.from_numpy(prob.indices["selector"]).to(dev)
+    ro = torch.from_numpy(prob.row_offsets).to(dev)
+    y = torch.full((prob.num_rows,), float("nan"), dtype=torch.float64, device=dev)
+    desc = Desc(prob.num_rows, prob.nnz, prob.num_cols, 32, 0, 0, 0)
+    nbytes = ctypes.c_size_t()
+    for name in ("workspace_bytes", "plan", "launch", "device_status"):
+        getattr(lib, f"flexspmv_spmv_f64_{name}").restype = ctypes.c_int
+    lib.flexspmv_debug_withhold_stage.restype = ctypes.c_int
+    assert lib.flexspmv_spmv_f64_workspace_bytes(ctypes.byref(desc), ctypes.byref(nbytes)) == 0
+    ws = torch.zeros(nbytes.value, dtype=torch.uint8, device=dev)
+    wsp, nb = ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(nbytes.value)
+    vp = (ctypes.c_void_p * 2)(vals.data_ptr(), x.data_ptr())
+    ip = (ctypes.c_void_p * 1)(cols.data_ptr())
+    op = (ctypes.c_void_p * 1)(y.data_ptr())
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def plan_and_launch(withhold):
+        assert lib.flexspmv_spmv_f64_plan(ctypes.byref(desc), ctypes.c_void_p(ro.data_ptr()), wsp, nb, None) == 0
+        if withhold:
+            assert lib.flexspmv_debug_withhold_stage(wsp, ctypes.c_uint32(withhold), None) == 0
+        assert lib.flexspmv_spmv_f64_launch(ctypes.byref(desc), vp, ip, ctypes.c_void_p(ro.data_ptr()), op, wsp, nb, None) == 0
+        assert lib.flexspmv_spmv_f64_device_status(wsp, ctypes.c_void_p(status.data_ptr()), None) == 0
+        torch.cuda.synchronize()
+        return int(status.item())
+
+    tile_items = 1280
+    tiles = (prob.num_rows + prob.nnz + tile_items - 1) // tile_items
+    assert tiles >= 20
+    first_withheld = 11                                   # 1-based: tiles 0..9 are staged, 10.. never
+    assert plan_and_launch(first_withheld) == -6          # FLEXSPMV_ERR_TIMEOUT
+    coords = ir_eval.tile_coordinates(prob.row_offsets, tile_items)
+    done_rows = int(coords[first_withheld - 1, 0])        # rows that end inside the staged tiles
+    got = y.cpu().numpy()
+    from parity import row_error
+    assert row_error(got[:done_rows], ref[0][:done_rows], sums[0][:done_rows]) <= 1e-12
+    y.fill_(float("nan"))
+    assert plan_and_launch(0) == 0                        # plan resets the status and the aid
+    assert row_error(y.cpu().numpy(), ref[0], sums[0]) <= 1e-12
