@@ -313,3 +313,16 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable():
     y.fill_(float("nan"))
     assert plan_and_launch(0) == 0                        # plan resets the status and the aid
     assert row_error(y.cpu().numpy(), ref[0], sums[0]) <= 1e-12
+
+
+def test_rows_spanning_every_cta():
+    """Two rows of 1.5 M edges each: every CTA contributes a carry to the same row and the last CTA folds
+    hundreds of them (exact for int64, tolerance for fp64)."""
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    for dt in (np.int64, np.float64):
+        prob = problems.random_problem(ir, 2, 5000, 3_000_000, seed=41, dtype=dt)
+        prob.row_offsets = np.array([0, 1_500_000, 3_000_000], dtype=np.int32)
+        ref, _, sums = ir_eval.run_graph(ir, prob, dt, num_threads=8, want_abs_sums=True)
+        got, _ = run_gpu(ext, ir, prob, dt)
+        assert_outputs_match(ir, got, ref, sums, np.dtype(dt), what=f"two long rows {np.dtype(dt).name}")
