@@ -211,10 +211,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   const long long t_begin = (long long)blockIdx.x * q + ((long long)blockIdx.x < rem ? blockIdx.x : rem);
   const int count = (int)(q + ((long long)blockIdx.x < rem ? 1 : 0));
 
-  // ---- producer: stage one tile (lane 0 of the producer warp) ---------------------------------------
-  // Executed by the whole producer warp: lane i prepares window i (lane 0: row-end offsets, lane 1+I:
-  // stream I), a shuffle prefix sum places the windows in the stage, lane 0 posts the byte count, then
-  // every lane issues its own bulk copy.
+  // ---- producer ------------------------------------------------------------------------------------------
   // Table entry of a tile's gather windows, one piece per lane: the segment count in every lane, segment j in
   // lane 16 + j (read one tile ahead, like the coordinates).
   struct WinEnt { int nseg, first, len; };
@@ -231,6 +228,9 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     (void)tile_id;
     return e;
   };
+  // Stages one tile; executed by the whole producer warp: lane i prepares window i (lane 0: row-end offsets,
+  // lane 1+I: stream I, lane 16+j: gather-window segment j), a shuffle prefix sum places the windows in the
+  // stage, lane 0 posts the byte count, then every lane issues its own bulk copy.
   auto issue = [&](long long row0, long long nz0, long long row1, long long nz1, int s, const WinEnt& we) {
     unsigned char* dst = s_stage + (size_t)s * L::kStageBytes;
     Window w;
