@@ -151,7 +151,22 @@ def _override(symbol: str):
     return None
 
 
+def _with_node_names(ir: GraphIR) -> GraphIR:
+    """torch.fx gives a placeholder the node name ``l`` and the target ``L`` for an argument called ``L``; the
+    tracer records both (edge-tensor registers carry the target, everything else the name).  The emitter works
+    on node names only, so edge-tensor registers are renamed here when the two differ."""
+    alias = {i["target"]: i["name"] for i in ir.inputs if i["dtype"] != "int" and i["target"] != i["name"]}
+    if not any(s.get("selector") != 1 and s["target"] in alias for s in ir.selector_register):
+        return ir
+    import copy
+    ir = copy.copy(ir)
+    ir.selector_register = [dict(s, target=alias.get(s["target"], s["target"])) if s.get("selector") != 1 else s
+                            for s in ir.selector_register]
+    return ir
+
+
 def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, static_scratch_bytes: int = 0) -> str:
+    ir = _with_node_names(ir)
     cty, sfx = CTYPE[dtype]
     symbol = symbol or f"{ir.name}_{sfx}"
     cfg = tuple(config or _override(symbol) or TUNED_CONFIGS.get(symbol) or choose_config(ir, dtype))
