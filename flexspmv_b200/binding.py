@@ -108,8 +108,9 @@ class GraphExtension:
         """``gather_windows``: plan column segments per tile so that the kernel gathers from shared memory
         (include/flexspmv.h, FLEXSPMV_FLAG_GATHER_WINDOWS), for graphs that support it; None = off unless the
         environment variable FLEXSPMV_GATHER_WINDOWS is 1.  Costs 2 bytes of workspace per edge and a longer
-        first call per matrix; results are bit-identical for equal tile size and CTA count.  Measured on B200: faster on small stencil matrices
-        that are latency-bound (2-D Poisson 512^2: 14.4 us against 16.5 us per launch), slower on large ones
+        first call per matrix; results are bit-identical for equal tile size and CTA count.  Measured on B200:
+        faster on small stencil matrices that are latency-bound (2-D Poisson 512^2: 14.4 us against 16.5 us per
+        launch), slower on large ones
         (3-D Poisson: 62 % against 71 % of the HBM peak -- the kernel is bound by shared-memory / L1 data-pipe
         wavefronts there, and a gather from shared memory costs more of them than an L1-cached global gather)."""
         self.ir = ir
