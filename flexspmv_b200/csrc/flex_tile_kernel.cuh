@@ -74,7 +74,7 @@ struct DirectTile {
   long long nz0;
   __device__ __forceinline__ void advance(int records) { nz0 += records; }
   template <int I, class T>
-  __device__ __forceinline__ const T* stream(int le) const {
+  __device__ __forceinline__ const T* stream(long long le) const {
     return reinterpret_cast<const T*>(G::template stream_ptr<I>(*p) + (size_t)(nz0 + le) * G::template stream_bytes<I>());
   }
 };
