@@ -34,8 +34,12 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "fused SpMV effective GB/s"
-DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.045
 UNIT = "GB/s"
+# DRAM traffic of the headline kernel: dram__bytes_read.sum + dram__bytes_write.sum of ONE ncu capture of
+# flex_tile_kernel<spmv_f64, int64 offsets> on the 192^3 grid (the full-size launch holds too much memory to capture
+# with more than one pass); traffic grows in proportion to the grid, so it is scaled to the benchmarked launch by the
+# algorithmic bytes.  Part of y is still in L2 when that capture ends, so the write figure is a lower bound.
+DRAM_CAPTURE = {"grid": 192, "read_bytes": 718.3e6, "write_bytes": 24.3e6, "algorithmic_bytes": 761_757_704}
 
 
 def load_peaks():
@@ -50,6 +54,15 @@ def poisson3d_bytes(n: int) -> tuple[int, int]:
     n3 = n ** 3
     nnz = 7 * n3 - 6 * n * n
     return 12 * nnz + 8 * (n3 + 1) + 16 * n3, nnz
+
+
+def workload_config(n: int) -> dict:
+    """The `config` object of the JSON line: the workload only, identical for the CUDA arm and the CPU reference arm
+    (what differs between the arms -- partition, halo exchange, offset width -- is reported under `run`)."""
+    alg, nnz = poisson3d_bytes(n)
+    return {"workload": f"config4: 3D Poisson {n}^3 7-point SpMV y = A x, fp64 values, int32 columns, {nnz} non-zeros, "
+                        f"{n ** 3} rows, one SpMV per step",
+            "algorithmic_bytes_per_step": alg, "l2": "inputs larger than L2 (matrix >= 1.8 GB per GPU)"}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -121,40 +134,76 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------------
 # CPU reference arm
 # --------------------------------------------------------------------------------------------------
-def cpu_reference(grid: int, steps: int, warmup: int, planes: int = 32) -> dict:
-    """The reference's generated CPU operator on a z-slab of the benchmark matrix, all host threads."""
-    from flexspmv_b200 import graphs, problems
-    from oracle import ref_run
+def host_threads() -> int:
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    threads = min(cores, 256)
-    planes = min(planes, grid - 2) if grid > 2 else grid
-    z0 = 1 if grid > 2 else 0
-    prob = problems.poisson3d(grid, z_begin=z0, z_end=z0 + planes, offset_dtype=np.int32)
-    shift = (z0 - 1) * grid * grid if z0 > 0 else 0
-    n2 = grid * grid
-    prob.indices["selector"] = (prob.indices["selector"].astype(np.int64) - shift).astype(np.int32)
-    prob.values["x"] = np.ascontiguousarray(prob.values["x"][shift:shift + (planes + 2) * n2])
-    prob.num_cols = prob.values["x"].shape[0]
-    ir = graphs.spmv_graph()
-    nnz = prob.nnz
-    alg = 12 * nnz + 8 * (prob.num_rows + 1) + 8 * prob.num_cols + 8 * prob.num_rows
-    if ref_run.available("spmv"):
-        kind = "reference"
-        call = ref_run.PreparedCall(ir, prob, np.float64, num_threads=threads)
+    return min(cores, 256)      # the reference's carry arrays are [256] (codegen/merged_gen_core.py:75-77)
+
+
+def time_cpu_operator(ir, prob, dtype, steps: int, warmup: int, copy_inputs: bool = True) -> dict:
+    """Times the reference's generated CPU operator (oracle/_ref) on all host threads; where the AVX2 object of
+    the graph exists and runs here, both objects are tried and the faster one is timed.  Falls back to the C/numpy
+    restatement (kind "port", one thread) when oracle/_ref did not travel.  Returns the outputs of the last call."""
+    from oracle import ref_run
+    threads = host_threads()
+    if ref_run.available(ir.name):
+        kind, best = "reference", None
+        for variant in ref_run.variants(ir.name):
+            call = ref_run.PreparedCall(ir, prob, dtype, num_threads=threads, variant=variant, copy_inputs=copy_inputs)
+            call.run()
+            t0 = time.perf_counter()
+            call.run()
+            dt1 = time.perf_counter() - t0
+            if best is None or dt1 < best[0]:
+                best = (dt1, variant, call)
+        _, variant, call = best
         run = call.run
-    else:   # oracle/_ref did not travel: time the C/numpy restatement instead
-        kind, threads = "port", 1
+    else:
+        kind, threads, variant = "port", 1, "restatement"
         from oracle import ir_eval
-        run = lambda: ir_eval.run_graph(ir, prob, np.float64, num_threads=1)   # noqa: E731
+        run = lambda: ir_eval.run_graph(ir, prob, dtype, num_threads=1)[0]   # noqa: E731
     for _ in range(warmup):
         run()
-    t0 = time.perf_counter()
+    times = []
+    outs = None
     for _ in range(steps):
-        run()
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    return {"value": alg / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
-            "sample": f"{planes} of {grid} z-planes of the {grid}^3 7-point Laplacian ({prob.num_rows} rows, {nnz} non-zeros), "
-                      f"{steps} calls after {warmup} warm-up, int32 offsets (the reference's only width)",
+        t0 = time.perf_counter()
+        outs = run()
+        times.append(time.perf_counter() - t0)
+    return {"seconds_median": float(np.median(times)), "seconds_mean": float(np.mean(times)), "cores": threads, "kind": kind,
+            "object": {"so": "portable x86-64 object", "so_x86_64_v3": "-march=x86-64-v3 object"}.get(variant, variant),
+            "outputs": outs, "steps": steps, "warmup": warmup}
+
+
+def cpu_reference(grid: int, steps: int, warmup: int, planes=None) -> dict:
+    """The reference's generated CPU operator (OmpMergeSystem<double,int> behind a C trampoline: no torch::zeros
+    per call, which favours the reference) on the benchmark matrix, all host threads.  planes=None: the whole
+    grid^3 matrix with int32 offsets (the reference's only width; 937,951,232 + 134,217,728 < 2^31 at 512^3);
+    a number: that many z-planes of it (the fallback when the host cannot hold the 13 GB matrix)."""
+    from flexspmv_b200 import graphs, problems
+    ir = graphs.spmv_graph()
+    whole = planes is None
+    if whole:
+        try:
+            prob = problems.poisson3d_chunked(grid, offset_dtype=np.int32)
+        except MemoryError:
+            whole, planes = False, min(128, grid)
+    if not whole:
+        planes = min(planes, grid - 2) if grid > 2 else grid
+        z0 = 1 if grid > 2 else 0
+        prob = problems.poisson3d(grid, z_begin=z0, z_end=z0 + planes, offset_dtype=np.int32)
+        shift = (z0 - 1) * grid * grid if z0 > 0 else 0
+        n2 = grid * grid
+        prob.indices["selector"] = (prob.indices["selector"].astype(np.int64) - shift).astype(np.int32)
+        prob.values["x"] = np.ascontiguousarray(prob.values["x"][shift:shift + (planes + 2) * n2])
+        prob.num_cols = prob.values["x"].shape[0]
+    nnz = prob.nnz
+    alg = 12 * nnz + 8 * (prob.num_rows + 1) + 8 * prob.num_cols + 8 * prob.num_rows
+    r = time_cpu_operator(ir, prob, np.float64, steps, warmup, copy_inputs=False)
+    dt = r["seconds_mean"]
+    what = f"the whole {grid}^3 7-point Laplacian" if whole else f"{planes} of {grid} z-planes of the {grid}^3 7-point Laplacian"
+    return {"value": alg / dt / 1e9, "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "whole_problem": whole,
+            "sample": f"{what} ({prob.num_rows} rows, {nnz} non-zeros), {steps} calls after {warmup} warm-up, int32 offsets "
+                      f"(the reference's only width), {r['object']}, called through a C trampoline (no per-call output allocation)",
             "ms_per_step": dt * 1e3, "edges_per_s": nnz / dt}
 
 
@@ -162,12 +211,15 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 50))
-    r = cpu_reference(args.grid, steps, max(1, min(args.warmup, 3)))
+    steps, warmup = max(1, args.steps), max(args.warmup, 3)      # exactly the K and W of the CUDA arm (0.15 s per call)
+    r = cpu_reference(args.grid, steps, warmup, planes=args.cpu_planes)
     line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-            "warmup": max(1, min(args.warmup, 3)), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": {"workload": f"3D Poisson {args.grid}^3 7-point SpMV, fp64 (CPU arm: a bounded z-slab sample of it)"},
+            "config": workload_config(args.grid),
+            "run": {"arm": "the reference's generated CPU operator on the host cores, one call per step, int32 row offsets "
+                           "(its only width), no halo exchange (one host)",
+                    "whole_problem": r["whole_problem"]},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "edges_per_s": r["edges_per_s"]}
@@ -177,6 +229,20 @@ def run_reference(args) -> None:
 # --------------------------------------------------------------------------------------------------
 # single-GPU configurations 0-3 (kernel-only numbers, reported beside the headline at N = 1)
 # --------------------------------------------------------------------------------------------------
+def row_error(got: np.ndarray, ref: np.ndarray, abs_sums: np.ndarray) -> float:
+    """max over rows and components of |got - ref| / sum_j |term_ij| (the sum of the magnitudes of the row's
+    per-edge terms: rows such as 4x - sum(x) cancel, so |y_i| itself is no scale for a reordered sum)."""
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    scale = np.maximum(np.asarray(abs_sums, np.float64).reshape(ref.shape), np.finfo(np.float64).tiny)
+    finite = np.isfinite(ref)
+    if not np.array_equal(np.isfinite(got), finite):
+        return float("inf")
+    return float((np.abs(got - ref)[finite] / scale[finite]).max()) if finite.any() else 0.0
+
+
+TOLERANCE = {4: 1e-5, 8: 1e-12}      # per row, relative to the sum of term magnitudes: fp32 / fp64
+
+
 def time_config(name, ir, ext, values, indices, ro, outputs, num_rows, nnz, num_cols, alg_bytes, iters, peak, flush_buf):
     import torch
     launch = ext.prepare(values, indices, ro, outputs, num_rows, nnz, num_cols).launch
@@ -198,6 +264,7 @@ def time_config(name, ir, ext, values, indices, ro, outputs, num_rows, nnz, num_
         torch.cuda.synchronize()
         cold.append(a.elapsed_time(b))
     cold_ms = float(np.median(cold))
+    ext.check()                      # a kernel that gave up (bounded wait, unplanned workspace) fails the run here
     return {"config": name, "rows": int(num_rows), "edges": int(nnz), "algorithmic_bytes": int(alg_bytes),
             "warm": {"ms": warm_ms, "gbs": alg_bytes / warm_ms / 1e6, "frac_of_hbm_peak": alg_bytes / warm_ms / 1e6 / peak,
                      "edges_per_s": nnz / warm_ms * 1e3, "iters": iters},
@@ -205,7 +272,29 @@ def time_config(name, ir, ext, values, indices, ro, outputs, num_rows, nnz, num_
                                 "edges_per_s": nnz / cold_ms * 1e3, "iters": len(cold)}}
 
 
-def single_gpu_configs(peak: float, only=None) -> list:
+def cpu_beside(entry: dict, ir, prob, dtype, gpu_outputs, abs_sums=None, steps: int = 10) -> None:
+    """Adds to a configuration's entry the reference's generated CPU operator timed on the same arrays (all host
+    threads, median of `steps` calls after 2 warm-up calls) and the largest per-row error of the GPU result
+    against that operator's result."""
+    from oracle import ir_eval
+    r = time_cpu_operator(ir, prob, dtype, steps, 2)
+    sec = r["seconds_median"]
+    alg, nnz = entry["algorithmic_bytes"], entry["edges"]
+    entry["cpu_baseline"] = {"value": alg / sec / 1e9, "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "ms": sec * 1e3,
+                             "edges_per_s": nnz / sec, "sample": f"the same arrays, median of {steps} calls, {r['object']}"}
+    if abs_sums is None:
+        _, _, abs_sums = ir_eval.run_graph(ir, prob, dtype, num_threads=host_threads(), want_abs_sums=True)
+    errs = [row_error(g, c, a) for g, c, a in zip(gpu_outputs, r["outputs"], abs_sums)]
+    tol = TOLERANCE[np.dtype(dtype).itemsize]
+    entry["max_row_err"] = {"value": max(errs), "tol": tol, "ok": bool(max(errs) <= tol),
+                            "against": "the reference's generated CPU operator on the same arrays" if r["kind"] == "reference"
+                            else "the CPU restatement of the reference operator",
+                            "relative_to": "sum of the magnitudes of the row's per-edge terms"}
+    if not entry["max_row_err"]["ok"]:
+        raise SystemExit(f"bench.py: {entry['config']}: GPU result differs from the CPU operator: {entry['max_row_err']}")
+
+
+def single_gpu_configs(peak: float, only=None, with_cpu: bool = True) -> list:
     import torch
     from flexspmv_b200 import graphs, problems
     from flexspmv_b200.binding import GraphExtension
@@ -237,8 +326,11 @@ def single_gpu_configs(peak: float, only=None) -> list:
         outs = [torch.empty((prob.num_rows,) + (() if graphs.dim_of(o["shape"]) == 1 else (graphs.dim_of(o["shape"]),)),
                             dtype=dt, device=dev) for o in ir.outputs]
         alg = problems.algorithmic_bytes(ir, prob.num_rows, prob.nnz, prob.num_cols, vb, 4)
-        out.append(time_config(name, ir, GraphExtension(ir), vals, idxs, ro, outs, prob.num_rows, prob.nnz, prob.num_cols,
-                               alg, iters, peak, flush))
+        entry = time_config(name, ir, GraphExtension(ir), vals, idxs, ro, outs, prob.num_rows, prob.nnz, prob.num_cols,
+                            alg, iters, peak, flush)
+        if with_cpu:
+            cpu_beside(entry, ir, prob, np.float32 if vals[0].dtype == torch.float32 else np.float64, [o.cpu().numpy() for o in outs])
+        out.append(entry)
         del vals, idxs, ro, outs
     # ids 6, 7 (not BASELINE configs): the aggregator / map-only flavour (flex_edge_kernel) on 2^27 edges whose
     # selector walks a 2^24-vertex tensor in order (8 edges per vertex): a per-edge product + global sum, fp32,
@@ -268,10 +360,88 @@ def single_gpu_configs(peak: float, only=None) -> list:
     n, m = x.numel(), cols.numel()
     y = torch.empty(n, dtype=torch.float32, device=dev)
     alg = problems.algorithmic_bytes(ir, n, m, n, 4, 4)
-    out.append(time_config("config3 power-law CSR n=2^24 fp32", ir, GraphExtension(ir), [vals, x], [cols], ro, [y], n, m, n, alg,
-                           50, peak, flush))
+    entry = time_config("config3 power-law CSR n=2^24 fp32", ir, GraphExtension(ir), [vals, x], [cols], ro, [y], n, m, n, alg,
+                        50, peak, flush)
+    if with_cpu:
+        # the full-size arrays go to the host once (2.2 GB) and through the reference's CPU operator; the error scale
+        # (sum of |a_ij x_j| per row) is an independent torch reduction on the device
+        rid = torch.repeat_interleave(torch.arange(n, device=dev, dtype=torch.int32), (ro[1:] - ro[:-1]).long())
+        abs_sum = torch.zeros(n, dtype=torch.float32, device=dev).index_add_(0, rid.long(), (vals * x[cols.long()]).abs())
+        del rid
+        prob = problems.Problem("spmv", {"vals": vals.cpu().numpy(), "x": x.cpu().numpy()}, {"selector": cols.cpu().numpy()},
+                                ro.cpu().numpy(), n, n, {"config": 3})
+        cpu_beside(entry, ir, prob, np.float32, [y.cpu().numpy()], abs_sums=[abs_sum.cpu().numpy()], steps=5)
+        del prob, abs_sum
+    out.append(entry)
     del ro, cols, vals, x, y, flush
     torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# result check of the partitioned iteration (every N)
+# --------------------------------------------------------------------------------------------------
+def stencil_reference(x_local, plan, n: int):
+    """The 7-point stencil (6 on the diagonal, -1 off it, Dirichlet) applied with torch slicing to one rank's local
+    vector [halo below | owned planes | halo above]; a missing halo (first / last rank) is the zero boundary."""
+    import torch
+    n2 = n * n
+    planes = plan.rows // n2
+    X = torch.zeros((planes + 2) * n2, dtype=x_local.dtype, device=x_local.device)
+    off = n2 - plan.halo_lo
+    X[off:off + plan.local_len] = x_local
+    X = X.view(planes + 2, n, n)
+    C = X[1:-1]
+    ref = 6.0 * C - X[:-2] - X[2:]
+    ref[:, 1:, :] -= C[:, :-1, :]
+    ref[:, :-1, :] -= C[:, 1:, :]
+    ref[:, :, 1:] -= C[:, :, :-1]
+    ref[:, :, :-1] -= C[:, :, 1:]
+    return ref.reshape(-1)
+
+
+def verify_iteration(op, plan, n: int, rank: int, world: int, use_graph: bool, steps: int = 3) -> dict:
+    """After the timed region, on the same operator object: the owned vector is reset to a seeded U(-1,1) vector and
+    `steps` iterations are checked, each against the stencil applied to the rank's [halo | owned | halo] vector
+    (halos exchanged first).  With a captured graph, one replayed pair must also equal two eager steps bit for bit.
+    The largest error over all ranks, relative to 12 max|x| (the bound of a row's sum of term magnitudes)."""
+    import torch
+    import torch.distributed as dist
+    from flexspmv_b200 import multi_gpu
+    dev = op.buf[0].device
+    g = torch.Generator(device=dev)
+    g.manual_seed(977 + rank)
+    for b in op.buf:
+        b.zero_()
+    op.owned().copy_(torch.rand(plan.rows, generator=g, device=dev, dtype=torch.float64) * 2.0 - 1.0)
+    worst = 0.0
+    for _ in range(steps):
+        x = op.buf[op.cur]
+        multi_gpu.exchange_halos(x, plan, op.group)
+        ref = stencil_reference(x, plan, n)
+        scale = 12.0 * float(x.abs().max())
+        y = op.step()
+        worst = max(worst, float((y - ref).abs().max()) / max(scale, 1e-300))
+        del ref
+    graph_equal = None
+    if use_graph:
+        if op.cur != 0:
+            op.step()
+        start = op.owned().clone()
+        op.step_pair()                       # replays the captured pair
+        replayed = op.owned().clone()
+        op.owned().copy_(start)
+        op.step()
+        op.step()
+        graph_equal = bool(torch.equal(op.owned(), replayed))
+    t = torch.tensor([worst, 0.0 if graph_equal in (None, True) else 1.0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    err, graph_bad = float(t[0].item()), bool(t[1].item() > 0)
+    out = {"max_row_err": err, "tol": 1e-12, "steps": steps, "ok": bool(err <= 1e-12 and not graph_bad),
+           "against": "7-point stencil applied by torch slicing to each rank's [halo | owned | halo] vector"}
+    if use_graph:
+        out["graph_replay_equals_eager"] = not graph_bad
     return out
 
 
@@ -296,7 +466,7 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     peak, peak_kind = load_peaks()
     if args.only_config is not None:      # profiling aid: one single-GPU configuration, nothing else
-        print(json.dumps({"configs": single_gpu_configs(peak, only=[args.only_config])}), flush=True)
+        print(json.dumps({"configs": single_gpu_configs(peak, only=[args.only_config], with_cpu=not args.no_cpu)}), flush=True)
         return
     n = args.grid
     n2 = n * n
@@ -335,12 +505,16 @@ def run_ours(args) -> None:
     for i in range(W + (W % 2)):     # an even number of warm-up steps: the captured pair starts from buffer 0
         op.step()
     use_graph = world > 1 and not args.no_graph and K % 2 == 0 and K <= 200
+    graph_error = None
     if use_graph:
         flag = torch.tensor([1 if op.capture_pair() else 0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)          # all ranks replay, or none does
         use_graph = bool(flag.item())
+        graph_error = op.graph_error
         if not use_graph:
             op.graph = None
+            if graph_error is None:
+                graph_error = "capture failed on another rank"
     barrier()
     if rank == 0:
         sampler.mark_begin()
@@ -358,6 +532,7 @@ def run_ours(args) -> None:
             op.step()
     e1.record()
     barrier()
+    ext.check()          # raises if a kernel of the timed region gave up (bounded wait ran out, workspace not planned)
     timed_launches = (K * op.launches_per_step) if use_graph else (ext.launches - launches0 + extra)
     ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -385,6 +560,9 @@ def run_ours(args) -> None:
         dist.all_reduce(launches)
     ms_per_step = total_ms / K
     value = alg_bytes / ms_per_step / 1e6     # GB/s over the whole job
+    ext.check()
+    check = verify_iteration(op, plan, n, rank, world, use_graph)
+    ext.check()
 
     # ---- end to end through the reference-facing operator with host buffers ---------------------------
     # Every step: pinned-host x -> device, halo exchange, merged_spmv_launch (allocates y), y -> pinned host.
@@ -429,6 +607,7 @@ def run_ours(args) -> None:
     if world > 1:
         dist.all_reduce(ems, op=dist.ReduceOp.MAX)
     e2e_ms = float(ems.item()) / E
+    ext.check()
     hb = torch.tensor([plan.rows * 8], dtype=torch.int64, device=dev)
     if world > 1:
         dist.all_reduce(hb)
@@ -442,16 +621,16 @@ def run_ours(args) -> None:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": f"config4: 3D Poisson {n}^3 7-point SpMV, fp64 values, int64 row offsets, int32 columns, "
-                               f"{nnz_total} non-zeros, x <- A x with one z-plane halo per neighbour per iteration",
-                   "partition": f"{world} nnz-balanced z-slab(s), merge-path tile plan cached across iterations",
-                   "halo_overlap": bool(op.overlap), "launches_per_step_per_rank": op.launches_per_step,
-                   "cuda_graph": bool(use_graph),
-                   "l2": "inputs larger than L2 (per-GPU matrix slab >= 1.8 GB)", "algorithmic_bytes_per_step": alg_bytes,
-                   "halo_bytes_per_neighbour_per_direction": n2 * 8 if world > 1 else 0},
+        "config": workload_config(n),
+        "run": {"arm": "hand-written sm_100a kernels behind the C ABI, int64 row offsets, iterated as x <- A x with one z-plane "
+                       "halo per neighbour per iteration",
+                "partition": f"{world} nnz-balanced z-slab(s), merge-path tile plan cached across iterations",
+                "halo_overlap": bool(op.overlap), "launches_per_step_per_rank": op.launches_per_step,
+                "cuda_graph": bool(use_graph), "cuda_graph_error": graph_error,
+                "halo_bytes_per_neighbour_per_direction": n2 * 8 if world > 1 else 0},
         "edges_per_s": nnz_total / ms_per_step * 1e3,
         "frac_of_hbm_peak": value / (peak * world), "hbm_peak_gbs_per_gpu": peak, "hbm_peak_kind": peak_kind,
-        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches.item()),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches.item()), "check": check, "device_status": 0,
     }
     if world == 1:
         info = ext.symbols(torch.float64).graph_info
@@ -460,24 +639,27 @@ def run_ours(args) -> None:
                             "launch_ms": ms_per_step, "algorithmic_bytes_per_launch": alg_bytes,
                             "tile": {"block": info.block_threads, "items_per_thread": info.items_per_thread,
                                      "stages": info.stages, "smem_bytes": info.smem_bytes}}
-        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on the 192^3 grid (761,757,704
-        # algorithmic bytes: 742.8 MB read + 53.4 MB written = 1.045 x; a later capture that ended before all of y
-        # was written back read 718.3 + 24.3 MB); traffic grows in proportion to the grid, so it is scaled to this
-        # launch by the algorithmic bytes
-        line["roofline"]["traffic"] = DRAM_BYTES_PER_ALGORITHMIC_BYTE * alg_bytes
-        line["roofline"]["traffic_source"] = ("ncu --set full, flex_tile_kernel<spmv_f64, int64 offsets>, 3D Poisson 192^3: "
-                                              "742.8 MB read + 53.4 MB written for 761.8 MB of algorithmic bytes, scaled by "
-                                              "algorithmic bytes (profiles/flex_tile_kernel_spmv_f64_poisson3d.md)")
+        ratio = (DRAM_CAPTURE["read_bytes"] + DRAM_CAPTURE["write_bytes"]) / DRAM_CAPTURE["algorithmic_bytes"]
+        line["roofline"]["traffic"] = ratio * alg_bytes
+        line["roofline"]["traffic_source"] = (
+            f"one ncu capture of this kernel on the {DRAM_CAPTURE['grid']}^3 grid: {DRAM_CAPTURE['read_bytes'] / 1e6:.1f} MB read + "
+            f"{DRAM_CAPTURE['write_bytes'] / 1e6:.1f} MB written for {DRAM_CAPTURE['algorithmic_bytes'] / 1e6:.1f} MB of algorithmic "
+            f"bytes ({ratio:.3f} x; part of y was still in L2 when the capture ended), scaled by algorithmic bytes")
         del op, ro, cols, vals, x0, xbuf
         torch.cuda.empty_cache()
         if not args.no_configs:
-            line["configs"] = single_gpu_configs(peak)
+            line["configs"] = single_gpu_configs(peak, with_cpu=not args.no_cpu)
         if not args.no_cpu:
-            r = cpu_reference(n, 5, 1)
+            r = cpu_reference(n, 5, 1, planes=args.cpu_planes)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
             line["cpu_baseline"]["edges_per_s"] = r["edges_per_s"]
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if not check["ok"]:
+        sys.stderr.write(f"bench.py: result check failed: {check}\n")
+        sys.stderr.flush()
+        sys.stdout.flush()
+        os._exit(1)          # no communicator teardown (see below); a failed check is a failed run
     if world > 1:
         # A captured graph holds NCCL kernels; tearing the communicator down under it has hung at exit.
         # Everything is measured and printed: drop the graph, meet once more, and leave without the
@@ -499,7 +681,9 @@ def main():
     ap.add_argument("--grid", type=int, default=512)
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table (N = 1)")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (N = 1)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (N = 1)")
+    ap.add_argument("--cpu-planes", type=int, default=None,
+                    help="CPU arm: time this many z-planes of the matrix instead of the whole grid (hosts short of memory)")
     ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3, 5, 6, 7],
                     help="run just this single-GPU configuration (kernel-only timings) and print its entry")
     ap.add_argument("--overlap", action="store_true", help="N > 1: split off the halo-reading rows and overlap the exchange with the interior launch")

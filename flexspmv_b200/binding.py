@@ -17,7 +17,12 @@ Differences from the reference binding, all on the host side of the same contrac
   * the merge-path partition is planned once per (row_end_offsets tensor, version, stream) and cached;
   * int64 ``row_end_offsets`` are accepted as they are (the reference casts to int32);
   * an unsupported dtype raises (the reference prints to stderr and falls off the end of a non-void
-    function, cuda_template/merged_binding_template.cu:65-68).
+    function, cuda_template/merged_binding_template.cu:65-68);
+  * a kernel that gives up (a bounded device-side wait ran out, or the workspace was not planned for the
+    problem) stores its status in a page-locked host int registered with the workspace: the next call on
+    that workspace, or ``ext.check()``, raises FlexSpmvError.  The launch path itself never synchronises;
+    FLEXSPMV_CHECK_STATUS=1 makes every call synchronise and check.  After such an error the outputs of the
+    failed launch are undefined.
 
 There is no CPU path: a missing library or a CPU tensor is an error.
 """
@@ -74,6 +79,30 @@ def load_library(path: Optional[str] = None) -> ctypes.CDLL:
 def check(lib, status: int, what: str):
     if status != 0:
         raise FlexSpmvError(f"{what} failed: {lib.flexspmv_error_string(status).decode()} (status {status})")
+
+
+_CHECK_EVERY_CALL = os.environ.get("FLEXSPMV_CHECK_STATUS", "0") == "1"
+
+
+class _Plan:
+    """One planned workspace: the scratch tensor, its size, the tensors whose addresses it depends on, and
+    the page-locked int the kernels copy their error status to."""
+    __slots__ = ("ws", "nbytes", "keep", "flag", "_flag_view")
+
+    def __init__(self, ws, nbytes, keep):
+        self.ws, self.nbytes, self.keep = ws, nbytes, keep
+        self.flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._flag_view = self.flag.numpy()
+
+    def status(self) -> int:
+        return int(self._flag_view[0])
+
+
+def _raise_if_failed(lib, plan: "_Plan", what: str):
+    st = plan.status()
+    if st != 0:
+        raise FlexSpmvError(f"{what}: an earlier launch on this workspace failed on the device: "
+                            f"{lib.flexspmv_error_string(st).decode()} (status {st}); its outputs are undefined")
 
 
 def _stream_ptr() -> ctypes.c_void_p:
@@ -163,7 +192,7 @@ class GraphExtension:
                     self.tile_items, self.max_ctas, flags)
 
     def _workspace(self, syms: _Symbols, desc: Desc, ro: Optional[torch.Tensor], device,
-                   indices: Sequence[torch.Tensor] = ()) -> Tuple[torch.Tensor, int]:
+                   indices: Sequence[torch.Tensor] = ()) -> "_Plan":
         # a workspace holds per-launch state (ticket, carries): launches that may overlap on the GPU must not
         # share one, so the plan is cached per stream as well as per matrix
         key = (id(syms), desc.num_rows, desc.num_edges, desc.offset_bits, desc.tile_items, desc.max_ctas,
@@ -173,7 +202,7 @@ class GraphExtension:
         hit = self._plans.get(key)
         if hit is not None:
             self._plans.move_to_end(key)
-            return hit[0], hit[1]
+            return hit
         nbytes = ctypes.c_size_t()
         check(self.lib, syms.workspace_bytes(ctypes.byref(desc), ctypes.byref(nbytes)), "workspace_bytes")
         ws = torch.empty(nbytes.value, dtype=torch.uint8, device=device)
@@ -187,10 +216,15 @@ class GraphExtension:
             self.launches += 2
         self.launches += 2 if ro is not None else 1
         # keep the row-offset tensor alive so its address cannot be recycled under a cached plan
-        self._plans[key] = (ws, nbytes.value, ro, tuple(indices) if desc.reserved else None)
+        plan = _Plan(ws, nbytes.value, (ro, tuple(indices) if desc.reserved else None))
+        check(self.lib, self.lib.flexspmv_workspace_status_mirror(ctypes.c_void_p(ws.data_ptr()),
+                                                                  ctypes.c_void_p(plan.flag.data_ptr()), _stream_ptr()),
+              "workspace_status_mirror")
+        self.launches += 1
+        self._plans[key] = plan
         while len(self._plans) > self.PLAN_CACHE_ENTRIES:
             self._plans.popitem(last=False)
-        return ws, nbytes.value
+        return plan
 
     # -- the operator --------------------------------------------------------------------------------
     def merged_spmv_launch(self, *args, **kwargs):
@@ -238,15 +272,18 @@ class GraphExtension:
                 shape = (ne,) if d == 1 else (ne, d)
             outputs.append(torch.empty(shape, dtype=dt, device=device))
         with torch.cuda.device(device):
-            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
+            plan = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
+            _raise_if_failed(self.lib, plan, "merged_spmv_launch")
             vp = (ctypes.c_void_p * max(nv, 1))(*[t.data_ptr() for t in values])
             ip = (ctypes.c_void_p * max(ni, 1))(*[t.data_ptr() for t in indices])
             op = (ctypes.c_void_p * max(len(outputs), 1))(*[t.data_ptr() for t in outputs])
             st = syms.launch(ctypes.byref(desc), vp, ip,
                              ctypes.c_void_p(row_end_offsets.data_ptr() if has_red else 0), op,
-                             ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws_bytes), _stream_ptr())
+                             ctypes.c_void_p(plan.ws.data_ptr()), ctypes.c_size_t(plan.nbytes), _stream_ptr())
         check(self.lib, st, "merged_spmv_launch")
         self.launches += 1
+        if _CHECK_EVERY_CALL:
+            self.check()
         if not outputs:
             return None
         return tuple(outputs)
@@ -265,15 +302,18 @@ class GraphExtension:
         device = values[0].device
         desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols)
         with torch.cuda.device(device):
-            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
+            plan = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
+            _raise_if_failed(self.lib, plan, "launch_into")
             vp = (ctypes.c_void_p * max(len(values), 1))(*[t.data_ptr() for t in values])
             ip = (ctypes.c_void_p * max(len(indices), 1))(*[t.data_ptr() for t in indices])
             op = (ctypes.c_void_p * max(len(outputs), 1))(*[t.data_ptr() for t in outputs])
             st = syms.launch(ctypes.byref(desc), vp, ip,
                              ctypes.c_void_p(row_end_offsets.data_ptr() if has_red else 0), op,
-                             ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws_bytes), _stream_ptr())
+                             ctypes.c_void_p(plan.ws.data_ptr()), ctypes.c_size_t(plan.nbytes), _stream_ptr())
         check(self.lib, st, "launch_into")
         self.launches += 1
+        if _CHECK_EVERY_CALL:
+            self.check()
 
     def prepare(self, values: Sequence[torch.Tensor], indices: Sequence[torch.Tensor],
                 row_end_offsets: Optional[torch.Tensor], outputs: Sequence[torch.Tensor],
@@ -289,27 +329,41 @@ class GraphExtension:
         device = values[0].device
         desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols)
         with torch.cuda.device(device):
-            ws, ws_bytes = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
+            plan = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
         return PreparedLaunch(self, syms, desc, list(values), list(indices), row_end_offsets if has_red else None,
-                              list(outputs), ws, ws_bytes)
+                              list(outputs), plan)
 
     def device_status(self, dtype: torch.dtype, row_end_offsets: Optional[torch.Tensor] = None) -> int:
         """Reads back the status word of the most recently used workspace (synchronises)."""
         if not self._plans:
             return 0
-        ws = next(reversed(self._plans.values()))[0]
+        ws = next(reversed(self._plans.values())).ws
         out = torch.zeros(1, dtype=torch.int32, device=ws.device)
         syms = self.symbols(dtype)
-        check(self.lib, syms.device_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(out.data_ptr()), _stream_ptr()),
-              "device_status")
+        with torch.cuda.device(ws.device):
+            check(self.lib, syms.device_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(out.data_ptr()), _stream_ptr()),
+                  "device_status")
         return int(out.item())
+
+    def check(self) -> None:
+        """Waits for the work enqueued so far on every device this object planned for, then raises
+        FlexSpmvError if a kernel gave up on any of its cached workspaces (a bounded wait ran out, or a
+        launch met a workspace that was not planned for its problem).  Call it after a timed region or a
+        time-stepping loop; the launch path itself only looks at the host-side copy of the status."""
+        plans = list(self._plans.values())
+        for dev in {p.ws.device for p in plans}:
+            torch.cuda.synchronize(dev)
+        for p in plans:
+            _raise_if_failed(self.lib, p, "check")
 
 
 class PreparedLaunch:
     """One graph bound to one set of device tensors (see ``GraphExtension.prepare``)."""
 
-    def __init__(self, ext: GraphExtension, syms: _Symbols, desc: Desc, values, indices, ro, outputs, ws, ws_bytes):
+    def __init__(self, ext: GraphExtension, syms: _Symbols, desc: Desc, values, indices, ro, outputs, plan: _Plan):
         self.ext, self._syms, self._desc = ext, syms, desc
+        ws, ws_bytes = plan.ws, plan.nbytes
+        self._plan = plan
         self._keep = (values, indices, ro, outputs, ws)       # the raw pointers below borrow these tensors
         self._device = ws.device.index
         self._planned = torch.cuda.Event()                    # the plan kernels were enqueued on this stream
@@ -329,14 +383,22 @@ class PreparedLaunch:
         if torch.cuda.current_device() != self._device:
             with torch.cuda.device(self._device):
                 return self.launch()
+        if self._plan._flag_view[0]:
+            _raise_if_failed(self.ext.lib, self._plan, "launch")
         stream = torch.cuda.current_stream()
         if stream.cuda_stream not in self._ordered:           # first use on another stream: after the plan
+            if torch.cuda.is_current_stream_capturing():
+                # an event recorded outside a capture cannot be waited on inside it
+                raise FlexSpmvError("first launch of a prepared object on a stream that is being captured: launch it "
+                                    "once on that stream before the capture begins")
             stream.wait_event(self._planned)
             self._ordered.add(stream.cuda_stream)
         st = self._fn(*self._args, ctypes.c_void_p(stream.cuda_stream))
         if st != 0:
             check(self.ext.lib, st, "launch")
         self.ext.launches += 1
+        if _CHECK_EVERY_CALL:
+            self.ext.check()
 
     __call__ = launch
 

@@ -43,10 +43,28 @@ struct WorkspaceHeader {
   uint64_t win_index_offset;   // ... and per-edge 16-bit positions inside the tile's window area
   int32_t win_ready;           // 1 once the window plan has filled them
   int32_t reserved0;
-  char pad[256 - 4 * 4 - 3 * 8 - 2 * 4 - 4 * 8 - 8 * 4 - 2 * 8 - 2 * 4];
+  uint64_t status_mirror;      // device alias of a pinned host int32 that receives a copy of `status` when a
+                               // kernel raises an error (0: none); lets the host notice without a sync or a copy
+  char pad[256 - 4 * 4 - 3 * 8 - 2 * 4 - 4 * 8 - 8 * 4 - 2 * 8 - 2 * 4 - 8];
 };
 static_assert(sizeof(WorkspaceHeader) == 256, "header is one 256-byte block");
 constexpr uint32_t kMagic = 0x464c5831u;  // "FLX1"
+
+// Raises `err` in the workspace header (first error wins, sticky until the workspace is planned again) and
+// copies it to the host-visible mirror when one is registered.
+__device__ __forceinline__ void raise_status(WorkspaceHeader* h, int err) {
+  if (atomicCAS(&h->status, 0, err) == 0) {
+    volatile int32_t* m = reinterpret_cast<volatile int32_t*>(h->status_mirror);
+    if (m) { *m = err; __threadfence_system(); }
+  }
+}
+
+// A launch found a header that does not describe its problem.  A header that was planned for another problem
+// is otherwise intact; one that was never planned holds arbitrary bytes, so only the status word is written.
+__device__ __forceinline__ void raise_not_planned(WorkspaceHeader* h) {
+  if (h->magic == kMagic) raise_status(h, FLEXSPMV_ERR_NOT_PLANNED);
+  else h->status = FLEXSPMV_ERR_NOT_PLANNED;
+}
 
 // ---- gather windows ---------------------------------------------------------------------------------
 // On matrices whose tiles touch only a few contiguous column ranges (stencils, banded meshes) the plan can

@@ -61,6 +61,12 @@ __global__ void debug_withhold_kernel(WorkspaceHeader* h, uint32_t first_tile_pl
 __global__ void window_ready_kernel(WorkspaceHeader* h) {
   if (threadIdx.x == 0 && blockIdx.x == 0) h->win_ready = 1;
 }
+__global__ void status_mirror_kernel(WorkspaceHeader* h, int32_t* mirror) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    h->status_mirror = reinterpret_cast<uint64_t>(mirror);
+    if (mirror) { *reinterpret_cast<volatile int32_t*>(mirror) = h->status; __threadfence_system(); }
+  }
+}
 int window_ready_launch(void* ws, cudaStream_t st) {
   window_ready_kernel<<<1, 32, 0, st>>>(static_cast<WorkspaceHeader*>(ws));
   return (int)cudaGetLastError();
@@ -379,6 +385,19 @@ int flexspmv_debug_withhold_stage(void* d_workspace, uint32_t first_tile_plus_on
   if (!d_workspace) return FLEXSPMV_ERR_WORKSPACE;
   flex::debug_withhold_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<flex::WorkspaceHeader*>(d_workspace),
                                                                                first_tile_plus_one);
+  return (int)cudaGetLastError();
+}
+
+int flexspmv_workspace_status_mirror(void* d_workspace, int32_t* pinned_host_status, void* stream) {
+  if (!d_workspace) return FLEXSPMV_ERR_WORKSPACE;
+  int32_t* alias = nullptr;
+  if (pinned_host_status) {
+    void* dptr = nullptr;
+    cudaError_t e = cudaHostGetDevicePointer(&dptr, pinned_host_status, 0);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
+    alias = static_cast<int32_t*>(dptr);
+  }
+  flex::status_mirror_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<flex::WorkspaceHeader*>(d_workspace), alias);
   return (int)cudaGetLastError();
 }
 

@@ -37,6 +37,12 @@ __global__ void __launch_bounds__(BLOCK) flex_edge_kernel(const typename G::Para
   __shared__ V s_part[kWarps * kAgg];
   __shared__ int s_flag;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // a workspace that was not planned for this problem holds an arbitrary ticket: every CTA sees the same
+  // header, so all of them leave here and nothing is written
+  if (a.header->magic != kMagic || a.header->num_edges != a.num_edges || a.header->num_tiles != 0) {
+    if (tid == 0 && blockIdx.x == 0) raise_not_planned(a.header);
+    return;
+  }
   GlobalTile<G> tile{&p};
   V agg[kAgg];
 #pragma unroll

@@ -25,8 +25,13 @@ int window_ready_launch(void* ws, cudaStream_t st);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+struct NoWindows {   // in place of CfgWin: the gather-window variant of the kernel is not built and the flag is ignored
+  static constexpr int kTile = 0;
+};
+
 template <class G, class Cfg, class CfgWin = Cfg>
 struct GraphApi {
+  static constexpr bool kWindowsBuilt = !std::is_same_v<CfgWin, NoWindows>;
   using V = typename G::V;
   static constexpr int kEdgeBlock = 256, kEdgeIpt = 4;
   // Row-mode graphs run one thread per row, the trailing partial row of the tile included: on a mesh with
@@ -37,7 +42,7 @@ struct GraphApi {
 
   // Gather windows are used when the graph supports them and the caller asked for them in the descriptor.
   static bool use_win(const flexspmv_desc* d) {
-    if constexpr (G::kHasReducer) return G::kWindowGather && (d->reserved & FLEXSPMV_FLAG_GATHER_WINDOWS) != 0;
+    if constexpr (G::kHasReducer && kWindowsBuilt) return G::kWindowGather && (d->reserved & FLEXSPMV_FLAG_GATHER_WINDOWS) != 0;
     return false;
   }
   static int compiled_tile(const flexspmv_desc* d) { return use_win(d) ? CfgWin::kTile : Cfg::kTile; }
@@ -180,7 +185,7 @@ struct GraphApi {
   static int plan_windows(const flexspmv_desc* d, const void* const* indices, void* ws, size_t ws_bytes, cudaStream_t st) {
     if (int e = check_desc(d)) return e;
     if (!use_win(d)) return 0;          // nothing to do for graphs / descriptors without windows
-    if constexpr (G::kHasReducer && G::kWindowGather) {
+    if constexpr (G::kHasReducer && G::kWindowGather && kWindowsBuilt) {
       if (!ws) return FLEXSPMV_ERR_WORKSPACE;
       if (!indices || !indices[0]) return FLEXSPMV_ERR_BAD_ARG;
       WorkspaceHeader h{};
@@ -212,7 +217,7 @@ struct GraphApi {
     if constexpr (G::kHasReducer) {
       if (!row_offsets) return FLEXSPMV_ERR_BAD_ARG;
       if (!aligned16(row_offsets)) return FLEXSPMV_ERR_ALIGN;
-      if constexpr (G::kWindowGather) {
+      if constexpr (G::kWindowGather && kWindowsBuilt) {
         if (use_win(d)) {
           if (d->offset_bits == 64) return launch_tiles<long long, CfgWin, true>(d, p, row_offsets, ws, h, st);
           return launch_tiles<int, CfgWin, true>(d, p, row_offsets, ws, h, st);
@@ -239,7 +244,7 @@ struct GraphApi {
   static int device_status(const void* ws, int32_t* d_out, cudaStream_t st) {
     if (!ws || !d_out) return FLEXSPMV_ERR_BAD_ARG;
     const char* src = static_cast<const char*>(ws) + offsetof(WorkspaceHeader, status);
-    return (int)cudaMemcpyAsync(d_out, src, sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+    return (int)cudaMemcpyAsync(d_out, src, sizeof(int32_t), cudaMemcpyDefault, st);
   }
 };
 
@@ -297,10 +302,14 @@ struct GraphApi {
     }                                                                                                           \
   } static_scratch_##SYM;                                                                                       \
   }                                                                                                             \
-  extern "C" int flexspmv_##SYM##_launch_static(const flexspmv_desc* d, const void* const* v,                   \
+  extern "C" int flexspmv_##SYM##_launch_static(const flexspmv_desc* d_in, const void* const* v,                \
                                                 const void* const* ix, const void* ro, void* const* o,          \
                                                 void* st) {                                                     \
-    using Api = flex::GraphApi<GRAPH, CFG>;                                                                     \
+    using Api = flex::GraphApi<GRAPH, CFG, flex::NoWindows>;                                                    \
+    if (!d_in) return FLEXSPMV_ERR_BAD_ARG;                                                                     \
+    flexspmv_desc desc = *d_in;                                                                                 \
+    desc.reserved = 0; /* gather windows need a second planning step and 2 bytes of scratch per edge: not here */ \
+    const flexspmv_desc* d = &desc;                                                                             \
     size_t need = 0;                                                                                            \
     if (int e = Api::workspace_bytes(d, &need)) return e;                                                       \
     if (need > (size_t)(BYTES)) return FLEXSPMV_ERR_STATIC_SCRATCH;                                             \
@@ -311,4 +320,9 @@ struct GraphApi {
     /* every tile coordinate this problem reads; the carry slots are written before they are read      */      \
     if (int e = Api::plan(d, ro, ws, (size_t)(BYTES), stream)) return e;                                        \
     return Api::launch(d, v, ix, ro, o, ws, (size_t)(BYTES), stream);                                           \
+  }                                                                                                             \
+  extern "C" int flexspmv_##SYM##_static_device_status(int32_t* d_out, void* st) {                              \
+    void* ws = nullptr;                                                                                         \
+    if (int e = static_scratch_##SYM.lookup(&ws)) return e;                                                     \
+    return flex::GraphApi<GRAPH, CFG, flex::NoWindows>::device_status(ws, d_out, static_cast<cudaStream_t>(st)); \
   }

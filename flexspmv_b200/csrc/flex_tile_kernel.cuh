@@ -199,7 +199,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   // sees the same header, so all of them leave here and the ticket stays untouched
   if (a.header->magic != kMagic || a.header->num_tiles != a.num_tiles || a.header->num_rows != a.num_rows ||
       a.header->num_edges != a.num_edges || a.header->offset_bits != (int)(8 * sizeof(OffsetT))) {
-    if (tid == 0 && blockIdx.x == 0 && a.header->magic == kMagic) atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_NOT_PLANNED);
+    if (tid == 0 && blockIdx.x == 0) raise_not_planned(a.header);
     return;
   }
 
@@ -340,7 +340,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       }
       if (!pfail && count >= 1) prefetch_gathers(count - 1);
       if (pfail && lane == 0) {   // the consumers never released a stage: flag it, let copies in flight land, leave
-        atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
+        raise_status(a.header, FLEXSPMV_ERR_TIMEOUT);
         a.header->debug[4] = (uint32_t)issued; a.header->debug[5] = blockIdx.x;
         for (int j = issued > S ? issued - S : 0; j < issued; ++j)
           mbar_wait_bounded(&bars[j % S], (uint32_t)(j / S) & 1u, kWaitPolls);
@@ -380,7 +380,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       const bool ok = named_bar_and(1, BLOCK, mbar_wait_bounded(&bars[s], (uint32_t)(k / S) & 1u, kWaitPolls));
       if (!ok) {
         if (tid == 0) {
-          atomicCAS(&a.header->status, 0, FLEXSPMV_ERR_TIMEOUT);
+          raise_status(a.header, FLEXSPMV_ERR_TIMEOUT);
           a.header->debug[0] = (uint32_t)(t_begin + k); a.header->debug[1] = (uint32_t)s; a.header->debug[2] = blockIdx.x;
         }
         return false;

@@ -218,6 +218,7 @@ class PartitionedSpmv:
         # boundary launches cost more than the 2 MiB exchange they hide -- so overlapping is opt-in
         self.overlap = bool(overlap) and plan.world > 1
         self._prepared = {}
+        self.graph, self.graph_error = None, None
         self.parts = []          # (row_begin, row_end, ro_sub, cols_sub, vals_sub); interior first
         if self.overlap:
             lo_rows, hi_rows = boundary_rows(row_offsets, cols_local, plan)
@@ -274,12 +275,18 @@ class PartitionedSpmv:
         and stays eager if the capture is refused."""
         if self.cur != 0:
             self.step()
+        self.graph, self.graph_error = None, None
         try:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
+                # one eager pair on the capture stream first: a prepared launch orders its first use on a new
+                # stream after its plan with an event wait, which is not allowed inside a capture
+                self.step()
+                self.step()
+                side.synchronize()
                 with torch.cuda.graph(g, stream=side):
                     self.step()
                     self.step()
@@ -287,7 +294,7 @@ class PartitionedSpmv:
             torch.cuda.synchronize()
             self.graph = g
             return True
-        except Exception as e:      # eager path keeps working
+        except Exception as e:      # eager path keeps working; the reason is kept for the caller to report
             self.graph = None
             self.graph_error = repr(e)
             torch.cuda.synchronize()

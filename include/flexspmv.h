@@ -112,6 +112,17 @@ int flexspmv_row_blocks(const void *d_row_offsets, int32_t offset_bits, int64_t 
 int flexspmv_debug_withhold_stage(void *d_workspace, uint32_t first_tile_plus_one, void *stream);
 
 /*
+ * Host-visible copy of a workspace's status word.  `pinned_host_status` is an int32 in page-locked host
+ * memory (cudaHostAlloc / cudaHostRegister; NULL removes the registration).  From then on a kernel that
+ * raises FLEXSPMV_ERR_TIMEOUT or FLEXSPMV_ERR_NOT_PLANNED on this workspace also stores the code there, so
+ * the host can notice a failed launch by reading one int -- no copy, no synchronisation on the launch path.
+ * The call itself stores the current status (normally 0).  Planning the workspace again drops the
+ * registration.  After FLEXSPMV_ERR_TIMEOUT the outputs of that launch are undefined (rows of the tiles
+ * that were not reached are not written).  No reference counterpart (its kernels cannot fail this way).
+ */
+int flexspmv_workspace_status_mirror(void *d_workspace, int32_t *pinned_host_status, void *stream);
+
+/*
  * Halo plan of a 1-D row-block partition (host only, pure integers): given the world + 1 block
  * boundaries and, per block, the smallest and largest global column its rows reference (for an empty
  * block: row_begin and row_begin - 1), computes for every rank how many vector entries it needs from
@@ -183,7 +194,7 @@ int flexspmv_swe_rk_stage(int32_t value_bytes, const void *const *d_r, const voi
  *                                the aggregator flavour cuda_template/aggregator/...:348-409).
  *                                Every output element is written (outputs need no zero fill).
  *   flexspmv_G_T_device_status   copies the workspace's device status word into *d_status_out
- *                                (device int32) without synchronising
+ *                                (int32 in device or page-locked host memory) without synchronising
  *
  * Pointer arrays of launch (device pointers; order = the operator's positional order,
  * codegen/merged_gen_binding.py:65-78):
@@ -258,7 +269,12 @@ FLEXSPMV_DECLARE_GRAPH(edge_copy_i64)
  *   - Same arguments and results as flexspmv_spmv_f64_plan followed by flexspmv_spmv_f64_launch, minus
  *     the workspace: every call partitions the problem into the static array (two small kernels) and
  *     runs the fused pass, all on `stream`.  It calls no cudaMalloc, cudaFree or allocating library
- *     routine.
+ *     routine.  FLEXSPMV_FLAG_GATHER_WINDOWS in the descriptor is ignored (the windows need a second
+ *     planning step and two more bytes of scratch per edge).
+ *   - flexspmv_spmv_f64_static_device_status copies the array's status word (0, FLEXSPMV_ERR_TIMEOUT
+ *     or FLEXSPMV_ERR_NOT_PLANNED, as raised by the kernels of the most recent call) into *d_status_out
+ *     (int32 in device or page-locked host memory) on `stream`, without synchronising: the error
+ *     channel that flexspmv_spmv_f64_device_status gives callers who own a workspace.
  *   - Problems whose scratch need (flexspmv_spmv_f64_workspace_bytes) exceeds the array are refused
  *     with FLEXSPMV_ERR_STATIC_SCRATCH; with the default tile size that is about 160 million rows +
  *     non-zeros with 64-bit offsets, twice that with 32-bit offsets.
@@ -272,6 +288,7 @@ FLEXSPMV_DECLARE_GRAPH(edge_copy_i64)
 int flexspmv_spmv_f64_launch_static(const flexspmv_desc *desc, const void *const *values,
                                     const void *const *indices, const void *d_row_offsets,
                                     void *const *outputs, void *stream);
+int flexspmv_spmv_f64_static_device_status(int32_t *d_status_out, void *stream);
 
 #ifdef __cplusplus
 }

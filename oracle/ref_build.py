@@ -11,11 +11,19 @@ exactly as merged_gen_cpu.py does, and compile the resulting ``OmpMergeSystem<Va
 ``g++ -O3 -fopenmp`` (the flags of test_full/easier_full.py:476; no -march so the object runs on any
 x86-64 host) behind a three-line ``extern "C"`` trampoline written here.  The reference's torch
 binding (merged_binding_cpu.cpp) is a thin shim over the same function and is not needed.
+The trampoline also exports the header's own free function ``MergePathSearch``
+(cpu_template/merged_spmv_template_reducer.h:27-51) as ``ref_merge_path_search`` so that partition
+coordinates can be compared with the reference's search itself.
+
+The reference's Makefile compiles with ``-march=native`` (Makefile:18).  The machine that times the CPU
+arm is not the machine that compiles it (the reference tree is only present on the latter), so a
+second object of the plain SpMV graph is built with ``-march=x86-64-v3`` (AVX2 + FMA, what every recent
+x86-64 server has); the benchmark times both and keeps the faster.  The tests use the portable one.
 
 No reference source text is copied into the repository: the generated header lives in a temporary
-directory and only the compiled object is kept.  Requires the reference tree (its location is REF_DIR
-below, FLEXSPMV_REFERENCE_DIR overrides it); when it is absent this script does nothing and the prebuilt
-objects already in oracle/_ref are used.
+directory and only the compiled object is kept.  Requires the reference tree: FLEXSPMV_REFERENCE_DIR, or
+a directory called ``reference`` beside the repository; when it is absent this script does nothing and
+the prebuilt objects already in oracle/_ref are used.
 """
 from __future__ import annotations
 
@@ -28,9 +36,11 @@ import sys
 import tempfile
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.environ.get("FLEXSPMV_REFERENCE_DIR", "/root/reference")
+REF_DIR = os.environ.get("FLEXSPMV_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 OUT_DIR = os.path.join(_HERE, "_ref")
 CXX = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+
+RECIPE = 2      # bumped when the trampoline or the compile commands change, so that existing objects are rebuilt
 
 _CTYPE = {"float32": ("float", "f32"), "float64": ("double", "f64"), "int64": ("long", "i64")}
 
@@ -102,14 +112,25 @@ def build_graph(ir, dtypes) -> dict:
             tramp.append(
                 f"void ref_run_{sfx}(int num_threads, int* row_offsets, void** p, int num_rows, int nnz) {{\n"
                 f"  OmpMergeSystem<{cty}, int>(num_threads, {ro}{args}{', ' if args else ''}num_rows, nnz);\n}}")
+        if has_rows:   # the reducer template defines the search; `a` = row END offsets (the callee's shifted pointer)
+            tramp.append(
+                "void ref_merge_path_search(int diagonal, int* row_end_offsets, int num_rows, int nnz, int* xy) {\n"
+                "  int2 c; CountingInputIterator<int> nz(0);\n"
+                "  MergePathSearch(diagonal, row_end_offsets, nz, num_rows, nnz, c);\n"
+                "  xy[0] = c.x; xy[1] = c.y;\n}")
         tramp.append("}")
         with open(os.path.join(tmp, "trampoline.cpp"), "w") as f:
             f.write("\n".join(tramp) + "\n")
         so = os.path.join(OUT_DIR, f"libref_{ir.name}.so")
-        cmd = [CXX, "-O3", "-fopenmp", "-fPIC", "-shared", "-w", "-I", REF_DIR, "-I", tmp,
-               os.path.join(tmp, "trampoline.cpp"), "-o", so]
-        subprocess.check_call(cmd)
-    return {"so": os.path.basename(so), "params": params, "dtypes": list(dtypes), "has_rows": has_rows}
+        base = [CXX, "-O3", "-fopenmp", "-fPIC", "-shared", "-w", "-I", REF_DIR, "-I", tmp,
+                os.path.join(tmp, "trampoline.cpp")]
+        subprocess.check_call(base + ["-o", so])
+        ent = {"so": os.path.basename(so), "params": params, "dtypes": list(dtypes), "has_rows": has_rows}
+        if ir.name == "spmv":      # the graph the benchmark's CPU arm times
+            so3 = os.path.join(OUT_DIR, f"libref_{ir.name}_x86_64_v3.so")
+            subprocess.check_call(base + ["-march=x86-64-v3", "-o", so3])
+            ent["so_x86_64_v3"] = os.path.basename(so3)
+    return ent
 
 
 def build_all(force: bool = False) -> bool:
@@ -127,11 +148,12 @@ def build_all(force: bool = False) -> bool:
     for name, make in ALL_GRAPHS.items():
         ir = make()
         ent = manifest.get(name)
-        if (not force and ent and ent.get("digest") == ir.digest()
+        if (not force and ent and ent.get("digest") == ir.digest() and ent.get("recipe") == RECIPE
                 and os.path.exists(os.path.join(OUT_DIR, ent["so"]))):
             continue
         ent = build_graph(ir, GRAPH_DTYPES[name])
         ent["digest"] = ir.digest()
+        ent["recipe"] = RECIPE
         manifest[name] = ent
         changed = True
     if changed:

@@ -19,7 +19,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, n, iters, overlap, out_dir):
+def _worker(rank, world, port, n, iters, overlap, out_dir, graph=False):
     import torch.distributed as dist
     from flexspmv_b200 import multi_gpu
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -39,24 +39,34 @@ def _worker(rank, world, port, n, iters, overlap, out_dir):
     g.manual_seed(7)
     x_full = (torch.rand(n ** 3, generator=g, dtype=torch.float64) * 2 - 1)
     op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x_full[plan.row_begin:plan.row_end].to(dev), overlap=overlap)
-    for _ in range(iters):
-        op.step()
+    captured = None
+    if graph:
+        captured = op.capture_pair()          # runs one eager pair on the capture stream, then captures a pair
+        for _ in range((iters - 2) // 2):
+            op.step_pair()
+    else:
+        for _ in range(iters):
+            op.step()
     torch.cuda.synchronize()
-    torch.save({"rows": (plan.row_begin, plan.row_end), "y": op.owned().cpu()}, os.path.join(out_dir, f"rank{rank}.pt"))
+    op.ext.check()
+    torch.save({"rows": (plan.row_begin, plan.row_end), "y": op.owned().cpu(), "captured": captured,
+                "graph_error": op.graph_error}, os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
     os._exit(0)      # no communicator teardown: nothing is in flight and the results are on disk
 
 
-@pytest.mark.parametrize("overlap", [False, True])
-def test_two_ranks_match_one_gpu(overlap, tmp_path):
+@pytest.mark.parametrize("overlap,graph", [(False, False), (True, False), (False, True), (True, True)],
+                         ids=["eager", "eager-overlap", "graph", "graph-overlap"])
+def test_two_ranks_match_one_gpu(overlap, graph, tmp_path):
+    """Eager steps, and (graph) a captured pair of iterations replayed: the capture must succeed on both ranks."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from flexspmv_b200 import multi_gpu
     from flexspmv_b200.binding import load_builtin
-    n, iters = 48, 4
+    n, iters = 48, 6
     ctx = mp.get_context("spawn")
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, n, iters, overlap, str(tmp_path))) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, n, iters, overlap, str(tmp_path), graph)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
@@ -77,6 +87,8 @@ def test_two_ranks_match_one_gpu(overlap, tmp_path):
     for r in range(2):
         d = torch.load(os.path.join(str(tmp_path), f"rank{r}.pt"))
         got[d["rows"][0]:d["rows"][1]] = d["y"]
+        if graph:
+            assert d["captured"] is True, d["graph_error"]
     # rows that straddle a CTA boundary add their two partial sums in a different association when the
     # blocks (and so the CTA boundaries) differ: agreement to the fp64 parity tolerance, not bit for bit
     scale = float(ref.abs().max())

@@ -116,7 +116,13 @@ def test_partition_coordinates_bit_exact(bits, tile_items):
                                     tile_items, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(0))
         assert st == 0
         torch.cuda.synchronize()
-        assert np.array_equal(out.cpu().numpy().reshape(-1, 2), ref)
+        got = out.cpu().numpy().reshape(-1, 2)
+        assert np.array_equal(got, ref)
+        # and against the reference header's own MergePathSearch, called in the compiled reference object
+        from oracle import ref_run
+        if ref_run.available("spmv") and got.shape[0] <= 4000:
+            diagonals = np.minimum(np.arange(got.shape[0], dtype=np.int64) * tile_items, nr + nnz)
+            assert np.array_equal(got, ref_run.reference_merge_path_search(ro, diagonals))
 
 
 def test_row_blocks_bit_exact():
@@ -313,6 +319,82 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable():
     y.fill_(float("nan"))
     assert plan_and_launch(0) == 0                        # plan resets the status and the aid
     assert row_error(y.cpu().numpy(), ref[0], sums[0]) <= 1e-12
+
+
+def test_failed_launch_reaches_the_host_without_a_status_copy():
+    """The operator registers a page-locked int with every workspace it plans; a kernel that gives up stores its
+    status there.  `ext.check()` and the next call on that workspace raise; nothing on the launch path
+    synchronises.  A fresh plan (new row-offset tensor) works again."""
+    from flexspmv_b200.binding import FlexSpmvError
+    lib = load_library()
+    lib.flexspmv_debug_withhold_stage.restype = ctypes.c_int
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    prob = problems.random_problem(ir, 4000, 4000, 60000, seed=78, dtype=np.float64)
+    dev = torch.device("cuda:0")
+    vals, x = (torch.from_numpy(prob.values[k]).to(dev) for k in ("vals", "x"))
+    cols = torch.from_numpy(prob.indices["selector"]).to(dev)
+    ro = torch.from_numpy(prob.row_offsets).to(dev)
+    (want,) = ext.merged_spmv_launch(vals, x, cols, ro, prob.num_rows, prob.num_cols)
+    ext.check()                                            # nothing failed so far
+    plan = next(reversed(ext._plans.values()))
+    assert plan.status() == 0
+    assert lib.flexspmv_debug_withhold_stage(ctypes.c_void_p(plan.ws.data_ptr()), ctypes.c_uint32(5), None) == 0
+    ext.merged_spmv_launch(vals, x, cols, ro, prob.num_rows, prob.num_cols)     # enqueues; the wait runs out on the device
+    with pytest.raises(FlexSpmvError, match="bounded device-side wait"):
+        ext.check()
+    with pytest.raises(FlexSpmvError, match="outputs are undefined"):
+        ext.merged_spmv_launch(vals, x, cols, ro, prob.num_rows, prob.num_cols)
+    assert ext.device_status(torch.float64) == -6
+    ro2 = ro.clone()                                       # another tensor: another plan, another workspace
+    (again,) = ext.merged_spmv_launch(vals, x, cols, ro2, prob.num_rows, prob.num_cols)
+    torch.cuda.synchronize()
+    assert torch.equal(again, want)
+
+
+def test_edge_kernel_refuses_a_workspace_that_was_never_planned():
+    """The aggregator / map-only kernel checks the header like the tile kernel: on a zero-filled workspace it
+    raises FLEXSPMV_ERR_NOT_PLANNED, writes no output, and a planned workspace of another problem size is
+    refused the same way."""
+    lib = load_library()
+    for name in ("workspace_bytes", "plan", "launch", "device_status"):
+        getattr(lib, f"flexspmv_edge_sum_f32_{name}").restype = ctypes.c_int
+    dev = torch.device("cuda:0")
+    E, NV = 5000, 300
+    g = torch.Generator(device="cpu")
+    g.manual_seed(5)
+    ew = torch.rand(E, 2, generator=g).to(dev)
+    vx = torch.rand(NV, 2, generator=g).to(dev)
+    sel = torch.randint(0, NV, (E,), generator=g, dtype=torch.int32).to(dev)
+    prod = torch.full((E, 2), float("nan"), device=dev)
+    total = torch.full((2,), float("nan"), device=dev)
+    desc = Desc(0, E, NV, 32, 0, 0, 0)
+    nbytes = ctypes.c_size_t()
+    assert lib.flexspmv_edge_sum_f32_workspace_bytes(ctypes.byref(desc), ctypes.byref(nbytes)) == 0
+    ws = torch.zeros(nbytes.value, dtype=torch.uint8, device=dev)
+    wsp, nb = ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(nbytes.value)
+    vp = (ctypes.c_void_p * 2)(ew.data_ptr(), vx.data_ptr())
+    ip = (ctypes.c_void_p * 1)(sel.data_ptr())
+    op = (ctypes.c_void_p * 2)(prod.data_ptr(), total.data_ptr())
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def launch(d):
+        assert lib.flexspmv_edge_sum_f32_launch(ctypes.byref(d), vp, ip, None, op, wsp, nb, None) == 0
+        assert lib.flexspmv_edge_sum_f32_device_status(wsp, ctypes.c_void_p(status.data_ptr()), None) == 0
+        torch.cuda.synchronize()
+        return int(status.item())
+
+    assert launch(desc) == -7                              # FLEXSPMV_ERR_NOT_PLANNED
+    assert torch.isnan(prod).all() and torch.isnan(total).all()
+    assert lib.flexspmv_edge_sum_f32_plan(ctypes.byref(desc), None, wsp, nb, None) == 0
+    assert launch(desc) == 0
+    want = ew * vx[sel.long()]
+    assert torch.equal(prod, want)
+    assert torch.allclose(total, want.sum(dim=0), rtol=1e-5)
+    smaller = Desc(0, E - 1, NV, 32, 0, 0, 0)              # planned for E edges, launched for E - 1
+    prod.fill_(float("nan"))
+    assert launch(smaller) == -7
+    assert torch.isnan(prod).all()
 
 
 def test_rows_spanning_every_cta():

@@ -123,6 +123,25 @@ def test_tile_coordinates_and_row_blocks():
     assert per.max() - per.min() <= 2 * np.diff(ro).max()      # balanced up to one row
 
 
+def test_restated_search_equals_the_reference_headers_own_search():
+    """The tile coordinates of the restatement against the reference's free function MergePathSearch
+    (cpu_template/merged_spmv_template_reducer.h:27-51), called through the compiled reference object, for every
+    tile diagonal of several matrices (empty rows, rows spanning tiles, no rows, no edges)."""
+    from oracle import ref_run
+    if not ref_run.available("spmv"):
+        pytest.skip("oracle/_ref not built")
+    rng = np.random.default_rng(11)
+    for nr, nnz in ((1, 0), (1, 5), (37, 211), (500, 40), (3, 5000), (12314, 123134)):
+        ro = problems.random_cut_csr(nr, nnz, rng)
+        for tile in (5, 320, 896, 1280):
+            if (nr + nnz) // tile > 3000:
+                continue
+            ours = ir_eval.tile_coordinates(ro, tile)
+            diagonals = np.minimum(np.arange(ours.shape[0], dtype=np.int64) * tile, nr + nnz)
+            theirs = ref_run.reference_merge_path_search(ro, diagonals)
+            assert np.array_equal(ours, theirs), (nr, nnz, tile)
+
+
 def test_tensor_semantics_corner_cases():
     """guarded divide returns 0 on a zero divisor for equal widths and scalar/tensor, but the
     mixed-width broadcast and tensor/scalar divides are plain IEEE (data_struct_shared.cuh)."""

@@ -58,13 +58,18 @@ def _static_result(lib, desc, vals, x, cols, ro):
     st = lib.flexspmv_spmv_f64_launch_static(ctypes.byref(desc), _ptrs(vals, x), _ptrs(cols),
                                              ctypes.c_void_p(ro.data_ptr()), _ptrs(y), stream)
     assert st == 0, lib.flexspmv_error_string(st).decode()
+    # the error channel of this entry point: the status word of the built-in array
+    status = torch.full((1,), 99, dtype=torch.int32, device=vals.device)
+    assert lib.flexspmv_spmv_f64_static_device_status(ctypes.c_void_p(status.data_ptr()), stream) == 0
     torch.cuda.synchronize()
+    assert int(status.item()) == 0
     return y
 
 
 def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
     lib = load_library()
     lib.flexspmv_spmv_f64_launch_static.restype = ctypes.c_int
+    lib.flexspmv_spmv_f64_static_device_status.restype = ctypes.c_int
     ir = graphs.spmv_graph()
     first = problems.random_problem(ir, 20000, 20000, 300000, seed=21, dtype=np.float64)   # long and empty rows
     second = problems.poisson2d(96)                                                         # short rows, other size
@@ -75,6 +80,8 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
         got = _static_result(lib, desc, vals, x, cols, ro)
         assert not torch.isnan(got).any()
         assert torch.equal(got, expect)
+        flagged = Desc(prob.num_rows, prob.nnz, prob.num_cols, desc.offset_bits, 0, 0, 1)   # gather-window flag: ignored here
+        assert torch.equal(_static_result(lib, flagged, vals, x, cols, ro), expect)
 
 
 def test_static_scratch_entry_refuses_oversized_problems():
