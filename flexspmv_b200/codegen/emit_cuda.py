@@ -21,7 +21,7 @@ CTYPE = {"float32": ("float", "f32"), "float64": ("double", "f64"), "int64": ("l
 VBYTES = {"float32": 4, "float64": 8, "int64": 8}
 
 _BIN = {"add": "Add", "sub": "Sub", "mul": "Mul", "pow": "Pow", "truediv": "Div", "lt": "Lt", "gt": "Gt"}
-_CXX_OP = {"add": "+", "sub": "-", "mul": "*", "truediv": "/"}
+_SCALAR_FN = {"add": "vadd", "sub": "vsub", "mul": "vmul", "truediv": "vdiv"}
 
 
 class Var:
@@ -450,9 +450,9 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
                 b(f"    const auto {name} = fx::zip_sv({A.expr}, {B.expr}, fx::{opn}{{}});")
                 env[name] = Var("vec", B.dim, name)
             else:
-                if kind not in _CXX_OP or (A.kind == "lit" and B.kind == "lit"):
+                if kind not in _SCALAR_FN or (A.kind == "lit" and B.kind == "lit"):
                     raise ValueError(f"unsupported scalar-scalar op {kind}")
-                b(f"    const fx::Vec<V, 1> {name}{{{{ V({A.expr} {_CXX_OP[kind]} {B.expr}) }}}};")
+                b(f"    const fx::Vec<V, 1> {name}{{{{ fx::{_SCALAR_FN[kind]}(V({A.expr}), V({B.expr})) }}}};")
                 env[name] = Var("vec", 1, name)
         elif kind == "neg":
             A = operand(args[0])

@@ -4,7 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include "../../include/flexspmv.h"
+#include "flexspmv.h"   // the public C header (include/ of the project; the build passes -I for it)
 
 namespace flex {
 

@@ -15,9 +15,11 @@
 //   where3(c, x, y)    select on c != 0 with modulo broadcast (:425-449)
 //   norm(a)            sum of squares accumulated left to right, one sqrt (:346-353)
 //
-// No fast-math anywhere: + - * / sqrt are single IEEE operations, and the translation units that
-// include this header are compiled with -fmad=false so that a map chain evaluates exactly as the
-// reference's CPU code does (only the order of the per-row summation differs).
+// No fast-math anywhere: + - * / sqrt are single IEEE operations written with the round-to-nearest
+// intrinsics, which the compiler neither contracts into fused multiply-adds nor replaces by the
+// approximate forms of --use_fast_math, so a map chain evaluates exactly as the reference's CPU code
+// does whatever flags the translation unit is built with (only the order of the per-row summation
+// differs).  pow and exp are the CUDA math library's and do follow the build flags.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -44,19 +46,32 @@ __device__ __forceinline__ long long vpow(long long a, long long b) { return (lo
 __device__ __forceinline__ float vexp(float a) { return expf(a); }
 __device__ __forceinline__ double vexp(double a) { return exp(a); }
 __device__ __forceinline__ long long vexp(long long a) { return (long long)exp((double)a); }
-__device__ __forceinline__ float vsqrt(float a) { return sqrtf(a); }
-__device__ __forceinline__ double vsqrt(double a) { return sqrt(a); }
+__device__ __forceinline__ float vsqrt(float a) { return __fsqrt_rn(a); }
+__device__ __forceinline__ double vsqrt(double a) { return __dsqrt_rn(a); }
 __device__ __forceinline__ long long vsqrt(long long a) { return (long long)sqrt((double)a); }
 __device__ __forceinline__ float vabs(float a) { return fabsf(a); }
 __device__ __forceinline__ double vabs(double a) { return fabs(a); }
 __device__ __forceinline__ long long vabs(long long a) { return a < 0 ? -a : a; }
 
-struct Add { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return a + b; } };
-struct Sub { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return a - b; } };
-struct Mul { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return a * b; } };
-struct Div { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return a / b; } };
+__device__ __forceinline__ float vadd(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double vadd(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ long long vadd(long long a, long long b) { return a + b; }
+__device__ __forceinline__ float vsub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ double vsub(double a, double b) { return __dsub_rn(a, b); }
+__device__ __forceinline__ long long vsub(long long a, long long b) { return a - b; }
+__device__ __forceinline__ float vmul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double vmul(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ long long vmul(long long a, long long b) { return a * b; }
+__device__ __forceinline__ float vdiv(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ double vdiv(double a, double b) { return __ddiv_rn(a, b); }
+__device__ __forceinline__ long long vdiv(long long a, long long b) { return a / b; }
+
+struct Add { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return vadd(a, b); } };
+struct Sub { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return vsub(a, b); } };
+struct Mul { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return vmul(a, b); } };
+struct Div { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return vdiv(a, b); } };
 struct DivGuard {
-  template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return (b != V(0)) ? V(a / b) : V(0); }
+  template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return (b != V(0)) ? vdiv(a, b) : V(0); }
 };
 struct Pow { template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return vpow(a, b); } };
 // pow(a, 0.5) as one correctly rounded sqrt; the two IEEE special cases where pow and sqrt differ
@@ -64,7 +79,7 @@ struct Pow { template <typename V> __device__ __forceinline__ V operator()(V a, 
 struct PowHalf {
   template <typename V> __device__ __forceinline__ V operator()(V a, V) const {
     if (a == V(0)) return V(0);
-    if (a < V(0) && a * V(0.5) == a) return -a;   // -inf
+    if (a < V(0) && vmul(a, V(0.5)) == a) return -a;   // -inf
     return vsqrt(a);
   }
 };
@@ -126,7 +141,7 @@ template <typename V, int N>
 __device__ __forceinline__ V norm(const Vec<V, N>& a) {
   V s = V(0);
 #pragma unroll
-  for (int i = 0; i < N; ++i) s += a.v[i] * a.v[i];
+  for (int i = 0; i < N; ++i) s = vadd(s, vmul(a.v[i], a.v[i]));
   return vsqrt(s);
 }
 template <typename V, int N>
@@ -240,12 +255,12 @@ __device__ __forceinline__ void st_vec(V* p, const Vec<V, D>& a) {
 template <int OFF, typename V, int D>
 __device__ __forceinline__ void accumulate(V* acc, const Vec<V, D>& a) {
 #pragma unroll
-  for (int i = 0; i < D; ++i) acc[OFF + i] += a.v[i];
+  for (int i = 0; i < D; ++i) acc[OFF + i] = vadd(acc[OFF + i], a.v[i]);
 }
 template <int OFF, int D, typename V>
 __device__ __forceinline__ void accumulate_scalar(V* acc, V s) {
 #pragma unroll
-  for (int i = 0; i < D; ++i) acc[OFF + i] += s;
+  for (int i = 0; i < D; ++i) acc[OFF + i] = vadd(acc[OFF + i], s);
 }
 
 }  // namespace fx
