@@ -165,11 +165,15 @@ def _with_node_names(ir: GraphIR) -> GraphIR:
     return ir
 
 
-def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, static_scratch_bytes: int = 0) -> str:
+def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, static_scratch_bytes: int = 0,
+               windows: bool = True) -> str:
+    """One translation unit for ``ir`` compiled for ``dtype``.  ``windows=False`` leaves out the gather-window
+    variant of the tile kernel (half the kernel instantiations: the form the torch-extension shim is built in)."""
     ir = _with_node_names(ir)
     cty, sfx = CTYPE[dtype]
     symbol = symbol or f"{ir.name}_{sfx}"
-    cfg = tuple(config or _override(symbol) or TUNED_CONFIGS.get(symbol) or choose_config(ir, dtype))
+    # measured configurations are keyed by graph and value type, whatever symbol prefix the unit is emitted under
+    cfg = tuple(config or _override(symbol) or TUNED_CONFIGS.get(f"{ir.name}_{sfx}") or choose_config(ir, dtype))
     block, ipt, stages, min_ctas = cfg[:4]
     pipeline = len(cfg) > 4 and bool(cfg[4])     # fifth field: software-pipelined tiles (TileCfg::kPipeline)
     batch_override = cfg[5] if len(cfg) > 5 else 0   # sixth field: edges per register batch in the fused row mode
@@ -221,6 +225,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     w(f"// GENERATED by flexspmv_b200.codegen.emit_cuda -- graph '{ir.name}' ({dtype}), digest {ir.digest()}")
     w('#include "flex_graph_api.cuh"')
     w("namespace {")
+    w(f"namespace gen_{symbol} {{      // several generated units may share one translation unit")
     w("struct Graph {")
     w(f"  using V = {cty};")
     w(f"  static constexpr int kNumValues = {len(value_names)}, kNumIndices = {len(index_names)}, kNumOutputs = {len(ir.outputs)};")
@@ -537,9 +542,14 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     batch = batch_override or batch
     w(f"using Cfg = flex::TileCfg<{block}, {ipt}, {stages}, {min_ctas}, {batch}, {'true' if pipeline else 'false'}>;")
     wb_, wi_, ws_, wm_ = tuple(_override(symbol + "_win") or TUNED_WIN_CONFIGS.get(symbol) or (block, ipt, stages, min_ctas))[:4]
-    w(f"using CfgWin = flex::TileCfg<{wb_}, {wi_}, {ws_}, {wm_}, {batch}, false>;   // the gather-window variant of the kernel")
+    if windows:
+        w(f"using CfgWin = flex::TileCfg<{wb_}, {wi_}, {ws_}, {wm_}, {batch}, false>;   // the gather-window variant of the kernel")
+    else:
+        w("using CfgWin = flex::NoWindows;      // built without the gather-window variant of the kernel")
+    w(f"}}  // namespace gen_{symbol}")
     w("}  // namespace")
-    w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, Graph, Cfg, CfgWin)")
+    ns = f"gen_{symbol}::"
+    w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, {ns}Graph, {ns}Cfg, {ns}CfgWin)")
     if static_scratch_bytes:
-        w(f"FLEXSPMV_DEFINE_STATIC_SCRATCH_LAUNCH({symbol}, Graph, Cfg, {int(static_scratch_bytes)})")
+        w(f"FLEXSPMV_DEFINE_STATIC_SCRATCH_LAUNCH({symbol}, {ns}Graph, {ns}Cfg, {int(static_scratch_bytes)})")
     return "\n".join(L) + "\n"

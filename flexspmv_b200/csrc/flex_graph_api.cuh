@@ -97,7 +97,7 @@ struct GraphApi {
     if constexpr (G::kHasReducer) o->smem_bytes = TileSmemLayout<G, long long, Cfg>::kTotal;
     o->acc_dim = G::kHasReducer ? G::kAccDim : G::kAggDim;
     o->reserved = 0;
-    if constexpr (G::kHasReducer) o->reserved = G::kWindowGather ? 1 : 0;   // bit 0: the graph can use gather windows
+    if constexpr (G::kHasReducer) o->reserved = (G::kWindowGather && kWindowsBuilt) ? 1 : 0;   // bit 0: the graph can use gather windows
     return 0;
   }
 

@@ -1,6 +1,7 @@
 """Front-end pieces that sit above the operator: the tracer equivalent (driven with stand-ins for the
 absent ``easier`` package), the reference-named codegen entry points and the runtime wrapper."""
 import operator
+import os
 
 import numpy as np
 import pytest
@@ -9,7 +10,7 @@ import torch.fx
 import torch.nn as nn
 
 from flexspmv_b200 import graphs
-from flexspmv_b200.codegen import emit_cuda, merged_gen_gpu
+from flexspmv_b200.codegen import emit_cuda, merged_gen_binding, merged_gen_gpu
 from flexspmv_b200.python_wrapper.dynamic_replace_submodule import (DynamicCudaWrapper, coo_rows_to_csr_ptr,
                                                                     dynamic_replace_submodule)
 from flexspmv_b200.trace.graph_trace import classify_op, trace_graph
@@ -86,7 +87,7 @@ def test_classify_op_follows_the_reference_table():
 def test_generate_sources_from_ir(tmp_path):
     paths = merged_gen_gpu.generate_cuda_code_from_ir(graphs.spring_mass_graph(), ("float32",), str(tmp_path))
     text = open(paths[0]).read()
-    assert "FLEXSPMV_DEFINE_GRAPH(spring_mass_f32, Graph, Cfg, CfgWin)" in text and "kGatherNeedsRow = true" in text
+    assert "FLEXSPMV_DEFINE_GRAPH(spring_mass_f32, gen_spring_mass_f32::Graph," in text and "kGatherNeedsRow = true" in text
 
 
 def test_coo_rows_to_csr_ptr():
@@ -132,3 +133,20 @@ def test_wrapper_marshals_arguments_in_operator_order():
     assert a_ro.dtype == torch.int32 and a_ro.tolist() == [0, 2, 3, 3, 6]
     assert (n_rows, n_cols) == (4, 4)
     assert not dynamic_replace_submodule(eqn, ext, "no_such_node")
+
+
+def test_generated_binding_source_follows_the_reference_contract(tmp_path):
+    """No GPU work: the emitted text has the operator's positional order and keyword names, the output shapes of
+    every output kind, and no per-call allocation of scratch."""
+    ir = graphs.mixed_dims_graph()
+    path = merged_gen_binding.generate_binding_code(str(tmp_path), ir.inputs, ir.outputs, ir.selector_register,
+                                                    ir.map_operations, ir.reducer_operations, ir.aggregator_operations,
+                                                    name=ir.name, dtypes=("float32", "int64"))
+    text = open(path).read()
+    order = [text.index(f'py::arg("{n}")') for n in ("ea", "eb", "vx", "s0_idx", "s1_idx", "row_end_offsets", "num_rows", "num_cols")]
+    assert order == sorted(order)
+    assert "torch::empty({num_rows, 2}" in text and "torch::empty({num_rows, 6}" in text and "torch::empty({ne, 2}" in text
+    assert "case torch::kLong" in text and "case torch::kDouble" not in text
+    assert "cudaMalloc" not in text and "cudaFree" not in text
+    for f in ("flexspmv.h", "flex_tile_kernel.cuh", "merged_graph_merged_mixed_dims_f32.cuh", "merged_graph_merged_mixed_dims_i64.cuh"):
+        assert os.path.exists(os.path.join(str(tmp_path), "include", f))
