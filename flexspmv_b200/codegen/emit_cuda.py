@@ -98,7 +98,8 @@ def smem_bytes(ir: GraphIR, dtype: str, block: int, ipt: int, stages: int) -> in
         + vb * acc * (block // 32) + vb * acc * 2 + 16 + 8 * 16 + 128
     needs_row = any(s_.get("selector") == 1 and s_.get("row_identity") for s_ in ir.selector_register)
     buffers = 1   # 2 only when the kernel is built with tile pipelining (TileCfg::kPipeline)
-    return fixed + 4 * (tile + 1) * buffers + (2 * tile if needs_row else 0) + vb * acc * tile * buffers + stages * stage
+    # row-mode graphs reduce in registers: no product buffer
+    return fixed + 4 * (tile + 1) * buffers + (0 if needs_row else vb * acc * tile * buffers) + stages * stage
 
 
 def choose_config(ir: GraphIR, dtype: str) -> Tuple[int, int, int, int]:

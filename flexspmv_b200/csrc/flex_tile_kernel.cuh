@@ -8,8 +8,8 @@
 //   row sums its products and stores the row; rows longer than kShortRowMax are summed by whole warps.
 //   Row-mode graphs (a selector equals the row id: spring-mass, fluxes): in tiles without long rows one
 //   thread per row loads the row's own record once, gathers and maps its edges in register batches and
-//   stores the row; tiles with long rows record the row of every edge, run the two phases and combine
-//   the per-thread partial sums with a warp-shuffle segmented scan and a cross-warp fold.
+//   stores the row; in tiles with a long row whole warps take the rows one at a time (lanes 32 edges
+//   apart, shuffle tree).  Nothing of a row-mode graph passes through a shared-memory product buffer.
 // The carry of a row that spans tiles travels inside the CTA in shared memory; the only cross-CTA state
 // is one carry per CTA, folded in by the last CTA to finish (ticket counter), in CTA order.  No atomics
 // on the output, no pre-zeroed output, run-to-run deterministic.
@@ -113,9 +113,12 @@ struct TileSmemLayout {
   static constexpr int kOffLong = int(align_up(kOffFlag + 16, 16));
   static constexpr int kBuffers = (!G::kGatherNeedsRow && Cfg::kPipeline) ? 2 : 1;   // s_rel / s_prod / long-row list double-buffered when tiles are pipelined
   static constexpr int kOffRel = int(align_up(kOffLong + 4 * (4 + kMaxLong * kBuffers), 16));
-  static constexpr int kOffRowId = int(align_up(kOffRel + 4 * (Cfg::kTile + 1) * kBuffers, 16));
-  static constexpr int kOffProd = int(align_up(kOffRowId + (G::kGatherNeedsRow ? 2 * Cfg::kTile : 0), 16));
-  static constexpr int kOffStages = int(align_up(kOffProd + sizeof(V) * kAcc * Cfg::kTile * kBuffers, 128));
+  // Row-mode graphs (a selector equals the row id) reduce in registers in every tile: no product buffer.  The
+  // shared memory a kernel does not claim stays L1 cache, and the number of gather misses an SM can have in
+  // flight grows with that cache (measured on B200: 63 / 130 / 183 / 225 / 265 G random 4-byte gathers per
+  // second at 228 / 196 / 164 / 132 / <= 32 KB of shared memory per SM).
+  static constexpr int kOffProd = int(align_up(kOffRel + 4 * (Cfg::kTile + 1) * kBuffers, 16));
+  static constexpr int kOffStages = int(align_up(kOffProd + (G::kGatherNeedsRow ? 0 : sizeof(V) * kAcc * Cfg::kTile * kBuffers), 128));
   static constexpr int kTotal = kOffStages + kStageBytes * Cfg::kStages;
 };
 
@@ -187,7 +190,6 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   int* s_nlong = reinterpret_cast<int*>(smem + L::kOffLong);
   int* s_long = s_nlong + 4;
   int* s_rel = reinterpret_cast<int*>(smem + L::kOffRel);
-  unsigned short* s_rowid = reinterpret_cast<unsigned short*>(smem + L::kOffRowId);
   V* s_prod = reinterpret_cast<V*>(smem + L::kOffProd);
   unsigned char* s_stage = smem + L::kOffStages;
 
@@ -459,7 +461,6 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (i * BLOCK + tid < t.nnz) {
-        if constexpr (G::kGatherNeedsRow) G::gather_row(p, t.row0 + s_rowid[i * BLOCK + tid], gr[i]);
 #ifndef FLEX_EXP_SKIP_GATHER
         G::gather_edge(p, er[i], ge[i]);
 #else
@@ -761,7 +762,11 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       if (!acquire(k, t, tile, rend)) { failed = true; break; }
       last_row1 = t.row0 + t.nrows;
       const bool my_long = convert(t, rend, s_rel, -1);
+#ifdef FLEX_FORCE_EDGE_PARALLEL
+      const bool long_tile = named_bar_or(1, BLOCK, true);      // experiment: every tile takes the edge-parallel path
+#else
       const bool long_tile = named_bar_or(1, BLOCK, my_long);   // [R] s_rel complete, tile classified
+#endif
       if (!long_tile) {
         // short rows: one thread per row does gather + map + sum in registers (the row's own vertex data is
         // loaded once) and stores the row; local row 0 continues the CTA's carry, local row `nrows`
@@ -794,31 +799,44 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
         release(k);
         continue;
       }
-      // long rows: each thread walks its merge-path span once and records the row of every edge
-      int xs, ys, n_items;
-      thread_span(t, s_rel, xs, ys, n_items);
-      {
-        int row = xs, nz = ys, re = s_rel[xs];
+      // a tile with a long row: whole warps take the rows one at a time -- every lane holds the row's own record,
+      // lanes map edges 32 apart, a shuffle tree folds the lanes' partial sums (no shared-memory buffers)
+      for (int r = warp; r <= t.nrows; r += Cfg::kWarps) {
+        const int lo = r ? s_rel[r - 1] : 0;
+        const int hi = r < t.nrows ? s_rel[r] : t.nnz;
+        V sum[kAcc];
 #pragma unroll
-        for (int i = 0; i < IPT; ++i) {
-          if (i < n_items) {
-            if (nz < re) { s_rowid[nz] = (unsigned short)row; ++nz; }
-            else { ++row; re = s_rel[row]; }
+        for (int j = 0; j < kAcc; ++j) sum[j] = V(0);
+        if (lo < hi) {
+          typename G::GRow grow;
+          G::gather_row(p, t.row0 + r, grow);
+          for (int e = lo + lane; e < hi; e += 32) {
+            typename G::EReg er;
+            typename G::GEdge ge;
+            G::load_edge(p, tile, e, t.nz0 + e, er);
+            G::gather_edge(p, er, ge);
+            G::map(p, er, t.nz0 + e, grow, ge, sum);
+          }
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) sum[j] += shfl_down_any(sum[j], off);
+          }
+        }
+        if (lane == 0) {
+          if (r == 0) {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) sum[j] = s_carry[(k & 1) * kAcc + j] + sum[j];
+          }
+          if (r < t.nrows) {
+            store_row(t.row0 + r, sum);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) s_carry[((k + 1) & 1) * kAcc + j] = sum[j];
           }
         }
       }
-      named_bar_sync(1, BLOCK);   // [W] s_rowid complete
-      {
-        typename G::EReg er[IPT];
-        typename G::GEdge ge[IPT];
-        typename G::GRow gr[IPT];
-        map_load(t, tile, er);
-        release(k);
-        map_gather(t, er, ge, gr);
-        map_products(t, er, ge, gr, s_prod);
-      }
-      named_bar_sync(1, BLOCK);   // [P] products complete
-      reduce_long(t, k & 1, s_prod, s_rel, xs, ys, n_items);
+      release(k);
     }
   }
 

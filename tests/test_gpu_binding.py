@@ -62,8 +62,10 @@ def test_generated_binding_builds_and_matches(gname, dt, make):
     torch.cuda.synchronize()
     assert all(torch.equal(a, b) for a, b in zip(outs, outs64))
     # the checks of the reference binding, and the dtype that is not compiled raises instead of falling through
-    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+    with pytest.raises(RuntimeError, match="CUDA device required"):
         ext.merged_spmv_launch(vals[0].cpu(), *vals[1:], *idxs, ro, prob.num_rows, prob.num_cols)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        ext.merged_spmv_launch(*vals[:-1], vals[-1].cpu(), *idxs, ro, prob.num_rows, prob.num_cols)
     with pytest.raises(RuntimeError, match="dtype mismatch"):
         ext.merged_spmv_launch(*vals, *[i.long() for i in idxs], ro, prob.num_rows, prob.num_cols)
     other = torch.float32 if dt == "float64" else torch.float64
