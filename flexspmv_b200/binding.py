@@ -133,8 +133,15 @@ class GraphExtension:
     PLAN_CACHE_ENTRIES = 8
 
     def __init__(self, ir: GraphIR, lib_path: Optional[str] = None, symbol_prefix: Optional[str] = None,
-                 tile_items: int = 0, max_ctas: int = 0, gather_windows: Optional[bool] = None):
-        """``gather_windows``: plan column segments per tile so that the kernel gathers from shared memory
+                 tile_items: int = 0, max_ctas: int = 0, gather_windows: Optional[bool] = None,
+                 random_gather: Optional[bool] = None):
+        """``random_gather``: run the kernel for matrices whose columns have no locality (include/flexspmv.h,
+        FLEXSPMV_FLAG_RANDOM_GATHER), for graphs built with it.  None = decide per matrix the first time it is
+        planned, from a sample of its index array (one device-to-host read, at plan time only): the flag is set
+        when 32 consecutive edges gather from more than 16 different cache lines on average.  The environment
+        variable FLEXSPMV_RANDOM_GATHER=0/1 overrides None.
+
+        ``gather_windows``: plan column segments per tile so that the kernel gathers from shared memory
         (include/flexspmv.h, FLEXSPMV_FLAG_GATHER_WINDOWS), for graphs that support it; None = off unless the
         environment variable FLEXSPMV_GATHER_WINDOWS is 1.  Costs 2 bytes of workspace per edge and a longer
         first call per matrix; results are bit-identical for equal tile size and CTA count.  Measured on B200:
@@ -146,6 +153,12 @@ class GraphExtension:
         if gather_windows is None:
             gather_windows = os.environ.get("FLEXSPMV_GATHER_WINDOWS", "0") == "1"
         self.gather_windows = bool(gather_windows)
+        if random_gather is None and os.environ.get("FLEXSPMV_RANDOM_GATHER") in ("0", "1"):
+            random_gather = os.environ["FLEXSPMV_RANDOM_GATHER"] == "1"
+        self.random_gather = random_gather
+        self._locality: Dict[tuple, bool] = {}
+        edge_sel = [s_ for s_ in ir.selector_register if s_.get("selector") == 1 and not s_.get("row_identity")]
+        self._gather_dim = dim_of(edge_sel[0]["shape"]) if edge_sel else 1
         self.lib = load_library(lib_path)
         self.prefix = symbol_prefix or ir.name
         self.tile_items, self.max_ctas = int(tile_items), int(max_ctas)
@@ -179,13 +192,39 @@ class GraphExtension:
             raise TypeError(f"merged_spmv_launch() got unexpected keyword arguments {sorted(extra)}")
         return vals
 
-    def _flags(self, syms: _Symbols) -> int:
-        return 1 if (self.gather_windows and (syms.graph_info.reserved & 1)) else 0
+    def _looks_random(self, idx: torch.Tensor, record_bytes: int) -> bool:
+        """Whether 32 consecutive edges of a sample from the middle of the index array gather from more than 16
+        different 128-byte cache lines on average.  Small matrices never qualify: they are latency-bound and the
+        staged kernel serves them."""
+        n = idx.numel()
+        if n < (1 << 20):
+            return False
+        key = (idx.data_ptr(), idx._version, n)
+        hit = self._locality.get(key)
+        if hit is None:
+            m = min(n, 1 << 18) // 32 * 32
+            start = (n - m) // 2 // 32 * 32
+            lines = (idx[start:start + m].view(-1, 32).long() * record_bytes) >> 7
+            lines = lines.sort(dim=1).values
+            distinct = 1 + (lines[:, 1:] != lines[:, :-1]).sum(dim=1)
+            hit = bool(float(distinct.float().mean().item()) > 16.0)
+            if len(self._locality) > 64:
+                self._locality.clear()
+            self._locality[key] = hit
+        return hit
 
-    def _desc(self, syms: _Symbols, values, row_end_offsets, num_rows: int, num_edges: int, num_cols: int) -> Desc:
+    def _flags(self, syms: _Symbols, values=(), indices=()) -> int:
+        flags = 1 if (self.gather_windows and (syms.graph_info.reserved & 1)) else 0
+        if (syms.graph_info.reserved & 2) and self.random_gather is not False and len(indices):
+            if self.random_gather or self._looks_random(indices[0], self._gather_dim * values[0].element_size()):
+                flags = 2
+        return flags
+
+    def _desc(self, syms: _Symbols, values, row_end_offsets, num_rows: int, num_edges: int, num_cols: int,
+              indices=()) -> Desc:
         has_red = self.ir.has_reducer
-        flags = self._flags(syms)
-        if flags:      # the windows are bounded by the gathered array's length: take it from the tensor itself
+        flags = self._flags(syms, values, indices)
+        if flags & 1:      # the windows are bounded by the gathered array's length: take it from the tensor itself
             num_cols = int(values[len(self.non_gather)].shape[0])
         return Desc(num_rows if has_red else 0, num_edges, num_cols,
                     64 if (has_red and row_end_offsets.dtype == torch.int64) else 32,
@@ -195,10 +234,10 @@ class GraphExtension:
                    indices: Sequence[torch.Tensor] = ()) -> "_Plan":
         # a workspace holds per-launch state (ticket, carries): launches that may overlap on the GPU must not
         # share one, so the plan is cached per stream as well as per matrix
-        key = (id(syms), desc.num_rows, desc.num_edges, desc.offset_bits, desc.tile_items, desc.max_ctas,
+        key = (id(syms), desc.num_rows, desc.num_edges, desc.offset_bits, desc.tile_items, desc.max_ctas, desc.reserved,
                (ro.data_ptr(), ro._version) if ro is not None else None, device.index,
                torch.cuda.current_stream(device).cuda_stream,
-               tuple((t.data_ptr(), t._version) for t in indices) if desc.reserved else None)
+               tuple((t.data_ptr(), t._version) for t in indices) if (desc.reserved & 1) else None)
         hit = self._plans.get(key)
         if hit is not None:
             self._plans.move_to_end(key)
@@ -209,14 +248,14 @@ class GraphExtension:
         check(self.lib, syms.plan(ctypes.byref(desc), ctypes.c_void_p(ro.data_ptr() if ro is not None else 0),
                                   ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(nbytes.value), _stream_ptr()),
               "plan")
-        if desc.reserved:      # gather windows: the second planning step reads the index array
+        if desc.reserved & 1:      # gather windows: the second planning step reads the index array
             ip = (ctypes.c_void_p * max(len(indices), 1))(*[t.data_ptr() for t in indices])
             check(self.lib, syms.plan_windows(ctypes.byref(desc), ip, ctypes.c_void_p(ws.data_ptr()),
                                               ctypes.c_size_t(nbytes.value), _stream_ptr()), "plan_windows")
             self.launches += 2
         self.launches += 2 if ro is not None else 1
         # keep the row-offset tensor alive so its address cannot be recycled under a cached plan
-        plan = _Plan(ws, nbytes.value, (ro, tuple(indices) if desc.reserved else None))
+        plan = _Plan(ws, nbytes.value, (ro, tuple(indices) if (desc.reserved & 1) else None))
         check(self.lib, self.lib.flexspmv_workspace_status_mirror(ctypes.c_void_p(ws.data_ptr()),
                                                                   ctypes.c_void_p(plan.flag.data_ptr()), _stream_ptr()),
               "workspace_status_mirror")
@@ -259,7 +298,7 @@ class GraphExtension:
             if row_end_offsets.numel() != num_rows + 1:
                 raise FlexSpmvError("row_end_offsets must have length num_rows + 1")
         device = dispatch.device
-        desc = self._desc(syms, values, row_end_offsets, num_rows, ne, num_cols)
+        desc = self._desc(syms, values, row_end_offsets, num_rows, ne, num_cols, indices)
         outputs: List[torch.Tensor] = []
         for o in self.ir.outputs:
             d = dim_of(o["shape"])
@@ -300,7 +339,7 @@ class GraphExtension:
         syms = self.symbols(dt)
         has_red = self.ir.has_reducer
         device = values[0].device
-        desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols)
+        desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols, indices)
         with torch.cuda.device(device):
             plan = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
             _raise_if_failed(self.lib, plan, "launch_into")
@@ -327,7 +366,7 @@ class GraphExtension:
         syms = self.symbols(dt)
         has_red = self.ir.has_reducer
         device = values[0].device
-        desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols)
+        desc = self._desc(syms, values, row_end_offsets, num_rows, num_edges, num_cols, indices)
         with torch.cuda.device(device):
             plan = self._workspace(syms, desc, row_end_offsets if has_red else None, device, indices)
         return PreparedLaunch(self, syms, desc, list(values), list(indices), row_end_offsets if has_red else None,

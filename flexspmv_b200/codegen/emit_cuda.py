@@ -134,6 +134,24 @@ TUNED_CONFIGS = {
 }
 
 
+# Configuration of the warp kernel for matrices whose gathers have no locality (csrc/flex_warp_kernel.cuh):
+# (threads per CTA, merge items per lane, min CTAs per SM).  It is built for graphs whose gathers all depend on the
+# edge and whose accumulator is at most 16 bytes wide (its one shared-memory buffer holds a product per item, and
+# the point of the kernel is to leave the shared-memory / L1 array to the gathers).
+LEAN_CONFIG = (256, 5, 4)
+TUNED_LEAN_CONFIGS = {
+}
+
+
+def lean_eligible(ir: GraphIR, dtype: str) -> bool:
+    if not ir.has_reducer or ir.aggregator_operations:
+        return False
+    if any(s_.get("selector") == 1 and s_.get("row_identity") for s_ in ir.selector_register):
+        return False
+    acc = sum(dim_of(o["shape"]) for o in ir.outputs if str(o["target"]) == "reducer")
+    return acc * VBYTES[dtype] <= 16
+
+
 # Tile configurations of the gather-window variant (its stages also hold the window area).
 TUNED_WIN_CONFIGS = {
 }
@@ -547,10 +565,15 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
         w(f"using CfgWin = flex::TileCfg<{wb_}, {wi_}, {ws_}, {wm_}, {batch}, false>;   // the gather-window variant of the kernel")
     else:
         w("using CfgWin = flex::NoWindows;      // built without the gather-window variant of the kernel")
+    if lean_eligible(ir, dtype):
+        lb, li, lm = tuple(_override(symbol + "_lean") or TUNED_LEAN_CONFIGS.get(f"{ir.name}_{sfx}") or LEAN_CONFIG)[:3]
+        w(f"using CfgLean = flex::WarpCfg<{lb}, {li}, {lm}>;      // the warp kernel for matrices with random columns")
+    else:
+        w("using CfgLean = flex::NoLean;")
     w(f"}}  // namespace gen_{symbol}")
     w("}  // namespace")
     ns = f"gen_{symbol}::"
-    w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, {ns}Graph, {ns}Cfg, {ns}CfgWin)")
+    w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, {ns}Graph, {ns}Cfg, {ns}CfgWin, {ns}CfgLean)")
     if static_scratch_bytes:
         w(f"FLEXSPMV_DEFINE_STATIC_SCRATCH_LAUNCH({symbol}, {ns}Graph, {ns}Cfg, {int(static_scratch_bytes)})")
     return "\n".join(L) + "\n"

@@ -11,6 +11,7 @@
 #include "flex_common.cuh"
 #include "flex_edge_kernel.cuh"
 #include "flex_tile_kernel.cuh"
+#include "flex_warp_kernel.cuh"
 
 namespace flex {
 
@@ -29,9 +30,14 @@ struct NoWindows {   // in place of CfgWin: the gather-window variant of the ker
   static constexpr int kTile = 0;
 };
 
-template <class G, class Cfg, class CfgWin = Cfg>
+struct NoLean {      // in place of CfgLean: the warp kernel for matrices with random columns is not built
+  static constexpr int kChunk = 0;
+};
+
+template <class G, class Cfg, class CfgWin = Cfg, class CfgLean = NoLean>
 struct GraphApi {
   static constexpr bool kWindowsBuilt = !std::is_same_v<CfgWin, NoWindows>;
+  static constexpr bool kLeanBuilt = !std::is_same_v<CfgLean, NoLean>;
   using V = typename G::V;
   static constexpr int kEdgeBlock = 256, kEdgeIpt = 4;
   // Row-mode graphs run one thread per row, the trailing partial row of the tile included: on a mesh with
@@ -45,13 +51,23 @@ struct GraphApi {
     if constexpr (G::kHasReducer && kWindowsBuilt) return G::kWindowGather && (d->reserved & FLEXSPMV_FLAG_GATHER_WINDOWS) != 0;
     return false;
   }
-  static int compiled_tile(const flexspmv_desc* d) { return use_win(d) ? CfgWin::kTile : Cfg::kTile; }
+  // The warp kernel (flex_warp_kernel.cuh) is used when it was built for the graph and the caller says that the
+  // gathers have no locality; it wins over the gather windows when both flags are set.
+  static bool use_lean(const flexspmv_desc* d) {
+    if constexpr (G::kHasReducer && kLeanBuilt) return (d->reserved & FLEXSPMV_FLAG_RANDOM_GATHER) != 0;
+    return false;
+  }
+  static int compiled_tile(const flexspmv_desc* d) {
+    if (use_lean(d)) return CfgLean::kChunk;
+    return use_win(d) ? CfgWin::kTile : Cfg::kTile;
+  }
   // The tile kernel's shared-memory carve-up is compiled for Cfg::kTile items; a smaller tile is allowed
   // (tests exercise odd sizes), a larger one is not.  (Shrinking the default tile on small problems until every
   // CTA gets the same number of tiles was measured on B200 and changed nothing: 13.1 us against 13.0 us per
   // launch on the 2-D Poisson 512^2 matrix.)
   static int tile_items(const flexspmv_desc* d) {
     if (d->tile_items > 0) return d->tile_items;
+    if (use_lean(d)) return CfgLean::kChunk;
     return use_win(d) ? CfgWin::kTile : kDefaultTile;
   }
   static int max_ctas(const flexspmv_desc* d, int resident) {
@@ -76,11 +92,12 @@ struct GraphApi {
     const uint64_t pair = (d->offset_bits == 64 ? 16u : 8u);
     h.coords_offset = sizeof(WorkspaceHeader);
     h.carry_row_offset = align_up(h.coords_offset + (uint64_t)(tiles + 1) * pair, 256);
-    h.carry_val_offset = align_up(h.carry_row_offset + (uint64_t)kMaxCtas * 8u, 256);
+    const uint64_t carries = use_lean(d) ? kMaxWarpCarries : kMaxCtas;      // one carry per CTA, or per warp
+    h.carry_val_offset = align_up(h.carry_row_offset + carries * 8u, 256);
     const int width = G::kHasReducer ? G::kAccDim : (G::kAggDim > 0 ? G::kAggDim : 1);
-    h.total_bytes = align_up(h.carry_val_offset + (uint64_t)kMaxCtas * width * sizeof(V), 256);
+    h.total_bytes = align_up(h.carry_val_offset + carries * width * sizeof(V), 256);
     h.win_table_offset = h.win_index_offset = 0;
-    if (use_win(d)) {
+    if (use_win(d) && !use_lean(d)) {
       h.win_table_offset = h.total_bytes;
       h.win_index_offset = align_up(h.win_table_offset + (uint64_t)tiles * kWinEntryInts * 4u, 256);
       h.total_bytes = align_up(h.win_index_offset + (uint64_t)d->num_edges * 2u, 256);
@@ -97,7 +114,8 @@ struct GraphApi {
     if constexpr (G::kHasReducer) o->smem_bytes = TileSmemLayout<G, long long, Cfg>::kTotal;
     o->acc_dim = G::kHasReducer ? G::kAccDim : G::kAggDim;
     o->reserved = 0;
-    if constexpr (G::kHasReducer) o->reserved = (G::kWindowGather && kWindowsBuilt) ? 1 : 0;   // bit 0: the graph can use gather windows
+    // bit 0: the graph can use gather windows, bit 1: the warp kernel for random columns is built
+    if constexpr (G::kHasReducer) o->reserved = ((G::kWindowGather && kWindowsBuilt) ? 1 : 0) | (kLeanBuilt ? 2 : 0);
     return 0;
   }
 
@@ -179,12 +197,59 @@ struct GraphApi {
     return (int)cudaGetLastError();
   }
 
+  template <typename OffsetT>
+  static int launch_lean(const flexspmv_desc* d, const typename G::Params& p, const void* row_offsets, void* ws,
+                         const WorkspaceHeader& h, cudaStream_t st) {
+    if constexpr (G::kHasReducer && kLeanBuilt) {
+      auto kernel = flex_warp_kernel<G, OffsetT, CfgLean>;
+      constexpr int kSmem = CfgLean::kWarps * G::kAccDim * CfgLean::kChunk * int(sizeof(V));
+      constexpr int kMaxDevices = 64;
+      static std::mutex mu;
+      static int resident_of[kMaxDevices] = {};      // 0: not initialised yet
+      int dev = 0;
+      if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return (int)e;
+      if (dev < 0 || dev >= kMaxDevices) return FLEXSPMV_ERR_BAD_ARG;
+      int resident = 0;
+      {
+        std::lock_guard<std::mutex> lock(mu);
+        if (resident_of[dev] == 0) {
+          cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+          int r = 0;
+          if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, kernel, CfgLean::kBlock, kSmem);
+          if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
+          resident_of[dev] = r < 1 ? -1 : r;
+        }
+        resident = resident_of[dev];
+      }
+      if (resident < 1) return FLEXSPMV_ERR_TOO_LARGE;
+      const long long chunks = h.num_tiles;
+      if (chunks == 0) return 0;
+      long long grid = d->max_ctas > 0 ? d->max_ctas : (long long)device_sm_count() * resident;
+      const long long need = (chunks + CfgLean::kWarps - 1) / CfgLean::kWarps;
+      if (grid > need) grid = need;
+      if (grid > kMaxWarpCarries / CfgLean::kWarps) grid = kMaxWarpCarries / CfgLean::kWarps;
+      if (grid < 1) grid = 1;
+      WarpKernelArgs a;
+      a.row_offsets = row_offsets;
+      a.coords = static_cast<char*>(ws) + h.coords_offset;
+      a.header = static_cast<WorkspaceHeader*>(ws);
+      a.carry_row = reinterpret_cast<long long*>(static_cast<char*>(ws) + h.carry_row_offset);
+      a.carry_val = static_cast<char*>(ws) + h.carry_val_offset;
+      a.num_rows = d->num_rows; a.num_edges = d->num_edges; a.num_chunks = chunks;
+      kernel<<<(unsigned)grid, CfgLean::kBlock, kSmem, st>>>(p, a);
+      return (int)cudaGetLastError();
+    } else {
+      (void)d; (void)p; (void)row_offsets; (void)ws; (void)h; (void)st;
+      return FLEXSPMV_ERR_BAD_ARG;
+    }
+  }
+
   // Second planning step for descriptors with FLEXSPMV_FLAG_GATHER_WINDOWS (after plan, same workspace): reads the
   // index array of the graph's one gather and fills the per-tile segment table and the per-edge positions.
   // Until it has run, a launch treats every tile as having no windows.
   static int plan_windows(const flexspmv_desc* d, const void* const* indices, void* ws, size_t ws_bytes, cudaStream_t st) {
     if (int e = check_desc(d)) return e;
-    if (!use_win(d)) return 0;          // nothing to do for graphs / descriptors without windows
+    if (!use_win(d) || use_lean(d)) return 0;          // nothing to do for graphs / descriptors without windows
     if constexpr (G::kHasReducer && G::kWindowGather && kWindowsBuilt) {
       if (!ws) return FLEXSPMV_ERR_WORKSPACE;
       if (!indices || !indices[0]) return FLEXSPMV_ERR_BAD_ARG;
@@ -217,6 +282,10 @@ struct GraphApi {
     if constexpr (G::kHasReducer) {
       if (!row_offsets) return FLEXSPMV_ERR_BAD_ARG;
       if (!aligned16(row_offsets)) return FLEXSPMV_ERR_ALIGN;
+      if (use_lean(d)) {
+        if (d->offset_bits == 64) return launch_lean<long long>(d, p, row_offsets, ws, h, st);
+        return launch_lean<int>(d, p, row_offsets, ws, h, st);
+      }
       if constexpr (G::kWindowGather && kWindowsBuilt) {
         if (use_win(d)) {
           if (d->offset_bits == 64) return launch_tiles<long long, CfgWin, true>(d, p, row_offsets, ws, h, st);
@@ -250,24 +319,24 @@ struct GraphApi {
 
 }  // namespace flex
 
-#define FLEXSPMV_DEFINE_GRAPH(SYM, GRAPH, CFG, CFGWIN)                                                          \
+#define FLEXSPMV_DEFINE_GRAPH(SYM, GRAPH, CFG, CFGWIN, CFGLEAN)                                                          \
   extern "C" {                                                                                                  \
-  int flexspmv_##SYM##_info(flexspmv_graph_info* info) { return flex::GraphApi<GRAPH, CFG, CFGWIN>::info(info); } \
+  int flexspmv_##SYM##_info(flexspmv_graph_info* info) { return flex::GraphApi<GRAPH, CFG, CFGWIN, CFGLEAN>::info(info); } \
   int flexspmv_##SYM##_workspace_bytes(const flexspmv_desc* d, size_t* b) {                                     \
-    return flex::GraphApi<GRAPH, CFG, CFGWIN>::workspace_bytes(d, b);                                           \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN, CFGLEAN>::workspace_bytes(d, b);                                           \
   }                                                                                                             \
   int flexspmv_##SYM##_plan(const flexspmv_desc* d, const void* ro, void* ws, size_t wb, void* st) {            \
-    return flex::GraphApi<GRAPH, CFG, CFGWIN>::plan(d, ro, ws, wb, static_cast<cudaStream_t>(st));              \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN, CFGLEAN>::plan(d, ro, ws, wb, static_cast<cudaStream_t>(st));              \
   }                                                                                                             \
   int flexspmv_##SYM##_plan_windows(const flexspmv_desc* d, const void* const* ix, void* ws, size_t wb, void* st) { \
-    return flex::GraphApi<GRAPH, CFG, CFGWIN>::plan_windows(d, ix, ws, wb, static_cast<cudaStream_t>(st));      \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN, CFGLEAN>::plan_windows(d, ix, ws, wb, static_cast<cudaStream_t>(st));      \
   }                                                                                                             \
   int flexspmv_##SYM##_launch(const flexspmv_desc* d, const void* const* v, const void* const* ix,              \
                               const void* ro, void* const* o, void* ws, size_t wb, void* st) {                  \
-    return flex::GraphApi<GRAPH, CFG, CFGWIN>::launch(d, v, ix, ro, o, ws, wb, static_cast<cudaStream_t>(st));  \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN, CFGLEAN>::launch(d, v, ix, ro, o, ws, wb, static_cast<cudaStream_t>(st));  \
   }                                                                                                             \
   int flexspmv_##SYM##_device_status(const void* ws, int32_t* out, void* st) {                                  \
-    return flex::GraphApi<GRAPH, CFG, CFGWIN>::device_status(ws, out, static_cast<cudaStream_t>(st));           \
+    return flex::GraphApi<GRAPH, CFG, CFGWIN, CFGLEAN>::device_status(ws, out, static_cast<cudaStream_t>(st));           \
   }                                                                                                             \
   }
 

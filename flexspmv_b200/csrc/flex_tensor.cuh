@@ -238,8 +238,8 @@ __device__ __forceinline__ void prefetch_l2_range(const void* b, const void* e, 
   for (; q < reinterpret_cast<const char*>(e); q += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
 }
 
-template <typename V, int D>
-__device__ __forceinline__ Vec<V, D> ld_vec(const V* p) {   // plain load (shared or global)
+template <typename V, int D, class P>
+__device__ __forceinline__ Vec<V, D> ld_vec(P p) {   // plain load through anything indexable (shared / global pointer, streaming accessor)
   Vec<V, D> r;
 #pragma unroll
   for (int i = 0; i < D; ++i) r.v[i] = p[i];

@@ -55,7 +55,7 @@ typedef struct flexspmv_desc {
   int32_t offset_bits;   /* 32 or 64: width of the row-offset entries                               */
   int32_t tile_items;    /* merge items (rows + edges) per tile; 0 = the graph's compiled default   */
   int32_t max_ctas;      /* cap on persistent CTAs; 0 = SM count x resident CTAs per SM             */
-  int32_t reserved;      /* flags: 0 or FLEXSPMV_FLAG_GATHER_WINDOWS (field name kept from ABI 1)     */
+  int32_t reserved;      /* flags: 0 or an OR of the FLEXSPMV_FLAG_* below (field name kept from ABI 1) */
 } flexspmv_desc;
 
 /*
@@ -71,6 +71,19 @@ typedef struct flexspmv_desc {
  * plain path run with the same tile size and CTA count.
  */
 #define FLEXSPMV_FLAG_GATHER_WINDOWS 1
+
+/*
+ * Random gathers (no reference counterpart; graphs whose flexspmv_graph_info.reserved has bit 1 set).
+ * The caller states that the columns of the matrix have no locality (consecutive edges gather from unrelated
+ * cache lines: power-law graphs, random sparse matrices).  With this flag in the descriptor -- the same for
+ * workspace_bytes, plan and launch -- a kernel without shared-memory staging runs instead: on such matrices
+ * the bound is the number of gather misses an SM has in flight, which grows with the part of the L1 /
+ * shared-memory array that stays cache.  The plan then splits the merge path into chunks of 32 x
+ * (items per lane) items, one warp each.  Results agree with the plain path to the parity tolerance (the
+ * summation order inside a row differs); run-to-run deterministic.  Ignored by graphs that were not built
+ * with that kernel.  On stencil / banded matrices the plain path is faster.
+ */
+#define FLEXSPMV_FLAG_RANDOM_GATHER 2
 
 /* ---- library-wide ----------------------------------------------------------------------------- */
 

@@ -397,6 +397,47 @@ def test_edge_kernel_refuses_a_workspace_that_was_never_planned():
     assert torch.isnan(prod).all()
 
 
+@pytest.mark.parametrize("dt", ["float32", "float64", "int64"])
+def test_warp_kernel_for_random_columns_matches_oracle(dt):
+    """The kernel without staging (FLEXSPMV_FLAG_RANDOM_GATHER): same shapes as the plain path (empty rows, rows
+    spanning many chunks, one row, no rows), odd chunk sizes and few CTAs (long carry chains across warps),
+    int64 bit-exact, run-to-run deterministic."""
+    ir = graphs.spmv_graph()
+    dtype = np.dtype(dt)
+    ext = GraphExtension(ir, random_gather=True)
+    assert ext.symbols(NP2T[dtype]).graph_info.reserved & 2
+    shapes = SHAPES + [(2, 5000, 300000), (40000, 40000, 40)]
+    for (nr, nv, nnz) in shapes:
+        prob = problems.random_problem(ir, nr, nv, nnz, seed=2000 + nr + nnz, dtype=dtype)
+        ref, _, sums = ir_eval.run_graph(ir, prob, dtype, num_threads=8, want_abs_sums=True)
+        got, _ = run_gpu(ext, ir, prob, dtype)
+        assert_outputs_match(ir, got, ref, sums, dtype, what=f"warp kernel {dt} {nr}x{nnz}")
+        again, _ = run_gpu(ext, ir, prob, dtype)
+        assert np.array_equal(got[0], again[0])
+    prob = problems.random_problem(ir, 97, 97, 60000, seed=6, dtype=dtype)
+    ref, _, sums = ir_eval.run_graph(ir, prob, dtype, num_threads=4, want_abs_sums=True)
+    for tile_items, max_ctas in ((1, 2), (7, 3), (33, 1), (160, 3), (159, 0)):
+        small = GraphExtension(ir, random_gather=True, tile_items=tile_items, max_ctas=max_ctas)
+        sub = prob if tile_items > 7 else problems.random_problem(ir, 97, 97, 3000, seed=6, dtype=dtype)
+        r2, _, s2 = (ref, None, sums) if sub is prob else ir_eval.run_graph(ir, sub, dtype, num_threads=4, want_abs_sums=True)
+        got, _ = run_gpu(small, ir, sub, dtype, offsets_dtype=np.int64 if tile_items == 33 else None)
+        assert_outputs_match(ir, got, r2, s2, dtype, what=f"warp kernel {dt} chunk {tile_items} ctas {max_ctas}")
+        assert small.device_status(NP2T[dtype]) == 0
+
+
+def test_random_gather_is_detected_per_matrix():
+    """Left to itself the operator samples the index array once per matrix: a power-law matrix with random columns
+    takes the warp kernel, a stencil matrix the staged kernel; both agree with the oracle."""
+    ir = graphs.spmv_graph()
+    ext = GraphExtension(ir)
+    for prob, expect in ((problems.powerlaw(1 << 17, cap=20000), 2), (problems.poisson2d(512), 0)):
+        ref, _, sums = ir_eval.run_graph(ir, prob, prob.values["vals"].dtype, num_threads=8, want_abs_sums=True)
+        got, _ = run_gpu(ext, ir, prob, prob.values["vals"].dtype)
+        assert_outputs_match(ir, got, ref, sums, prob.values["vals"].dtype, what="auto-detected kernel")
+        key = next(reversed(ext._plans))
+        assert key[6] == expect          # the flags the plan was made with
+
+
 def test_rows_spanning_every_cta():
     """Two rows of 1.5 M edges each: every CTA contributes a carry to the same row and the last CTA folds
     hundreds of them (exact for int64, tolerance for fp64)."""

@@ -34,7 +34,7 @@ def test_emitter_is_deterministic_and_resolves_overloads():
     assert "fx::zip(w, sel, fx::DivGuard{})" in a              # equal widths: guarded member operator/
     assert "fx::zip_sv(V(1.5), sel, fx::DivGuard{})" in a      # scalar / tensor: guarded
     assert "fx::zip_vs(a4, nn, fx::Div{})" in a                # tensor / scalar: plain IEEE divide
-    assert "FLEXSPMV_DEFINE_GRAPH(ops_zoo_f32, gen_ops_zoo_f32::Graph, gen_ops_zoo_f32::Cfg, gen_ops_zoo_f32::CfgWin)" in a
+    assert "FLEXSPMV_DEFINE_GRAPH(ops_zoo_f32, gen_ops_zoo_f32::Graph, gen_ops_zoo_f32::Cfg, gen_ops_zoo_f32::CfgWin, gen_ops_zoo_f32::CfgLean)" in a
     r = emit_cuda.emit_graph(graphs.rusanov_graph(), "float64")
     assert "fx::PowHalf{}" in r and "kGatherNeedsRow = true" in r and "kNumReducers = 3, kAccDim = 3" in r
     s = emit_cuda.emit_graph(graphs.spring_mass_graph(), "float32")
