@@ -53,7 +53,10 @@ def _compile(src: str, obj: str, extra=()) -> str:
 def generated_units():
     """[(symbol, source text)] for every built-in (graph, value type)."""
     units = []
+    only = [g for g in os.environ.get("FLEXSPMV_ONLY_GRAPHS", "").split(",") if g]      # tuning builds: a subset of the graphs
     for name, make in ALL_GRAPHS.items():
+        if only and name not in only:
+            continue
         ir = make()
         for dt in GRAPH_DTYPES[name]:
             sym = f"{name}_{CTYPE[dt][1]}"

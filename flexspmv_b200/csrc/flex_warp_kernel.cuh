@@ -8,10 +8,11 @@
 //   * no staging: every warp works alone on merge-path chunks of 32 x IPT items (coordinates planned per
 //     chunk), reads its index / value records with coalesced streaming loads straight into registers --
 //     one chunk ahead of the chunk whose gathers are in flight -- and gathers from registers;
-//   * the only shared memory is one product slot per item (the strided -> row-wise transposition):
-//     lanes take consecutive edges for loads and gathers, then one lane per row sums the row's products
-//     left to right; rows longer than 32 edges and the chunk's trailing partial row are summed by the
-//     whole warp (lanes 32 apart, shuffle tree);
+//   * the only shared memory is one product slot and one marker byte per item (the strided -> blocked
+//     transposition): lanes take consecutive edges for loads and gathers; then every lane takes IPT
+//     consecutive items, sums them left to right and closes the rows whose last edge is marked inside its
+//     span, and a warp-shuffle segmented scan of the lanes' open partial sums supplies what a row received
+//     from the lanes before (every lane is busy whatever the row lengths are);
 //   * a warp owns a contiguous run of chunks, so the carry of a row that spans chunks stays in a register;
 //     one carry per warp reaches global memory and the last CTA to finish folds them, in order.
 // No barriers between warps, no atomics on the output, run-to-run deterministic.
@@ -36,7 +37,6 @@ struct WarpCfg {
 };
 
 constexpr int kMaxWarpCarries = 16384;            // capacity of the per-warp carry arrays in the workspace
-constexpr int kWarpLongRow = 32;                  // rows longer than this are summed by the whole warp
 
 // Streaming accessor for the per-edge arrays: plain global pointers read with evict-first loads, so that the
 // lines of the streams do not compete with the gathered records for L1 and L2.
@@ -77,7 +77,11 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
   extern __shared__ __align__(16) unsigned char smem_w[];
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  V* sp = reinterpret_cast<V*>(smem_w) + (size_t)warp * kAcc * CH;      // this warp's product slots, [kAcc][CH]
+  static_assert(CH <= 255, "row numbers inside a chunk are kept in marker bytes");
+  constexpr int kWarpBytes = int(align_up(uint64_t(kAcc) * CH * sizeof(V) + CH, 16));
+  unsigned char* wbase = smem_w + (size_t)warp * kWarpBytes;
+  V* sp = reinterpret_cast<V*>(wbase);                                   // this warp's product slots, [kAcc][CH]
+  unsigned char* mk = wbase + (size_t)kAcc * CH * sizeof(V);            // per item: the row (inside the chunk) whose last edge it is, or 0xff
   const OffsetT* ro = static_cast<const OffsetT*>(a.row_offsets);
   const OffsetT* coords = static_cast<const OffsetT*>(a.coords);
 
@@ -137,7 +141,54 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     }
     cw_next = (k + 2 < count) ? load_coords(c_begin + k + 2) : 0;
 
-    // products into this warp's slots
+    // markers cleared; bounds of the first 32 rows that end inside the chunk requested before the gathers are waited for
+    {
+      uint32_t* mk32 = reinterpret_cast<uint32_t*>(mk);
+#pragma unroll
+      for (int w4 = lane; w4 < CH / 4; w4 += 32) mk32[w4] = 0xffffffffu;
+    }
+    auto row_bounds = [&](int r, long long& beg, long long& end) {
+      if (r < nr) {
+        end = (long long)ro[x0 + r + 1];
+        beg = r ? (long long)ro[x0 + r] : y0;          // row x0 may have begun in an earlier chunk
+        if (beg < y0) beg = y0;
+      } else {
+        beg = end = y0;
+      }
+    };
+    long long beg = y0, end = y0;
+    row_bounds(lane, beg, end);
+    __syncwarp();
+
+    // rows that end inside the chunk, one lane per row: the last edge of a row is marked with the row's number;
+    // a row without edges in this chunk is finished here (row x0 then takes the whole carry)
+    bool seed_used = false;
+    for (int r0 = 0; r0 < nr; r0 += 32) {
+      const int r = r0 + lane;
+      const bool have = r < nr;
+      const int len = (int)(end - beg), last = (int)(end - y0) - 1;
+      if (r0 + 32 < nr) row_bounds(r + 32, beg, end);
+      if (have) {
+        if (len > 0) {
+          mk[last] = (unsigned char)r;
+        } else {
+          static_for<G::kNumReducers>([&](auto R) {
+            constexpr int d = G::template red_dim<R.value>();
+            constexpr int o = G::template red_off<R.value>();
+            V* dst = G::template red_out<R.value>(p) + (size_t)(x0 + r) * d;
+#pragma unroll
+            for (int j = 0; j < d; ++j) dst[j] = (r == 0) ? carry[o + j] : V(0);
+          });
+        }
+      }
+      if (r0 == 0) seed_used = __shfl_sync(0xffffffffu, (int)(have && len == 0), 0) != 0;
+    }
+    if (seed_used) {
+#pragma unroll
+      for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
+    }
+
+    // products into this warp's slots (lanes on consecutive edges)
     typename G::GRow gr;
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
@@ -152,90 +203,90 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     }
     __syncwarp();
 
-    // rows that end inside the chunk: one lane per row; the first one continues the warp's carry
-    long long tail_begin = y0;                         // first edge of the trailing partial row
-    for (int r0 = 0; r0 < nr; r0 += 32) {
-      const int r = r0 + lane;
-      const bool have = r < nr;
-      long long beg = 0, end = 0;
-      if (have) {
-        end = (long long)ro[x0 + r + 1];
-        beg = r ? (long long)ro[x0 + r] : y0;          // row x0 may have begun in an earlier chunk
-        if (beg < y0) beg = y0;
-      }
-      const int lo = (int)(beg - y0), len = (int)(end - beg);
-      V sum[kAcc];
+    // blocked pass: every lane sums IPT consecutive items and closes the rows that end inside its span
+    V run[kAcc], first[kAcc];
 #pragma unroll
-      for (int j = 0; j < kAcc; ++j) sum[j] = V(0);
-      const bool is_long = have && len > kWarpLongRow;
-      if (have && !is_long) {
-        const V* qv = sp + lo;
-        for (int n = 0; n < len; ++n) {
+    for (int j = 0; j < kAcc; ++j) { run[j] = V(0); first[j] = V(0); }
+    int first_row = -1;
+    {
+      V pv[IPT][kAcc];
+      unsigned char pm[IPT];
 #pragma unroll
-          for (int j = 0; j < kAcc; ++j) sum[j] += qv[j * CH + n];
+      for (int i = 0; i < IPT; ++i) {
+        const int e = lane * IPT + i;
+        pm[i] = 0xff;
+        if (e < ne) {
+          pm[i] = mk[e];
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) pv[i][j] = sp[j * CH + e];
         }
       }
-      unsigned longs = __ballot_sync(0xffffffffu, is_long);
-      while (longs) {                                  // long rows: lanes 32 apart, shuffle tree, result to the row's lane
-        const int src = __ffs(longs) - 1;
-        longs &= longs - 1;
-        const int llo = __shfl_sync(0xffffffffu, lo, src), llen = __shfl_sync(0xffffffffu, len, src);
-        V part[kAcc];
 #pragma unroll
-        for (int j = 0; j < kAcc; ++j) part[j] = V(0);
-        for (int n = lane; n < llen; n += 32) {
+      for (int i = 0; i < IPT; ++i) {
+        if (lane * IPT + i < ne) {
 #pragma unroll
-          for (int j = 0; j < kAcc; ++j) part[j] += sp[j * CH + llo + n];
+          for (int j = 0; j < kAcc; ++j) run[j] += pv[i][j];
+          if (pm[i] != 0xff) {
+            if (first_row < 0) {                       // may have begun in earlier lanes: finished after the scan
+              first_row = pm[i];
+#pragma unroll
+              for (int j = 0; j < kAcc; ++j) first[j] = run[j];
+            } else {
+              static_for<G::kNumReducers>([&](auto R) {
+                constexpr int d = G::template red_dim<R.value>();
+                constexpr int o = G::template red_off<R.value>();
+                V* dst = G::template red_out<R.value>(p) + (size_t)(x0 + pm[i]) * d;
+#pragma unroll
+                for (int j = 0; j < d; ++j) dst[j] = run[o + j];
+              });
+            }
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) run[j] = V(0);
+          }
         }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-          for (int j = 0; j < kAcc; ++j) part[j] += shfl_down_any(part[j], off);
-        }
-#pragma unroll
-        for (int j = 0; j < kAcc; ++j) {
-          const V tot = __shfl_sync(0xffffffffu, part[j], 0);
-          if (lane == src) sum[j] = tot;
-        }
-      }
-      if (have) {
-        if (r == 0) {
-#pragma unroll
-          for (int j = 0; j < kAcc; ++j) sum[j] = carry[j] + sum[j];
-        }
-        static_for<G::kNumReducers>([&](auto R) {
-          constexpr int d = G::template red_dim<R.value>();
-          constexpr int o = G::template red_off<R.value>();
-          V* dst = G::template red_out<R.value>(p) + (size_t)(x0 + r) * d;
-#pragma unroll
-          for (int j = 0; j < d; ++j) dst[j] = sum[o + j];
-        });
-      }
-      if (r0 + 32 >= nr) {                             // the last row's end is where the trailing partial row begins
-        const long long last_end = __shfl_sync(0xffffffffu, end, (nr - 1) & 31);
-        tail_begin = last_end > y0 ? last_end : y0;
       }
     }
-
-    // trailing partial row (all of the chunk when no row ends in it): whole warp, then into the carry
-    {
-      const int tlo = (int)(tail_begin - y0);
-      V part[kAcc];
+    // segmented inclusive scan of the open partial sums: a lane that closed a row passes on only what follows it
+    int flag = first_row >= 0 ? 1 : 0;
+    V scan[kAcc];
 #pragma unroll
-      for (int j = 0; j < kAcc; ++j) part[j] = V(0);
-      for (int n = tlo + lane; n < ne; n += 32) {
+    for (int j = 0; j < kAcc; ++j) scan[j] = run[j];
 #pragma unroll
-        for (int j = 0; j < kAcc; ++j) part[j] += sp[j * CH + n];
-      }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-        for (int j = 0; j < kAcc; ++j) part[j] += shfl_down_any(part[j], off);
-      }
+    for (int d = 1; d < 32; d <<= 1) {
+      const int f_up = __shfl_up_sync(0xffffffffu, flag, d);
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) {
-        const V tot = __shfl_sync(0xffffffffu, part[j], 0);
-        carry[j] = (nr > 0) ? tot : carry[j] + tot;
+        const V v_up = shfl_up_any(scan[j], d);
+        if (lane >= d && !flag) scan[j] = v_up + scan[j];
+      }
+      if (lane >= d) flag |= f_up;
+    }
+    // what the lanes before this one left open (plus the warp's carry when none of them closed a row)
+    int f_ex = __shfl_up_sync(0xffffffffu, flag, 1);
+    if (lane == 0) f_ex = 0;
+    V in[kAcc];
+#pragma unroll
+    for (int j = 0; j < kAcc; ++j) {
+      V v_ex = shfl_up_any(scan[j], 1);
+      if (lane == 0) v_ex = V(0);
+      in[j] = f_ex ? v_ex : carry[j] + v_ex;
+    }
+    if (first_row >= 0) {
+      static_for<G::kNumReducers>([&](auto R) {
+        constexpr int d = G::template red_dim<R.value>();
+        constexpr int o = G::template red_off<R.value>();
+        V* dst = G::template red_out<R.value>(p) + (size_t)(x0 + first_row) * d;
+#pragma unroll
+        for (int j = 0; j < d; ++j) dst[j] = in[o + j] + first[o + j];
+      });
+    }
+    // the warp's new carry: what is still open behind the last lane
+    {
+      const int f31 = __shfl_sync(0xffffffffu, flag, 31);
+#pragma unroll
+      for (int j = 0; j < kAcc; ++j) {
+        const V v31 = __shfl_sync(0xffffffffu, scan[j], 31);
+        carry[j] = f31 ? v31 : carry[j] + v31;
       }
     }
     end_row = x1;
