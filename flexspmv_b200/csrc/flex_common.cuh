@@ -186,6 +186,13 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
                "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
                : "memory");
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it on the stream is still running; everything it does before pdl_wait() must
+// touch no global memory.  pdl_wait() returns once that kernel has completed and its writes are visible (at
+// once when the launch carried no such attribute); pdl_launch_dependents() lets the next such launch start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Orders earlier generic-proxy shared-memory accesses before later async-proxy (bulk copy) ones.
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

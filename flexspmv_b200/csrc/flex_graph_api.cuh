@@ -6,6 +6,7 @@
 // include/merged_spmv.cuh:22-182): no per-call device-attribute queries, no per-call temp-storage
 // allocation, one kernel launch per operator call, partition cached in the caller's workspace.
 #pragma once
+#include <cstdlib>
 #include <mutex>
 
 #include "flex_common.cuh"
@@ -25,6 +26,12 @@ int window_plan_launch(const void* d_coords, int offset_bits, long long num_tile
 int window_ready_launch(void* ws, cudaStream_t st);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// FLEXSPMV_NO_PDL=1 in the environment launches the tile kernel without the programmatic-dependent-launch attribute.
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("FLEXSPMV_NO_PDL"); return !(e && e[0] == '1'); }();
+  return on;
+}
 
 struct NoWindows {   // in place of CfgWin: the gather-window variant of the kernel is not built and the flag is ignored
   static constexpr int kTile = 0;
@@ -193,8 +200,16 @@ struct GraphApi {
       a.win_table = reinterpret_cast<const int*>(static_cast<char*>(ws) + h.win_table_offset);
       a.win_index = reinterpret_cast<const unsigned short*>(static_cast<char*>(ws) + h.win_index_offset);
     }
-    kernel<<<(unsigned)grid, kThreads, L::kTotal, st>>>(p, a);
-    return (int)cudaGetLastError();
+    // Programmatic dependent launch: the CTAs may be placed while the kernel before this one on the stream drains; the
+    // kernel touches no global memory before its griddepcontrol.wait.  Back-to-back launches of small problems
+    // (a time-stepping loop) then overlap one launch's set-up with the tail of the one before.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = L::kTotal; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, p, a);
   }
 
   template <typename OffsetT>

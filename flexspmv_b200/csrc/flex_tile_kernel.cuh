@@ -197,6 +197,11 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   const OffsetT* row_offsets = static_cast<const OffsetT*>(a.row_offsets);
   const OffsetT* coords = static_cast<const OffsetT*>(a.coords);
 
+  // With a programmatic dependent launch the CTA may have been placed while the kernel before this one on the stream
+  // was still draining: wait for its results (and for this workspace's ticket) before the first global access.
+  pdl_wait();
+  pdl_launch_dependents();
+
   // a workspace that was never planned for this problem holds no usable coordinates: every CTA
   // sees the same header, so all of them leave here and the ticket stays untouched
   if (a.header->magic != kMagic || a.header->num_tiles != a.num_tiles || a.header->num_rows != a.num_rows ||
