@@ -74,6 +74,7 @@ def build(force: bool = False, jobs: int | None = None, verbose_ptxas: bool = Fa
     work = []   # (src, obj)
     core_src = os.path.join(CSRC, "flex_core.cu")
     work.append((core_src, os.path.join(BUILD, "flex_core.o")))
+    work.append((os.path.join(CSRC, "flex_sort.cu"), os.path.join(BUILD, "flex_sort.o")))
     for sym, text in generated_units():
         src = os.path.join(BUILD, f"graph_{sym}.cu")
         old = open(src).read() if os.path.exists(src) else None

@@ -8,8 +8,11 @@ install a wrapper whose ``__call__`` marshals the placeholders into the operator
 What the reference's wrapper does on every call and this one does once: ``.contiguous()`` copies
 (:147-149; here only non-contiguous arguments are copied), device moves of the index buffers, and the
 int64 -> int32 cast of the row offsets (kept int64 when they do not fit int32: the kernels take both).
-What the reference never checks and this one does once at construction: the Reducer's row ids must be
-sorted ascending (its ``_coo_rows_to_csr_ptr`` silently assumes it, :20-41).
+What the reference never checks and this one does once at construction: whether the Reducer's row ids are
+sorted ascending (its ``_coo_rows_to_csr_ptr`` silently assumes it, :20-41).  Ids on the device that are not
+sorted are sorted here, once, by the library's stable radix sort (``flexspmv_sort_rows``); the wrapper then
+permutes the selector index arrays once and the per-edge value inputs on every call
+(``flexspmv_permute_edges``), and scatters per-edge outputs back into the caller's edge order.
 
 Selector / Reducer modules are recognised by duck typing (an ``idx`` tensor; a Reducer also has ``n``), so
 the module works with ``easier``'s classes without importing them.
@@ -60,6 +63,52 @@ def coo_rows_to_csr_ptr(row_ids: torch.Tensor, num_rows: Optional[int] = None) -
     return crow
 
 
+def sort_edges_by_row(row_ids: torch.Tensor, num_rows: int):
+    """Stable sort of CUDA row ids on the device: returns (perm int32, CSR offsets int64) with
+    ``row_ids[perm]`` ascending and equal ids in their input order."""
+    import ctypes
+    from ..binding import check, load_library
+    lib = load_library()
+    ids = row_ids.contiguous()
+    if ids.dtype not in (torch.int32, torch.int64):
+        ids = ids.to(torch.int64)
+    n = ids.numel()
+    nbytes = ctypes.c_size_t()
+    lib.flexspmv_sort_rows_bytes.restype = ctypes.c_int
+    lib.flexspmv_sort_rows.restype = ctypes.c_int
+    check(lib, lib.flexspmv_sort_rows_bytes(ctypes.c_int64(n), ctypes.byref(nbytes)), "sort_rows_bytes")
+    dev = ids.device
+    scratch = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+    perm = torch.empty(n, dtype=torch.int32, device=dev)
+    crow = torch.empty(num_rows + 1, dtype=torch.int64, device=dev)
+    status = torch.empty(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        st = lib.flexspmv_sort_rows(ctypes.c_void_p(ids.data_ptr()), 64 if ids.dtype == torch.int64 else 32, ctypes.c_int64(n),
+                                    ctypes.c_int64(num_rows), ctypes.c_void_p(perm.data_ptr()), ctypes.c_void_p(crow.data_ptr()), 64,
+                                    ctypes.c_void_p(scratch.data_ptr()), ctypes.c_size_t(nbytes.value),
+                                    ctypes.c_void_p(status.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    check(lib, st, "sort_rows")
+    check(lib, int(status.item()), "sort_rows (row ids)")
+    return perm, crow
+
+
+def permute_edges(src: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
+    """dst[k] = src[perm[k]] along the first dimension (records of 4-byte multiples), by the library's kernel."""
+    import ctypes
+    from ..binding import check, load_library
+    lib = load_library()
+    src = src.contiguous()
+    rec = src.element_size() * (src.numel() // max(src.shape[0], 1))
+    dst = torch.empty_like(src)
+    with torch.cuda.device(src.device):
+        lib.flexspmv_permute_edges.restype = ctypes.c_int
+        st = lib.flexspmv_permute_edges(ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(perm.data_ptr()),
+                                        ctypes.c_int64(src.shape[0]), ctypes.c_int32(rec),
+                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    check(lib, st, "permute_edges")
+    return dst
+
+
 def _is_selector(m) -> bool:
     return hasattr(m, "idx") and not hasattr(m, "n")
 
@@ -71,9 +120,14 @@ def _is_reducer(m) -> bool:
 class DynamicCudaWrapper(nn.Module):
     def __init__(self, ext, input_param_names: Sequence[str], non_gather_value_inputs: Sequence[str],
                  gather_value_inputs: Sequence[str], selector_idx_tensors: Sequence[torch.Tensor],
-                 row_end_offsets: Optional[torch.Tensor]):
+                 row_end_offsets: Optional[torch.Tensor], edge_perm: Optional[torch.Tensor] = None):
+        """``edge_perm``: permutation that sorts the edges by row (None: they already are); the CSR offsets and
+        kernels work in the sorted order."""
         super().__init__()
         self._ext = ext
+        self._perm = edge_perm
+        if edge_perm is not None:
+            selector_idx_tensors = [permute_edges(t.to(edge_perm.device), edge_perm) for t in selector_idx_tensors]
         self._names = list(input_param_names)
         self._non_gather, self._gather = list(non_gather_value_inputs), list(gather_value_inputs)
         self._sel_names: List[str] = []
@@ -112,12 +166,25 @@ class DynamicCudaWrapper(nn.Module):
             num_rows = num_cols
         else:
             num_rows = int(ro.numel() - 1)
+        if self._perm is not None:      # per-edge inputs into the sorted edge order
+            ne = int(self._perm.numel())
+            for n in self._non_gather:
+                if amap[n].dim() >= 1 and amap[n].shape[0] == ne:
+                    amap[n] = permute_edges(amap[n], self._perm)
         call_args = [amap[n] for n in self._non_gather] + [amap[n] for n in self._gather] + \
                     [getattr(self, n) for n in self._sel_names] + [ro, num_rows, num_cols]
         outs = self._ext.merged_spmv_launch(*call_args)
         if outs is None:
             return []
-        return list(outs) if isinstance(outs, tuple) else [outs]
+        outs = list(outs) if isinstance(outs, tuple) else [outs]
+        if self._perm is not None:      # per-edge outputs back into the caller's edge order
+            ne = int(self._perm.numel())
+            for i, o in enumerate(outs):
+                if o.dim() >= 1 and o.shape[0] == ne and o.shape[0] != num_rows:
+                    back = torch.empty_like(o)
+                    back[self._perm.long()] = o
+                    outs[i] = back
+        return outs
 
 
 def dynamic_replace_submodule(compiled_eqn: nn.Module, ext, submodule_name: str) -> bool:
@@ -143,9 +210,16 @@ def dynamic_replace_submodule(compiled_eqn: nn.Module, ext, submodule_name: str)
                 for a in n.args:
                     if hasattr(a, "op") and a.op == "placeholder" and a.name not in gathers:
                         gathers.append(a.name)
-        ro = coo_rows_to_csr_ptr(reducer.idx, int(reducer.n)) if reducer is not None else None
+        ro, perm = None, None
+        if reducer is not None:
+            try:
+                ro = coo_rows_to_csr_ptr(reducer.idx, int(reducer.n))
+            except ValueError:
+                if not reducer.idx.is_cuda:
+                    raise
+                perm, ro = sort_edges_by_row(reducer.idx, int(reducer.n))      # unsorted ids: sorted once, on the device
         wrapper = DynamicCudaWrapper(ext, names, [n for n in names if n not in gathers], gathers,
-                                     [m.idx for _, m in selectors], ro)
+                                     [m.idx for _, m in selectors], ro, perm)
         setattr(compiled_eqn, submodule_name, wrapper)
         return True
     return False

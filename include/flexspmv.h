@@ -175,6 +175,24 @@ int flexspmv_coo_rows_to_csr(const void *d_row_ids, int32_t id_bits, int64_t num
                              int32_t *d_status, void *stream);
 
 /*
+ * Unsorted reducers: a stable sort of the edges by row id.  d_perm (int32, num_edges entries) receives the
+ * permutation -- d_perm[k] = original position of the edge that comes k-th when the edges are ordered by row,
+ * edges of one row keeping their input order (a stable argsort) -- and d_row_offsets the CSR offsets with the
+ * leading 0 of the sorted order.  The caller permutes its per-edge arrays once with flexspmv_permute_edges
+ * (dst[k] = src[d_perm[k]], records of record_bytes bytes, a multiple of 4) and then uses the CSR kernels.
+ * Scratch: flexspmv_sort_rows_bytes(num_edges) bytes, 16-byte aligned.  *d_status (device int32) becomes
+ * FLEXSPMV_ERR_BAD_ARG when an id lies outside [0, num_rows), else 0.  num_edges and num_rows < 2^31.
+ * The reference has no counterpart: its _coo_rows_to_csr_ptr assumes ascending ids and is silently wrong
+ * otherwise (python_wrapper/dynamic_replace_submodule.py:20-41).
+ */
+int flexspmv_sort_rows_bytes(int64_t num_edges, size_t *bytes);
+int flexspmv_sort_rows(const void *d_row_ids, int32_t id_bits, int64_t num_edges, int64_t num_rows,
+                       int32_t *d_perm, void *d_row_offsets, int32_t offset_bits, void *d_scratch,
+                       size_t scratch_bytes, int32_t *d_status, void *stream);
+int flexspmv_permute_edges(const void *d_src, void *d_dst, const int32_t *d_perm, int64_t num_edges,
+                           int32_t record_bytes, void *stream);
+
+/*
  * One Runge-Kutta stage of the per-cell arithmetic of the reference's shallow-water model
  * (shallow_water_equation/swe_main.py:100-146), which the reference leaves to torch element-wise
  * kernels: with r = the three interior reducer sums and rb = the two boundary sums,
