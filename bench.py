@@ -431,6 +431,8 @@ def verify_iteration(op, plan, n: int, rank: int, world: int, use_graph: bool, s
         op.step_pair()                       # replays the captured pair
         replayed = op.owned().clone()
         op.owned().copy_(start)
+        if op.overlap:
+            op.refresh_halos()               # the halos in place belong to the replayed state
         op.step()
         op.step()
         graph_equal = bool(torch.equal(op.owned(), replayed))
@@ -496,6 +498,8 @@ def run_ours(args) -> None:
         # ||A|| <= 12: rescale before the iterate can overflow fp64 (one tiny extra kernel every 200 steps)
         if step_index and step_index % 200 == 0:
             op.owned().mul_(2.0 ** -700)
+            if op.overlap:
+                op.refresh_halos()       # the halos were sent before the rescaling
             return 1
         return 0
 

@@ -160,6 +160,7 @@ class GraphExtension:
         edge_sel = [s_ for s_ in ir.selector_register if s_.get("selector") == 1 and not s_.get("row_identity")]
         self._gather_dim = dim_of(edge_sel[0]["shape"]) if edge_sel else 1
         self.lib = load_library(lib_path)
+        self._lib_path = lib_path
         self.prefix = symbol_prefix or ir.name
         self.tile_items, self.max_ctas = int(tile_items), int(max_ctas)
         self.non_gather, self.gathers, self.index_names = operator_signature(ir)

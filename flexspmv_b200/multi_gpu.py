@@ -198,13 +198,19 @@ class PartitionedSpmv:
     """One rank's share of y = A x for a row-block partitioned banded matrix, iterated as
     x <- A x: the local vector is double-buffered ([halo_lo | owned | halo_hi] each) so an
     iteration is "exchange halos of the current buffer, fused SpMV into the owned part of the other
-    buffer".  With ``overlap`` the rows are split once into
-    the few that read a halo (first / last rows of the block) and the interior: the interior launch is
-    enqueued while the NCCL transfers are in flight and the two small boundary launches follow them
-    (``overlap=True``; off by default, see ``__init__``)."""
+    buffer".
+
+    With ``overlap`` the rows are split once into the few that read a halo (first / last rows of the block) and the
+    interior, and an iteration becomes: one small launch over BOTH boundary row groups (their results are exactly
+    what the neighbours need next) -> the send / receive of those results into the neighbours' halos of the next
+    buffer, on NCCL's stream -> the interior launch on the compute stream, concurrently with the transfer.  The
+    halos of iteration k + 1 thus travel while iteration k's interior is computed.  The interior launch leaves a
+    few CTA slots free (``overlap_spare_ctas``): the kernel runs persistent CTAs over static tile runs, so a CTA
+    that finds no free slot because a communication kernel sits on its SM would double the launch time."""
 
     def __init__(self, plan: HaloPlan, row_offsets: torch.Tensor, cols_local: torch.Tensor, vals: torch.Tensor,
-                 x_owned: torch.Tensor, group=None, ext=None, overlap: Optional[bool] = None):
+                 x_owned: torch.Tensor, group=None, ext=None, overlap: Optional[bool] = None,
+                 overlap_spare_ctas: int = 16):
         from .binding import load_builtin
         self.plan, self.group = plan, group
         self.ro, self.cols, self.vals = row_offsets, cols_local, vals
@@ -214,58 +220,84 @@ class PartitionedSpmv:
         self.cur = 0
         self.buf[0][plan.halo_lo:plan.halo_lo + plan.rows] = x_owned
         self.nnz = int(cols_local.numel())
-        # measured on 8 B200s (512^3, 100 steps): 0.479 ms/step without the split, 0.491 ms with it -- the two
-        # boundary launches cost more than the 2 MiB exchange they hide -- so overlapping is opt-in
         self.overlap = bool(overlap) and plan.world > 1
         self._prepared = {}
         self.graph, self.graph_error = None, None
-        self.parts = []          # (row_begin, row_end, ro_sub, cols_sub, vals_sub); interior first
+        self._halos_valid = False        # overlap mode: the current buffer's halos already hold the neighbours' values
         if self.overlap:
             lo_rows, hi_rows = boundary_rows(row_offsets, cols_local, plan)
-            if lo_rows + hi_rows >= plan.rows:      # block too thin to have an interior
+            if lo_rows + hi_rows >= plan.rows or lo_rows + hi_rows == 0:      # block too thin to have an interior
                 self.overlap = False
-            else:
-                for (r0, r1) in ((lo_rows, plan.rows - hi_rows), (0, lo_rows), (plan.rows - hi_rows, plan.rows)):
-                    if r1 > r0:
-                        self.parts.append((r0, r1) + sub_csr(row_offsets, cols_local, vals, r0, r1))
+        if self.overlap:
+            from .binding import GraphExtension
+            rows = plan.rows
+            self.lo_rows, self.hi_rows = lo_rows, hi_rows
+            # interior rows: views of the block's arrays
+            self.interior = (lo_rows, rows - hi_rows) + sub_csr(row_offsets, cols_local, vals, lo_rows, rows - hi_rows)
+            # both boundary row groups as ONE small CSR (lower group first), results into one scratch vector
+            ro64 = row_offsets.to(torch.int64)
+            e_lo, e_hi0 = int(ro64[lo_rows]), int(ro64[rows - hi_rows])
+            ro_b = torch.cat([ro64[:lo_rows + 1], ro64[rows - hi_rows + 1:] - e_hi0 + e_lo]).to(row_offsets.dtype).contiguous()
+            self.boundary = (ro_b, torch.cat([cols_local[:e_lo], cols_local[e_hi0:]]).contiguous(),
+                             torch.cat([vals[:e_lo], vals[e_hi0:]]).contiguous())
+            self.boundary_out = torch.empty(lo_rows + hi_rows, dtype=vals.dtype, device=dev)
+            props = torch.cuda.get_device_properties(dev)
+            info = self.ext.symbols(vals.dtype).graph_info
+            resident = max(1, min(2048 // (info.block_threads + 32), (227 * 1024) // max(info.smem_bytes, 1)))
+            self.ext_interior = GraphExtension(self.ext.ir, lib_path=self.ext._lib_path,
+                                               max_ctas=max(1, props.multi_processor_count * resident - int(overlap_spare_ctas)),
+                                               random_gather=False)
 
     def owned(self, which: Optional[int] = None) -> torch.Tensor:
         b = self.buf[self.cur if which is None else which]
         return b[self.plan.halo_lo:self.plan.halo_lo + self.plan.rows]
 
-    def _launch(self, x, y, part=None):
-        if part is None:
-            # the two ping-pong directions are bound once each; later steps are one foreign call
-            key = (x.data_ptr(), y.data_ptr())
-            prepared = self._prepared.get(key)
-            if prepared is None:
-                prepared = self._prepared[key] = self.ext.prepare([self.vals, x], [self.cols], self.ro, [y], self.plan.rows,
-                                                                  self.nnz, self.plan.local_len)
-            prepared.launch()
-        else:
-            r0, r1, ro, cols, vals = part
-            self.ext.launch_into([vals, x], [cols], ro, [y[r0:r1]], r1 - r0, int(cols.numel()), self.plan.local_len)
+    def refresh_halos(self) -> None:
+        """Exchanges the halos of the current buffer now (after the owned part was rewritten from outside)."""
+        exchange_halos(self.buf[self.cur], self.plan, self.group)
+        self._halos_valid = True
+
+    def _prepared_launch(self, ext, key, values, indices, ro, outputs, rows, nnz):
+        prepared = self._prepared.get(key)
+        if prepared is None:       # bound once per ping-pong direction; later steps are one foreign call
+            prepared = self._prepared[key] = ext.prepare(values, indices, ro, outputs, rows, nnz, self.plan.local_len)
+        prepared.launch()
 
     def step(self) -> torch.Tensor:
-        """halo exchange + y = A_local x_local; y becomes the next iteration's owned vector."""
+        """One iteration: y = A_local x_local; y becomes the next iteration's owned vector."""
+        plan = self.plan
         x = self.buf[self.cur]
+        nxt = self.buf[1 - self.cur]
         y = self.owned(1 - self.cur)
         if not self.overlap:
-            exchange_halos(x, self.plan, self.group)
-            self._launch(x, y)
+            exchange_halos(x, plan, self.group)
+            self._prepared_launch(self.ext, ("all", self.cur), [self.vals, x], [self.cols], self.ro, [y], plan.rows, self.nnz)
         else:
-            reqs = start_halo_exchange(x, self.plan, self.group)
-            self._launch(x, y, self.parts[0])      # interior rows read no halo entry
-            for w in reqs:
+            if not self._halos_valid:
+                self.refresh_halos()
+            lo_rows, hi_rows, rows = self.lo_rows, self.hi_rows, plan.rows
+            ro_b, cols_b, vals_b = self.boundary
+            # (i) the rows that read a halo: the first / last rows of the block, one launch
+            self._prepared_launch(self.ext, ("boundary", self.cur), [vals_b, x], [cols_b], ro_b, [self.boundary_out],
+                                  lo_rows + hi_rows, int(cols_b.numel()))
+            if lo_rows:
+                y[:lo_rows].copy_(self.boundary_out[:lo_rows])
+            if hi_rows:
+                y[rows - hi_rows:].copy_(self.boundary_out[lo_rows:])
+            # (ii) their results are the neighbours' halos of the next iteration: sent now, on NCCL's stream
+            reqs = start_halo_exchange(nxt, plan, self.group)
+            # (iii) the interior rows read no halo entry: computed while the transfer is in flight
+            r0, r1, ro_i, cols_i, vals_i = self.interior
+            self._prepared_launch(self.ext_interior, ("interior", self.cur), [vals_i, x], [cols_i], ro_i, [y[r0:r1]],
+                                  r1 - r0, int(cols_i.numel()))
+            for w in reqs:           # the next iteration's first launch waits for the halos, not this one's interior
                 w.wait()
-            for part in self.parts[1:]:
-                self._launch(x, y, part)
         self.cur = 1 - self.cur
         return y
 
     @property
     def launches_per_step(self) -> int:
-        return len(self.parts) if self.overlap else 1
+        return 2 if self.overlap else 1
 
     def capture_pair(self) -> bool:
         """Captures two consecutive iterations (the buffers ping-pong, so two steps return to the same
