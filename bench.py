@@ -486,7 +486,10 @@ def run_ours(args) -> None:
     g.manual_seed(4 * 1000 + rank)
     x0 = torch.rand(plan.rows, generator=g, device=dev, dtype=torch.float64) * 2.0 - 1.0
     ext = load_builtin("spmv")
-    op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x0, ext=ext, overlap=args.overlap)
+    # measured on 8 B200s (512^3): 0.459 ms/step with the exchange in front of one launch, 0.432 ms with the boundary rows
+    # first and the exchange behind the interior launch; at 2 GPUs the split costs more than it hides (1.633 against 1.608 ms)
+    overlap = (world >= 4) if args.overlap is None else bool(args.overlap)
+    op = multi_gpu.PartitionedSpmv(plan, ro, cols, vals, x0, ext=ext, overlap=overlap, overlap_spare_ctas=args.spare_ctas)
     alg_bytes, nnz_total = poisson3d_bytes(n)
 
     def barrier():
@@ -578,8 +581,9 @@ def run_ours(args) -> None:
     hx.copy_(x0.cpu())
     lo = plan.halo_lo
     lanes = []
-    for i in range(2 if world == 1 else 1):      # the halo exchange is stream-ordered with NCCL: one lane when N > 1
-        lanes.append({"stream": torch.cuda.Stream() if world == 1 else torch.cuda.current_stream(),
+    n_lanes = args.e2e_lanes
+    for i in range(n_lanes):      # every rank issues its lanes in the same order, so the NCCL exchanges pair up across ranks
+        lanes.append({"stream": torch.cuda.Stream() if n_lanes > 1 else torch.cuda.current_stream(),
                       "xbuf": op.buf[i], "hy": torch.empty(plan.rows, dtype=torch.float64).pin_memory()})
 
     def e2e_step(i):
@@ -619,7 +623,7 @@ def run_ours(args) -> None:
     e2e = {"value": alg_bytes / e2e_ms / 1e6, "unit": UNIT, "h2d_bytes_per_step": int(hb.item()), "d2h_bytes_per_step": int(hb.item()),
            "ms_per_step": e2e_ms, "steps": E, "streams": len(lanes),
            "what": "per step: pinned-host x -> device, halo exchange, merged_spmv_launch (allocates y), y -> pinned host; steps "
-                   "alternate between two streams at N = 1 so one step's download overlaps the next step's upload; "
+                   "alternate between the streams so one step's download overlaps the next step's upload; "
                    "the CSR matrix is static across iterations and stays resident"}
 
     line = {
@@ -684,13 +688,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--grid", type=int, default=512)
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--e2e-lanes", type=int, default=2, choices=[1, 2],
+                    help="end-to-end loop: steps alternate between this many streams (one step's download overlaps the next upload)")
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table (N = 1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (N = 1)")
     ap.add_argument("--cpu-planes", type=int, default=None,
                     help="CPU arm: time this many z-planes of the matrix instead of the whole grid (hosts short of memory)")
     ap.add_argument("--only-config", type=int, default=None, choices=[0, 1, 2, 3, 5, 6, 7],
                     help="run just this single-GPU configuration (kernel-only timings) and print its entry")
-    ap.add_argument("--overlap", action="store_true", help="N > 1: split off the halo-reading rows and overlap the exchange with the interior launch")
+    ap.add_argument("--overlap", dest="overlap", action="store_true", default=None,
+                    help="N > 1: boundary rows first, halo exchange behind the interior launch (default: on from 4 GPUs)")
+    ap.add_argument("--no-overlap", dest="overlap", action="store_false", help="N > 1: exchange halos in front of one launch per step")
+    ap.add_argument("--spare-ctas", type=int, default=16, help="CTA slots the overlapped interior launch leaves to the communication kernel")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: enqueue every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
