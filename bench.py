@@ -39,7 +39,7 @@ UNIT = "GB/s"
 # flex_tile_kernel<spmv_f64, int64 offsets> on the 192^3 grid (the full-size launch holds too much memory to capture
 # with more than one pass); traffic grows in proportion to the grid, so it is scaled to the benchmarked launch by the
 # algorithmic bytes.  Part of y is still in L2 when that capture ends, so the write figure is a lower bound.
-DRAM_CAPTURE = {"grid": 192, "read_bytes": 718.3e6, "write_bytes": 24.3e6, "algorithmic_bytes": 761_757_704}
+DRAM_CAPTURE = {"grid": 192, "read_bytes": 718.1e6, "write_bytes": 24.6e6, "algorithmic_bytes": 761_757_704}
 
 
 def load_peaks():
@@ -294,7 +294,41 @@ def cpu_beside(entry: dict, ir, prob, dtype, gpu_outputs, abs_sums=None, steps: 
         raise SystemExit(f"bench.py: {entry['config']}: GPU result differs from the CPU operator: {entry['max_row_err']}")
 
 
-def single_gpu_configs(peak: float, only=None, with_cpu: bool = True) -> list:
+def probe_gather(log2_rows: int) -> dict:
+    """The chip's rate of 4-byte gathers without locality, on the config-3 arrays (flexspmv_probe_gather): the bound of
+    any kernel on that matrix, as a function of the shared memory the kernel claims per SM."""
+    import ctypes
+    import torch
+    from flexspmv_b200 import problems
+    from flexspmv_b200.binding import check, load_library
+    lib = load_library()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ro, cols, vals, x = problems.powerlaw_device(1 << log2_rows, 3, dev)
+    m = cols.numel()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    out = torch.zeros(sms * 8, device=dev)
+    rows = []
+    for kb_per_sm in (0, 32, 64, 132, 164, 196, 224):
+        def fn():
+            check(lib, lib.flexspmv_probe_gather(ctypes.c_void_p(cols.data_ptr()), ctypes.c_void_p(vals.data_ptr()),
+                                                 ctypes.c_void_p(x.data_ptr()), ctypes.c_int64(m), ctypes.c_void_p(out.data_ptr()),
+                                                 sms * 8, kb_per_sm * 1024 // 8, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                  "probe_gather")
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / 10
+        rows.append({"shared_kb_per_sm": kb_per_sm, "ms": ms, "giga_gathers_per_s": m / ms / 1e6})
+    return {"probe": "random 4-byte gathers, power-law CSR arrays", "rows": 1 << log2_rows, "edges": int(m), "results": rows}
+
+
+def single_gpu_configs(peak: float, only=None, with_cpu: bool = True, c3_log2_rows: int = 24) -> list:
     import torch
     from flexspmv_b200 import graphs, problems
     from flexspmv_b200.binding import GraphExtension
@@ -356,11 +390,11 @@ def single_gpu_configs(peak: float, only=None, with_cpu: bool = True) -> list:
         return out
     # config 3 is generated on the device (268 M non-zeros)
     ir = graphs.spmv_graph()
-    ro, cols, vals, x = problems.powerlaw_device(1 << 24, 3, dev)
+    ro, cols, vals, x = problems.powerlaw_device(1 << c3_log2_rows, 3, dev)
     n, m = x.numel(), cols.numel()
     y = torch.empty(n, dtype=torch.float32, device=dev)
     alg = problems.algorithmic_bytes(ir, n, m, n, 4, 4)
-    entry = time_config("config3 power-law CSR n=2^24 fp32", ir, GraphExtension(ir), [vals, x], [cols], ro, [y], n, m, n, alg,
+    entry = time_config(f"config3 power-law CSR n=2^{c3_log2_rows} fp32", ir, GraphExtension(ir), [vals, x], [cols], ro, [y], n, m, n, alg,
                         50, peak, flush)
     if with_cpu:
         # the full-size arrays go to the host once (2.2 GB) and through the reference's CPU operator; the error scale
@@ -467,8 +501,12 @@ def run_ours(args) -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     peak, peak_kind = load_peaks()
+    if args.probe_gather:                 # measurement aid: the gather bound of the chip on the config-3 arrays
+        print(json.dumps(probe_gather(args.config3_log2_rows)), flush=True)
+        return
     if args.only_config is not None:      # profiling aid: one single-GPU configuration, nothing else
-        print(json.dumps({"configs": single_gpu_configs(peak, only=[args.only_config], with_cpu=not args.no_cpu)}), flush=True)
+        print(json.dumps({"configs": single_gpu_configs(peak, only=[args.only_config], with_cpu=not args.no_cpu,
+                                                        c3_log2_rows=args.config3_log2_rows)}), flush=True)
         return
     n = args.grid
     n2 = n * n
@@ -700,6 +738,9 @@ def main():
                     help="N > 1: boundary rows first, halo exchange behind the interior launch (default: on from 4 GPUs)")
     ap.add_argument("--no-overlap", dest="overlap", action="store_false", help="N > 1: exchange halos in front of one launch per step")
     ap.add_argument("--spare-ctas", type=int, default=16, help="CTA slots the overlapped interior launch leaves to the communication kernel")
+    ap.add_argument("--config3-log2-rows", type=int, default=24, help="rows of the power-law matrix of config 3 (profiling: 22)")
+    ap.add_argument("--probe-gather", action="store_true",
+                    help="print the chip's rate of random 4-byte gathers on the config-3 arrays for several shared-memory sizes")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: enqueue every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

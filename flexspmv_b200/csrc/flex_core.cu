@@ -327,9 +327,46 @@ int swe_stage_launch(const void* const* r, const void* const* rb, const void* ar
   return (int)cudaGetLastError();
 }
 
+// Measurement aid (flexspmv_probe_gather): streams idx / vals with coalesced loads, gathers x[idx] and accumulates.
+// Nothing is written unless the sum hits a sentinel, so the kernel measures the rate at which an SM can issue
+// gathers; `smem_bytes` of dynamic shared memory (unused) shrink the L1 that is left to the misses in flight.
+__global__ void __launch_bounds__(256) probe_gather_kernel(const int* __restrict__ idx, const float* __restrict__ vals,
+                                                           const float* __restrict__ x, long long n, float* out) {
+  extern __shared__ float probe_dummy[];
+  constexpr int U = 4;
+  float acc = 0.f;
+  const long long chunk = (long long)blockDim.x * U;
+  for (long long base = (long long)blockIdx.x * chunk; base < n; base += (long long)gridDim.x * chunk) {
+    int id[U];
+    float v[U], g[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long e = base + (long long)u * blockDim.x + threadIdx.x;
+      id[u] = 0; v[u] = 1.f;
+      if (e < n) { id[u] = __ldcs(idx + e); v[u] = __ldcs(vals + e); }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) g[u] = __ldg(x + id[u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc += v[u] * g[u];
+  }
+  if (acc == 123.456f) out[blockIdx.x] = acc + probe_dummy[0];
+}
+
 }  // namespace flex
 
 extern "C" {
+
+int flexspmv_probe_gather(const int32_t* d_idx, const float* d_vals, const float* d_x, int64_t num_edges, float* d_out,
+                          int32_t ctas, int32_t smem_bytes_per_cta, void* stream) {
+  if (!d_idx || !d_vals || !d_x || !d_out || num_edges < 0 || ctas < 1 || smem_bytes_per_cta < 0 || smem_bytes_per_cta > 227 * 1024)
+    return FLEXSPMV_ERR_BAD_ARG;
+  const int smem = smem_bytes_per_cta < 16 ? 16 : smem_bytes_per_cta;
+  cudaError_t e = cudaFuncSetAttribute(flex::probe_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
+  flex::probe_gather_kernel<<<ctas, 256, smem, static_cast<cudaStream_t>(stream)>>>(d_idx, d_vals, d_x, num_edges, d_out);
+  return (int)cudaGetLastError();
+}
 
 int flexspmv_abi_version(void) { return FLEXSPMV_ABI_VERSION; }
 

@@ -125,6 +125,16 @@ int flexspmv_row_blocks(const void *d_row_offsets, int32_t offset_bits, int64_t 
 int flexspmv_debug_withhold_stage(void *d_workspace, uint32_t first_tile_plus_one, void *stream);
 
 /*
+ * Measurement aid: the rate at which the GPU gathers 4-byte records without locality.  Streams d_idx / d_vals
+ * (num_edges entries, coalesced), gathers d_x[d_idx[e]] and accumulates; writes nothing (d_out needs `ctas` floats
+ * and stays untouched).  `smem_bytes_per_cta` of unused dynamic shared memory per 256-thread CTA shrink the L1
+ * that is left to the misses in flight (the driver sizes the carve-out for 8 such CTAs per SM).  Time it with
+ * events: num_edges / time is the bound of any kernel that gathers this index array.  No reference counterpart.
+ */
+int flexspmv_probe_gather(const int32_t *d_idx, const float *d_vals, const float *d_x, int64_t num_edges,
+                          float *d_out, int32_t ctas, int32_t smem_bytes_per_cta, void *stream);
+
+/*
  * Host-visible copy of a workspace's status word.  `pinned_host_status` is an int32 in page-locked host
  * memory (cudaHostAlloc / cudaHostRegister; NULL removes the registration).  From then on a kernel that
  * raises FLEXSPMV_ERR_TIMEOUT or FLEXSPMV_ERR_NOT_PLANNED on this workspace also stores the code there, so
