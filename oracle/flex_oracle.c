@@ -23,7 +23,7 @@
  * identical to the OpenMP run because spans do not interact before the fix-up.
  *
  * Parity pin: checked against the reference's own generated code compiled from its sources
- * (oracle/_ref, see ref_build.py) in tests/test_oracle_vs_ref.py and against tests/golden/.
+ * (oracle/_ref, see ref_build.py) in tests/test_oracle.py and against tests/golden/.
  */
 #include <stdint.h>
 #include <stdlib.h>
