@@ -327,6 +327,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     w("  struct GRow {")
     for s in row_sel:
         w(f"    fx::Vec<V, {dim_of(s['shape'])}> {s['name']};")
+    w("@@GROW_FIELDS@@")
     if not row_sel:
         w("    int unused;")
     w("  };")
@@ -340,6 +341,7 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     for s in row_sel:
         d = dim_of(s["shape"])
         w(f"    g.{s['name']} = fx::ldg_vec<V, {d}>(p.{s['target']} + row * {d});")
+    w("@@GROW_BODY@@")
     w("    (void)p; (void)row; (void)g;")
     w("  }")
     # per-edge data that comes out of the staged arrays: copied to registers first, so that the stage can
@@ -430,8 +432,24 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
 
     # ---- map ----------------------------------------------------------------------------------------
     env: Dict[str, Var] = {}
+    # Operations whose operands are only the row's own records (row-identity gathers), literals and other such
+    # operations depend on the row, not on the edge: they are evaluated once per row in gather_row (same operations
+    # in the same order, so bit-identical) and their results travel in GRow.  FLEXSPMV_HOIST=0 keeps them per edge.
+    import os as _os
+    hoisting = _os.environ.get("FLEXSPMV_HOIST", "1") != "0"
+    row_only = {s_["name"] for s_ in ir.selector_register if s_.get("selector") == 1 and s_.get("row_identity")}
+    pure_kinds = set(_BIN) | {"neg", "exp", "abs", "sign", "norm", "getitem", "clone", "where"}
     body: List[str] = []
-    b = body.append
+    row_body: List[str] = []
+    grow_fields: List[str] = []
+    target = [body]
+
+    def b(line: str):
+        target[0].append(line)
+
+    for s_ in ir.selector_register:
+        if s_.get("selector") == 1 and s_.get("row_identity"):
+            row_body.append(f"    const fx::Vec<V, {dim_of(s_['shape'])}>& {s_['name']} = g.{s_['name']};")
     for s in ir.selector_register:
         d = dim_of(s["shape"])
         if s.get("selector") == 1:
@@ -452,6 +470,11 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     for op in ir.map_operations:
         kind, name, args = op["op"], op["name"], op["args"]
         d = dim_of(op["shape"])
+        names_used = [a_ for a_ in args if isinstance(a_, str)]
+        hoist = hoisting and kind in pure_kinds and names_used and all(a_ in row_only for a_ in names_used)
+        target[0] = row_body if hoist else body
+        if hoist:
+            row_only.add(name)
         if kind in _BIN:
             A, B = operand(args[0]), operand(args[1])
             if A.kind == "vec" and B.kind == "vec":
@@ -538,6 +561,16 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
                 b(f"    fx::accumulate_scalar<{off}, {ad}>(acc, {A.expr});")
         else:
             raise ValueError(f"Operation {kind} not supported")
+        if hoist:
+            v_ = env[name]
+            if v_.kind == "scalar":
+                grow_fields.append(f"    V {name};")
+                body.append(f"    const V {name} = gr.{name};")
+            else:
+                grow_fields.append(f"    fx::Vec<V, {v_.dim}> {name};")
+                body.append(f"    const fx::Vec<V, {v_.dim}>& {name} = gr.{name};")
+            row_body.append(f"    g.{name} = {name};")
+    target[0] = body
     for n, d, _ in map_outs:
         v = operand(n)
         if v.kind == "vec":
@@ -572,6 +605,11 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
         w("using CfgLean = flex::NoLean;")
     w(f"}}  // namespace gen_{symbol}")
     w("}  // namespace")
+    for i_, line in enumerate(L):
+        if line == "@@GROW_FIELDS@@":
+            L[i_] = "\n".join(grow_fields) if grow_fields else "    // (no row-only intermediate values)"
+        elif line == "@@GROW_BODY@@":
+            L[i_] = "\n".join(row_body) if grow_fields else "    // (nothing to evaluate per row)"
     ns = f"gen_{symbol}::"
     w(f"FLEXSPMV_DEFINE_GRAPH({symbol}, {ns}Graph, {ns}Cfg, {ns}CfgWin, {ns}CfgLean)")
     if static_scratch_bytes:

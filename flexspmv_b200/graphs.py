@@ -312,6 +312,73 @@ def swe_boundary_graph() -> GraphIR:
     return _finish("swe_boundary", inputs, outputs, selreg, m, swe_boundary_graph.__doc__)
 
 
+def swe_init_edges_graph() -> GraphIR:
+    """The per-edge part of the reference's shallow-water mesh assembler (``ShallowWaterInitializer.forward``,
+    shallow_water_equation/assemble_shallow_water.py:178-215): from the vertices of the two triangles of every
+    edge (six Selector modules on ``points``) the face vector (sx, sy) of the face the two cells share, as seen from
+    the source cell -- the one of the source's three faces whose outward normal points away from the destination's
+    centroid side test -- and the interpolation weight ``alpha`` where the centroid line crosses that face, written
+    in place into the model's sx / sy / alpha tensors (three rounds of ``where`` + ``setitem``).  Map-only graph:
+    no reducer, no allocated output.
+    Operator: merged_spmv_launch(sx, sy, alpha, points, src_p0_idx, src_p1_idx, src_p2_idx, dst_p0_idx, dst_p1_idx,
+                                 dst_p2_idx, row_end_offsets(dummy), num_rows, num_cols) -> None"""
+    S1, S2 = (1,), (2,)
+    sels = [f"src_p{i}" for i in range(3)] + [f"dst_p{i}" for i in range(3)]
+    inputs = [placeholder("sx", S1), placeholder("sy", S1), placeholder("alpha", S1), placeholder("points", S2)]
+    inputs += [selector_input(n, "points", S2) for n in sels]
+    selreg = [edge_register("sx", S1), edge_register("sy", S1), edge_register("alpha", S1)]
+    selreg += [gather_register(n, "points", S2) for n in sels]
+    m: List[Dict[str, Any]] = []
+    count = [0]
+
+    def op(kind, shape, *args, name=None):
+        count[0] += 1
+        nm = name or f"t{count[0]}_{kind}"
+        m.append(mop(nm, kind, shape, *args))
+        return nm
+
+    def xy(pt):
+        return op("getitem", S1, pt, (None, 0)), op("getitem", S1, pt, (None, 1))
+
+    def centroid(a, b, c):
+        return op("truediv", S2, op("add", S2, op("add", S2, a, b), c), 3.0)
+
+    def face_norm(p0, p1, p2):      # get_face_norm(p0, p1, p2), :164-176
+        a1, a2 = xy(p0)
+        b1, b2 = xy(p1)
+        c1, c2 = xy(p2)
+        bc1, bc2 = op("sub", S1, b1, c1), op("sub", S1, b2, c2)
+        ac1, ac2 = op("sub", S1, a1, c1), op("sub", S1, a2, c2)
+        sg = op("sign", S1, op("sub", S1, op("mul", S1, bc1, ac2), op("mul", S1, bc2, ac1)))
+        return op("mul", S1, sg, bc2), op("mul", S1, op("neg", S1, sg), bc1)
+
+    def get_alpha(sc, dc, p0, p1):  # :141-162
+        x1, y1 = xy(sc)
+        x2, y2 = xy(dc)
+        x3, y3 = xy(p0)
+        x4, y4 = xy(p1)
+        y21, y43, y31 = op("sub", S1, y2, y1), op("sub", S1, y4, y3), op("sub", S1, y3, y1)
+        x31, x21, x43 = op("sub", S1, x3, x1), op("sub", S1, x2, x1), op("sub", S1, x4, x3)
+        num = op("sub", S1, op("mul", S1, x31, y43), op("mul", S1, y31, x43))
+        den = op("sub", S1, op("mul", S1, x21, y43), op("mul", S1, y21, x43))
+        return op("truediv", S1, num, den)
+
+    sp = ["src_p0", "src_p1", "src_p2"]
+    src_cent = centroid(*sp)
+    dst_cent = centroid("dst_p0", "dst_p1", "dst_p2")
+    rounds = [((sp[2], sp[0], sp[1]), (sp[0], sp[1])), ((sp[0], sp[1], sp[2]), (sp[1], sp[2])), ((sp[1], sp[2], sp[0]), (sp[2], sp[0]))]
+    normals = [face_norm(*own) for own, _ in rounds]                          # outward normals of the source's faces
+    tests = [face_norm(dst_cent, *face) for _, face in rounds]                # the same faces seen from the destination's centroid
+    for k, ((own, face), (nx, ny), (tx, ty)) in enumerate(zip(rounds, normals, tests)):
+        cond = op("lt", S1, op("add", S1, op("mul", S1, nx, tx), op("mul", S1, ny, ty)), 0.0)
+        al = get_alpha(src_cent, dst_cent, *face)
+        prev = (0.0, 0.0, 0.0) if k == 0 else ("sx", "sy", "alpha")
+        for tgt, val, old in (("sx", nx, prev[0]), ("sy", ny, prev[1]), ("alpha", al, prev[2])):
+            w_ = op("where", S1, cond, val, old)
+            op("setitem", S1, tgt, (None,), w_)
+    return _finish("swe_init_edges", inputs, [], selreg, m, swe_init_edges_graph.__doc__)
+
+
 def mixed_dims_graph() -> GraphIR:
     """Unit-test graph shaped like the reference's demo model (easier_spmv.py:17-69, generated
     instance include/merged_agent_spmv.cuh:124-149): two selectors on one dim-2 vertex tensor, edge
@@ -393,6 +460,7 @@ ALL_GRAPHS = {
     "rusanov": rusanov_graph,
     "swe_delta": swe_delta_graph,
     "swe_boundary": swe_boundary_graph,
+    "swe_init_edges": swe_init_edges_graph,
     "mixed_dims": mixed_dims_graph,
     "ops_zoo": ops_zoo_graph,
     "edge_sum": edge_sum_graph,
@@ -406,6 +474,7 @@ GRAPH_DTYPES = {
     "rusanov": ("float64", "float32"),
     "swe_delta": ("float64", "float32"),
     "swe_boundary": ("float64", "float32"),
+    "swe_init_edges": ("float64",),
     "mixed_dims": ("float32", "float64", "int64"),
     "ops_zoo": ("float32", "float64"),
     "edge_sum": ("float32", "float64", "int64"),

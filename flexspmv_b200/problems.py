@@ -216,6 +216,34 @@ def swe_mesh(n: int = 1024, dtype=np.float64) -> Problem:
                    ro.astype(np.int32), cells, cells, {"grid": n})
 
 
+def swe_init_mesh(n: int = 64, dtype=np.float64) -> Problem:
+    """Inputs of the mesh assembler's per-edge graph (graphs.swe_init_edges_graph) for the triangulated n x n square of
+    ``swe_mesh``: the (n + 1)^2 grid ``points``, and for every interior edge the three vertex ids of its source cell
+    (src_p0..2) and of its destination cell (dst_p0..2), as the reference reads them from its mesh files
+    (shallow_water_equation/assemble_shallow_water.py:94-110).  Square (ix, iy) holds cell 2 sq = (v00, v10, v11) and
+    cell 2 sq + 1 = (v00, v11, v01).  sx / sy / alpha start at zero and are written by the graph."""
+    mesh = swe_mesh(n, np.float64)
+    src, dst = mesh.indices["gather_src"].astype(np.int64), mesh.indices["gather_dst"].astype(np.int64)
+    hs = 1.0 / n
+    g = np.arange(n + 1) * hs
+    points = np.stack(np.meshgrid(g, g, indexing="xy"), axis=-1).reshape(-1, 2)      # point iy * (n + 1) + ix = (x, y)
+    sq = np.arange(n * n)
+    iy, ix = sq // n, sq % n
+    v00 = iy * (n + 1) + ix
+    v10, v01, v11 = v00 + 1, v00 + (n + 1), v00 + (n + 2)
+    cells = np.empty((2 * n * n, 3), np.int64)
+    cells[0::2] = np.stack([v00, v10, v11], axis=1)
+    cells[1::2] = np.stack([v00, v11, v01], axis=1)
+    e = src.shape[0]
+    values = {"sx": np.zeros(e, dtype), "sy": np.zeros(e, dtype), "alpha": np.zeros(e, dtype), "points": points.astype(dtype)}
+    indices = {}
+    for i in range(3):
+        indices[f"src_p{i}"] = cells[src, i].astype(np.int32)
+        indices[f"dst_p{i}"] = cells[dst, i].astype(np.int32)
+    indices = {k: indices[k] for k in [f"src_p{i}" for i in range(3)] + [f"dst_p{i}" for i in range(3)]}
+    return Problem("swe_init_edges", values, indices, None, 0, points.shape[0], {"grid": n})
+
+
 def swe_model_inputs(n: int = 64, dtype=np.float64) -> Dict[str, np.ndarray]:
     """Every array the reference's ``ShallowWaterEquation`` module loads (shallow_water_equation/
     swe_main.py:19-81) for the triangulated n x n square: interior edges (src, dst sorted by dst, alpha,

@@ -75,6 +75,15 @@ def test_config3_full_size_properties():
     abs_sum = torch.zeros(n, dtype=torch.float64, device=dev).index_add_(0, rid, terms.abs())
     err = ((y.double() - y_ref).abs() / abs_sum.clamp_min(1e-300)).max()
     assert float(err) <= TOL[np.dtype(np.float32)]
+    # the reference's own generated CPU operator on the same full-size arrays (rows of up to 100 000 edges included)
+    from oracle import ref_run
+    if ref_run.available("spmv"):
+        prob = problems.Problem("spmv", {"vals": vals.cpu().numpy(), "x": x.cpu().numpy()}, {"selector": cols.cpu().numpy()},
+                                ro.cpu().numpy(), n, n, {"config": 3})
+        call = ref_run.PreparedCall(graphs.spmv_graph(), prob, np.float32, num_threads=min(os.cpu_count() or 8, 64), copy_inputs=False)
+        (y_cpu,) = call.run()
+        assert row_error(y.cpu().numpy(), y_cpu, abs_sum.cpu().numpy()) <= TOL[np.dtype(np.float32)]
+        del prob, call, y_cpu
     # linearity: A(2x) == 2 A x exactly in binary floating point, and determinism
     y2 = _spmv(ext, vals, x * 2.0, cols, ro, n)
     assert torch.equal(y2, y * 2.0)
@@ -184,6 +193,23 @@ def test_shallow_water_model_step_matches_model_oracle():
             got = mesh[name].cpu().numpy()
             scale = max(float(np.abs(want).max()), 1e-300)
             assert float(np.abs(got - want).max()) <= 1e-12 * scale, (name, use_graph)
+
+
+def test_mesh_assembler_edge_graph_reproduces_the_model_mesh():
+    """The per-edge part of the reference's mesh assembler as a fused map-only graph (graphs.swe_init_edges_graph):
+    bit-identical to the CPU oracle, and equal to the closed-form face vectors / weights of the synthetic mesh the
+    model tests use (the assembler's vector is the SOURCE cell's outward normal, ``swe_mesh`` stores the destination's)."""
+    ir = graphs.swe_init_edges_graph()
+    prob = problems.swe_init_mesh(96)
+    _, want, _ = ir_eval.run_graph(ir, prob, np.float64, num_threads=8, want_abs_sums=True)
+    outs, written = run_gpu(GraphExtension(ir), ir, prob, np.float64)
+    assert outs == []
+    mesh = problems.swe_mesh(96)
+    for k in ("sx", "sy", "alpha"):
+        assert np.array_equal(written[k].reshape(-1), want[k].reshape(-1)), k
+    assert np.abs(written["sx"].reshape(-1) + mesh.values["sx"]).max() <= 1e-15
+    assert np.abs(written["sy"].reshape(-1) + mesh.values["sy"]).max() <= 1e-15
+    assert np.abs(written["alpha"].reshape(-1) - 0.5).max() <= 1e-12
 
 
 def test_more_than_two_to_the_31_nonzeros():
