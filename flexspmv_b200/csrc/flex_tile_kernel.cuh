@@ -852,9 +852,10 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     cv[tid] = failed ? V(0) : s_carry[(count & 1) * kAcc + tid];
   }
   if (tid == 0) a.carry_row[blockIdx.x] = (failed || count == 0) ? a.num_rows : last_row1;
-  __threadfence();
   named_bar_sync(1, BLOCK);
   if (tid == 0) {
+    // one fence after the barrier orders every consumer thread's stores (rows, carries) before the ticket
+    __threadfence();
     const unsigned t = atomicAdd(&a.header->ticket, 1u);
     s_flag[0] = (t == gridDim.x - 1) ? 1 : 0;
   }
@@ -864,13 +865,16 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
     const int n_cta = gridDim.x;
     const V* cvals = static_cast<const V*>(a.carry_val);
     for (int c = tid; c < n_cta; c += BLOCK) {
+      // the CTA's row, its neighbours' rows and its value are requested together: one memory round trip
       const long long row = __ldcg(a.carry_row + c);
-      if (row >= a.num_rows) continue;
-      if (c > 0 && __ldcg(a.carry_row + c - 1) == row) continue;   // not the head of its run
+      const long long row_before = c > 0 ? __ldcg(a.carry_row + c - 1) : -1;
+      long long row_after = c + 1 < n_cta ? __ldcg(a.carry_row + c + 1) : -1;
       V sum[kAcc];
 #pragma unroll
       for (int i = 0; i < kAcc; ++i) sum[i] = __ldcg(cvals + (size_t)c * kAcc + i);
-      for (int c2 = c + 1; c2 < n_cta && __ldcg(a.carry_row + c2) == row; ++c2) {
+      if (row >= a.num_rows) continue;
+      if (row_before == row) continue;   // not the head of its run
+      for (int c2 = c + 1; c2 < n_cta && row_after == row; ++c2, row_after = c2 < n_cta ? __ldcg(a.carry_row + c2) : -1) {
 #pragma unroll
         for (int i = 0; i < kAcc; ++i) sum[i] += __ldcg(cvals + (size_t)c2 * kAcc + i);
       }
