@@ -248,6 +248,18 @@ __device__ __forceinline__ Vec<V, D> ld_vec(P p) {   // plain load through anyth
 
 template <typename V, int D>
 __device__ __forceinline__ void st_vec(V* p, const Vec<V, D>& a) {
+  // records of whole 16-byte chunks go out as 16-byte stores when the destination allows it (map-only gather of
+  // 16-byte records written in place: 70.7 -> 93.2 % of the HBM peak; 8-byte vector stores of fp32 pairs measured
+  // slower than two 4-byte stores, 79.4 against 85.7 %, and are not used)
+  if constexpr ((sizeof(V) * D) % 16 == 0) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+      const int4* src = reinterpret_cast<const int4*>(a.v);
+      int4* dst = reinterpret_cast<int4*>(p);
+#pragma unroll
+      for (int i = 0; i < int(sizeof(V) * D / 16); ++i) dst[i] = src[i];
+      return;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < D; ++i) p[i] = a.v[i];
 }
