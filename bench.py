@@ -622,7 +622,8 @@ def run_ours(args) -> None:
     n_lanes = args.e2e_lanes
     for i in range(n_lanes):      # every rank issues its lanes in the same order, so the NCCL exchanges pair up across ranks
         lanes.append({"stream": torch.cuda.Stream() if n_lanes > 1 else torch.cuda.current_stream(),
-                      "xbuf": op.buf[i], "hy": torch.empty(plan.rows, dtype=torch.float64).pin_memory()})
+                      "xbuf": op.buf[i] if i < 2 else torch.zeros_like(op.buf[0]),
+                      "hy": torch.empty(plan.rows, dtype=torch.float64).pin_memory()})
 
     def e2e_step(i):
         ln = lanes[i % len(lanes)]
@@ -635,7 +636,7 @@ def run_ours(args) -> None:
 
     for ln in lanes:
         ln["stream"].wait_stream(torch.cuda.current_stream())
-    for i in range(2):
+    for i in range(max(2, n_lanes)):
         e2e_step(i)
     barrier()
     a0 = torch.cuda.Event(enable_timing=True)
@@ -726,7 +727,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--grid", type=int, default=512)
     ap.add_argument("--e2e-steps", type=int, default=10)
-    ap.add_argument("--e2e-lanes", type=int, default=2, choices=[1, 2],
+    ap.add_argument("--e2e-lanes", type=int, default=2, choices=[1, 2, 3, 4],
                     help="end-to-end loop: steps alternate between this many streams (one step's download overlaps the next upload)")
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table (N = 1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (N = 1)")
