@@ -379,6 +379,49 @@ def swe_init_edges_graph() -> GraphIR:
     return _finish("swe_init_edges", inputs, [], selreg, m, swe_init_edges_graph.__doc__)
 
 
+def swe_init_cells_graph() -> GraphIR:
+    """The per-cell part of the reference's mesh assembler (shallow_water_equation/assemble_shallow_water.py:217-239):
+    from the three vertices of every cell (three Selector modules on ``points``) its area
+    ``0.5 |x0 (y1 - y2) + x1 (y2 - y0) + x2 (y0 - y1)|``, its centroid (x, y) and the initial water height
+    ``h = 1 + 0.1 exp(-100 (x^2 + y^2))``, written in place into the model's tensors (``setitem``).  Map-only graph
+    whose "edges" are the cells.
+    Operator: merged_spmv_launch(area, x, y, h, points, cells_p0_idx, cells_p1_idx, cells_p2_idx,
+                                 row_end_offsets(dummy), num_rows, num_cols) -> None"""
+    S1, S2 = (1,), (2,)
+    sels = [f"cells_p{i}" for i in range(3)]
+    inputs = [placeholder(n, S1) for n in ("area", "x", "y", "h")] + [placeholder("points", S2)]
+    inputs += [selector_input(n, "points", S2) for n in sels]
+    selreg = [edge_register(n, S1) for n in ("area", "x", "y", "h")] + [gather_register(n, "points", S2) for n in sels]
+    m: List[Dict[str, Any]] = []
+
+    def op(name, kind, shape, *args):
+        m.append(mop(name, kind, shape, *args))
+        return name
+
+    xs, ys = [], []
+    for i, sname in enumerate(sels):
+        xs.append(op(f"x{i}", "getitem", S1, sname, (None, 0)))
+        ys.append(op(f"y{i}", "getitem", S1, sname, (None, 1)))
+    t0 = op("t0", "mul", S1, xs[0], op("d12", "sub", S1, ys[1], ys[2]))
+    t1 = op("t1", "mul", S1, xs[1], op("d20", "sub", S1, ys[2], ys[0]))
+    t2 = op("t2", "mul", S1, xs[2], op("d01", "sub", S1, ys[0], ys[1]))
+    twice = op("twice", "add", S1, op("t01", "add", S1, t0, t1), t2)
+    area = op("area_v", "mul", S1, 0.5, op("abs_twice", "abs", S1, twice))
+    op("set_area", "setitem", S1, "area", (None,), area)
+    cent = op("centroid", "truediv", S2, op("p012", "add", S2, op("p01", "add", S2, sels[0], sels[1]), sels[2]), 3.0)
+    cx = op("cx", "getitem", S1, cent, (None, 0))
+    cy = op("cy", "getitem", S1, cent, (None, 1))
+    op("set_x", "setitem", S1, "x", (None,), cx)
+    op("set_y", "setitem", S1, "y", (None,), cy)
+    # the tracer records the assignments above; the height then reads the tensors just written (self.x, self.y)
+    dx2 = op("dx2", "pow", S1, op("dx", "sub", S1, "x", 0.0), 2)
+    dy2 = op("dy2", "pow", S1, op("dy", "sub", S1, "y", 0.0), 2)
+    ex = op("ex", "exp", S1, op("arg", "mul", S1, -100.0, op("r2", "add", S1, dx2, dy2)))
+    hv = op("h_v", "add", S1, 1.0, op("bump", "mul", S1, 0.1, ex))
+    op("set_h", "setitem", S1, "h", (None,), hv)
+    return _finish("swe_init_cells", inputs, [], selreg, m, swe_init_cells_graph.__doc__)
+
+
 def mixed_dims_graph() -> GraphIR:
     """Unit-test graph shaped like the reference's demo model (easier_spmv.py:17-69, generated
     instance include/merged_agent_spmv.cuh:124-149): two selectors on one dim-2 vertex tensor, edge
@@ -461,6 +504,7 @@ ALL_GRAPHS = {
     "swe_delta": swe_delta_graph,
     "swe_boundary": swe_boundary_graph,
     "swe_init_edges": swe_init_edges_graph,
+    "swe_init_cells": swe_init_cells_graph,
     "mixed_dims": mixed_dims_graph,
     "ops_zoo": ops_zoo_graph,
     "edge_sum": edge_sum_graph,
@@ -475,6 +519,7 @@ GRAPH_DTYPES = {
     "swe_delta": ("float64", "float32"),
     "swe_boundary": ("float64", "float32"),
     "swe_init_edges": ("float64",),
+    "swe_init_cells": ("float64",),
     "mixed_dims": ("float32", "float64", "int64"),
     "ops_zoo": ("float32", "float64"),
     "edge_sum": ("float32", "float64", "int64"),

@@ -244,6 +244,25 @@ def swe_init_mesh(n: int = 64, dtype=np.float64) -> Problem:
     return Problem("swe_init_edges", values, indices, None, 0, points.shape[0], {"grid": n})
 
 
+def swe_init_cells_mesh(n: int = 64, dtype=np.float64) -> Problem:
+    """Inputs of the mesh assembler's per-cell graph (graphs.swe_init_cells_graph): ``points`` and the three vertex ids
+    of every cell of the triangulated n x n square (the cell numbering of ``swe_init_mesh``); area / x / y / h start
+    at zero and are written by the graph."""
+    em = swe_init_mesh(n, dtype)
+    sq = np.arange(n * n)
+    iy, ix = sq // n, sq % n
+    v00 = iy * (n + 1) + ix
+    v10, v01, v11 = v00 + 1, v00 + (n + 1), v00 + (n + 2)
+    cells = np.empty((2 * n * n, 3), np.int64)
+    cells[0::2] = np.stack([v00, v10, v11], axis=1)
+    cells[1::2] = np.stack([v00, v11, v01], axis=1)
+    nc = cells.shape[0]
+    values = {k: np.zeros(nc, dtype) for k in ("area", "x", "y", "h")}
+    values["points"] = em.values["points"]
+    indices = {f"cells_p{i}": cells[:, i].astype(np.int32) for i in range(3)}
+    return Problem("swe_init_cells", values, indices, None, 0, em.values["points"].shape[0], {"grid": n})
+
+
 def swe_model_inputs(n: int = 64, dtype=np.float64) -> Dict[str, np.ndarray]:
     """Every array the reference's ``ShallowWaterEquation`` module loads (shallow_water_equation/
     swe_main.py:19-81) for the triangulated n x n square: interior edges (src, dst sorted by dst, alpha,

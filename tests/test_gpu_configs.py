@@ -48,7 +48,9 @@ def test_gpu_matches_golden_fixture(path):
     assert_outputs_match(ir, got, outs, sums, dt, what=os.path.basename(path))
     for k, r in written.items():
         g = got_written[k].reshape(r.shape)
-        if np.dtype(dt).kind == "i" or prob.graph != "ops_zoo":
+        if prob.graph == "swe_init_cells":           # exp / pow: the CPU's math library against CUDA's
+            assert np.allclose(g, r, rtol=1e-13, atol=0), f"in-place input {k}"
+        elif np.dtype(dt).kind == "i" or prob.graph != "ops_zoo":
             assert np.array_equal(g, r), f"in-place input {k}"
 
 

@@ -47,6 +47,7 @@ SHAPES = [
 ]
 
 CASES = [(g, dt) for g in graphs.ALL_GRAPHS for dt in graphs.GRAPH_DTYPES[g]]
+LIBM_GRAPHS = {"swe_init_cells"}      # graphs whose in-place results pass through pow / exp
 
 
 @pytest.mark.parametrize("gname,dt", CASES)
@@ -61,7 +62,10 @@ def test_graph_matches_oracle(gname, dt):
         assert_outputs_match(ir, got, ref, sums, dtype, what=f"{gname}/{dt}/{nr}x{nnz}")
         for name, arr in ref_written.items():     # in-place map ops write through input pointers
             g = got_written[name].reshape(arr.shape)
-            assert np.array_equal(g, arr), f"{gname}: in-place input {name} differs"
+            if gname in LIBM_GRAPHS:               # pow / exp come from two different math libraries
+                assert np.allclose(g, arr, rtol=1e-5 if dtype == np.float32 else 1e-13, atol=0, equal_nan=True), f"{gname}: in-place input {name}"
+            else:
+                assert np.array_equal(g, arr), f"{gname}: in-place input {name} differs"
 
 
 @pytest.mark.parametrize("tile_items", [1, 7, 320, 896, 1000])
