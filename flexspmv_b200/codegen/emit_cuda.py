@@ -141,7 +141,10 @@ TUNED_CONFIGS = {
 # (threads per CTA, merge items per lane, min CTAs per SM).  It is built for graphs whose gathers all depend on the
 # edge and whose accumulator is at most 16 bytes wide (its one shared-memory buffer holds a product per item, and
 # the point of the kernel is to leave the shared-memory / L1 array to the gathers).
-LEAN_CONFIG = (256, 5, 4)
+# Measured on the power-law matrix (fp32, % of the HBM peak): one CTA of 1024 threads per SM 27.6, 2 x 512 26.9, 4 x 256 26.1,
+# 8 x 128 24.3, 16 x 64 23.0 (the same 32 warps per SM every time; the driver sizes the shared-memory carve-out for the
+# largest number of CTAs the kernel could have resident, so few large CTAs leave the most L1); 6 / 7 items per lane 27.6 / 25.5.
+LEAN_CONFIG = (1024, 5, 1)
 TUNED_LEAN_CONFIGS = {
 }
 
