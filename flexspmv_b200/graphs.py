@@ -422,6 +422,40 @@ def swe_init_cells_graph() -> GraphIR:
     return _finish("swe_init_cells", inputs, [], selreg, m, swe_init_cells_graph.__doc__)
 
 
+def swe_init_boundary_graph() -> GraphIR:
+    """The boundary part of the reference's mesh assembler (shallow_water_equation/assemble_shallow_water.py:241-248):
+    for every boundary face the two end points (Selector modules ``bp0`` / ``bp1`` on ``points``) and the centroid of
+    the cell the face belongs to (Selector ``bcells`` on the centroids computed by the per-cell part), giving the face
+    vector that points out of the domain, ``(bsx, bsy) = -get_face_norm(centroid, p0, p1)``, written in place
+    (``setitem``).  Map-only graph whose "edges" are the boundary faces; two gather sources of different lengths.
+    Operator: merged_spmv_launch(bsx, bsy, points, centroid, bp0_idx, bp1_idx, bcells_idx,
+                                 row_end_offsets(dummy), num_rows, num_cols) -> None"""
+    S1, S2 = (1,), (2,)
+    inputs = [placeholder("bsx", S1), placeholder("bsy", S1), placeholder("points", S2), placeholder("centroid", S2),
+              selector_input("bp0", "points", S2), selector_input("bp1", "points", S2),
+              selector_input("bcells", "centroid", S2)]
+    selreg = [edge_register("bsx", S1), edge_register("bsy", S1), gather_register("bp0", "points", S2),
+              gather_register("bp1", "points", S2), gather_register("bcells", "centroid", S2)]
+    m: List[Dict[str, Any]] = []
+
+    def op(name, kind, shape, *args):
+        m.append(mop(name, kind, shape, *args))
+        return name
+
+    # get_face_norm(p0 = centroid, p1 = b_p0, p2 = b_p1), :164-176
+    a1, a2 = op("a1", "getitem", S1, "bcells", (None, 0)), op("a2", "getitem", S1, "bcells", (None, 1))
+    b1, b2 = op("b1", "getitem", S1, "bp0", (None, 0)), op("b2", "getitem", S1, "bp0", (None, 1))
+    c1, c2 = op("c1", "getitem", S1, "bp1", (None, 0)), op("c2", "getitem", S1, "bp1", (None, 1))
+    bc1, bc2 = op("bc1", "sub", S1, b1, c1), op("bc2", "sub", S1, b2, c2)
+    ac1, ac2 = op("ac1", "sub", S1, a1, c1), op("ac2", "sub", S1, a2, c2)
+    sg = op("sg", "sign", S1, op("cross", "sub", S1, op("m0", "mul", S1, bc1, ac2), op("m1", "mul", S1, bc2, ac1)))
+    nx = op("nx", "mul", S1, sg, bc2)
+    ny = op("ny", "mul", S1, op("nsg", "neg", S1, sg), bc1)
+    op("set_bsx", "setitem", S1, "bsx", (None,), op("neg_nx", "neg", S1, nx))
+    op("set_bsy", "setitem", S1, "bsy", (None,), op("neg_ny", "neg", S1, ny))
+    return _finish("swe_init_boundary", inputs, [], selreg, m, swe_init_boundary_graph.__doc__)
+
+
 def mixed_dims_graph() -> GraphIR:
     """Unit-test graph shaped like the reference's demo model (easier_spmv.py:17-69, generated
     instance include/merged_agent_spmv.cuh:124-149): two selectors on one dim-2 vertex tensor, edge
@@ -505,6 +539,7 @@ ALL_GRAPHS = {
     "swe_boundary": swe_boundary_graph,
     "swe_init_edges": swe_init_edges_graph,
     "swe_init_cells": swe_init_cells_graph,
+    "swe_init_boundary": swe_init_boundary_graph,
     "mixed_dims": mixed_dims_graph,
     "ops_zoo": ops_zoo_graph,
     "edge_sum": edge_sum_graph,
@@ -520,6 +555,7 @@ GRAPH_DTYPES = {
     "swe_boundary": ("float64", "float32"),
     "swe_init_edges": ("float64",),
     "swe_init_cells": ("float64",),
+    "swe_init_boundary": ("float64",),
     "mixed_dims": ("float32", "float64", "int64"),
     "ops_zoo": ("float32", "float64"),
     "edge_sum": ("float32", "float64", "int64"),

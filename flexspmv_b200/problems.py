@@ -187,8 +187,9 @@ def swe_mesh(n: int = 1024, dtype=np.float64) -> Problem:
     """Inputs of the reference shallow-water model's fused ``delta`` graph (graphs.swe_delta_graph) on the
     triangulated n x n square of ``shallow_water``: one directed edge per interior face and side (src =
     the neighbour, dst = the cell the flux is scattered to), sorted by dst, so boundary cells have 2
-    edges (1 in two corners) and interior cells 3; face vectors (sx, sy) = outward normal x length as seen
-    from dst, interpolation weight alpha = 0.5 (equal-size cells), h as in ``shallow_water`` and a smooth
+    edges (1 in two corners) and interior cells 3; face vectors (sx, sy) = the SOURCE cell's outward normal x length
+    (it points into dst), the orientation the reference's assembler writes
+    (shallow_water_equation/assemble_shallow_water.py:178-215), interpolation weight alpha = 0.5 (equal-size cells), h as in ``shallow_water`` and a smooth
     non-zero momentum field.  Deterministic (no rng).  The reference reads the same arrays from its HDF5
     mesh files (shallow_water_equation/swe_main.py:19-75)."""
     base = shallow_water(n, np.float64)
@@ -209,7 +210,7 @@ def swe_mesh(n: int = 1024, dtype=np.float64) -> Problem:
     h = base.values["U"][:, 0]
     uh = 0.05 * h * np.sin(2 * np.pi * cx) * np.cos(2 * np.pi * cy)
     vh = -0.05 * h * np.cos(2 * np.pi * cx) * np.sin(2 * np.pi * cy)
-    values = {"alpha": np.full(src.shape[0], 0.5), "sx": face[:, 0] * face[:, 2], "sy": face[:, 1] * face[:, 2],
+    values = {"alpha": np.full(src.shape[0], 0.5), "sx": 0.0 - face[:, 0] * face[:, 2], "sy": 0.0 - face[:, 1] * face[:, 2],
               "h": h, "uh": uh, "vh": vh}
     return Problem("swe_delta", {k: np.ascontiguousarray(v.astype(dtype)) for k, v in values.items()},
                    {"gather_src": src.astype(np.int32), "gather_dst": dst.astype(np.int32)},
@@ -263,11 +264,37 @@ def swe_init_cells_mesh(n: int = 64, dtype=np.float64) -> Problem:
     return Problem("swe_init_cells", values, indices, None, 0, em.values["points"].shape[0], {"grid": n})
 
 
+def swe_init_boundary_mesh(n: int = 64, dtype=np.float64) -> Problem:
+    """Inputs of the mesh assembler's boundary graph (graphs.swe_init_boundary_graph) for the triangulated n x n
+    square: one record per wall face -- its two end points (bp0, bp1) and the cell it belongs to (bcells; a corner
+    cell with two wall faces appears twice) -- plus ``points`` and the cell centroids the per-cell graph computes.
+    bsx / bsy start at zero and are written by the graph."""
+    cm = swe_init_cells_mesh(n, dtype)
+    points = cm.values["points"]
+    cells = np.stack([cm.indices[f"cells_p{i}"].astype(np.int64) for i in range(3)], axis=1)
+    centroid = ((points[cells[:, 0]] + points[cells[:, 1]]) + points[cells[:, 2]]) / 3.0
+    ix, iy = points[:, 0] * n, points[:, 1] * n
+    on_wall = lambda a, b: (((ix[a] == 0) & (ix[b] == 0)) | ((ix[a] == n) & (ix[b] == n)) |
+                            ((iy[a] == 0) & (iy[b] == 0)) | ((iy[a] == n) & (iy[b] == n)))
+    recs = []
+    for f in range(3):
+        a, b = cells[:, f], cells[:, (f + 1) % 3]
+        c = np.flatnonzero(on_wall(a, b))
+        recs.append(np.stack([c, a[c], b[c]], axis=1))
+    rec = np.concatenate(recs)
+    rec = rec[np.argsort(rec[:, 0], kind="stable")]
+    nb = rec.shape[0]
+    values = {"bsx": np.zeros(nb, dtype), "bsy": np.zeros(nb, dtype), "points": points, "centroid": centroid.astype(dtype)}
+    indices = {"bp0": rec[:, 1].astype(np.int32), "bp1": rec[:, 2].astype(np.int32), "bcells": rec[:, 0].astype(np.int32)}
+    return Problem("swe_init_boundary", values, indices, None, 0, points.shape[0], {"grid": n})
+
+
 def swe_model_inputs(n: int = 64, dtype=np.float64) -> Dict[str, np.ndarray]:
     """Every array the reference's ``ShallowWaterEquation`` module loads (shallow_water_equation/
     swe_main.py:19-81) for the triangulated n x n square: interior edges (src, dst sorted by dst, alpha,
-    sx, sy) as in ``swe_mesh``; boundary cells ``bcells`` (sorted) with the summed outward face vector
-    (bsx, bsy) of their wall faces; cell ``area``; initial h, uh, vh."""
+    sx, sy) as in ``swe_mesh``; boundary cells ``bcells`` (sorted) with the summed face vector (bsx, bsy)
+    of their wall faces, pointing INTO the domain as the reference's assembler writes it
+    (shallow_water_equation/assemble_shallow_water.py:241-248); cell ``area``; initial h, uh, vh."""
     interior = swe_mesh(n, dtype)
     base = shallow_water(n, np.float64)
     nbr = base.indices["sel_nbr"].astype(np.int64)
@@ -282,7 +309,7 @@ def swe_model_inputs(n: int = 64, dtype=np.float64) -> Dict[str, np.ndarray]:
     d = dict(interior.values)
     d.update({"src": interior.indices["gather_src"], "dst": interior.indices["gather_dst"],
               "row_offsets": interior.row_offsets, "bcells": bcells.astype(np.int32),
-              "bsx": bx[bcells].astype(dtype), "bsy": by[bcells].astype(dtype),
+              "bsx": (0.0 - bx[bcells]).astype(dtype), "bsy": (0.0 - by[bcells]).astype(dtype),
               "area": np.full(cells, 0.5 * hs * hs, dtype=dtype)})
     return d
 

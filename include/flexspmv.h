@@ -285,6 +285,7 @@ FLEXSPMV_DECLARE_GRAPH(swe_boundary_f64)
 FLEXSPMV_DECLARE_GRAPH(swe_boundary_f32)
 FLEXSPMV_DECLARE_GRAPH(swe_init_edges_f64)
 FLEXSPMV_DECLARE_GRAPH(swe_init_cells_f64)
+FLEXSPMV_DECLARE_GRAPH(swe_init_boundary_f64)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_f32)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_f64)
 FLEXSPMV_DECLARE_GRAPH(mixed_dims_i64)

@@ -30,6 +30,7 @@ CASES = [
     ("swe_boundary_f64_cut_rows", "swe_boundary", np.float64, lambda ir: problems.random_problem(ir, 400, 400, 150, 15, np.float64), 4),
     ("swe_init_edges_f64_mesh_10", "swe_init_edges", np.float64, lambda ir: problems.swe_init_mesh(10), 4),
     ("swe_init_cells_f64_mesh_10", "swe_init_cells", np.float64, lambda ir: problems.swe_init_cells_mesh(10), 4),
+    ("swe_init_boundary_f64_mesh_10", "swe_init_boundary", np.float64, lambda ir: problems.swe_init_boundary_mesh(10), 4),
     ("mixed_dims_f64", "mixed_dims", np.float64, lambda ir: problems.random_problem(ir, 150, 90, 2500, 9, np.float64), 4),
     ("mixed_dims_i64", "mixed_dims", np.int64, lambda ir: problems.random_problem(ir, 150, 90, 2500, 10, np.int64), 4),
     ("ops_zoo_f64", "ops_zoo", np.float64, lambda ir: problems.random_problem(ir, 120, 80, 2000, 11, np.float64), 4),

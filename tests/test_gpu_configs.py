@@ -200,7 +200,7 @@ def test_shallow_water_model_step_matches_model_oracle():
 def test_mesh_assembler_edge_graph_reproduces_the_model_mesh():
     """The per-edge part of the reference's mesh assembler as a fused map-only graph (graphs.swe_init_edges_graph):
     bit-identical to the CPU oracle, and equal to the closed-form face vectors / weights of the synthetic mesh the
-    model tests use (the assembler's vector is the SOURCE cell's outward normal, ``swe_mesh`` stores the destination's)."""
+    model tests use."""
     ir = graphs.swe_init_edges_graph()
     prob = problems.swe_init_mesh(96)
     _, want, _ = ir_eval.run_graph(ir, prob, np.float64, num_threads=8, want_abs_sums=True)
@@ -209,9 +209,28 @@ def test_mesh_assembler_edge_graph_reproduces_the_model_mesh():
     mesh = problems.swe_mesh(96)
     for k in ("sx", "sy", "alpha"):
         assert np.array_equal(written[k].reshape(-1), want[k].reshape(-1)), k
-    assert np.abs(written["sx"].reshape(-1) + mesh.values["sx"]).max() <= 1e-15
-    assert np.abs(written["sy"].reshape(-1) + mesh.values["sy"]).max() <= 1e-15
+    assert np.abs(written["sx"].reshape(-1) - mesh.values["sx"]).max() <= 1e-15
+    assert np.abs(written["sy"].reshape(-1) - mesh.values["sy"]).max() <= 1e-15
     assert np.abs(written["alpha"].reshape(-1) - 0.5).max() <= 1e-12
+
+
+def test_mesh_assembler_boundary_graph_reproduces_the_model_boundary():
+    """The boundary part of the reference's mesh assembler (graphs.swe_init_boundary_graph; two gather sources of
+    different lengths): bit-identical to the CPU oracle, and its face vectors, summed per boundary cell, are the
+    bsx / bsy the model tests use."""
+    ir = graphs.swe_init_boundary_graph()
+    prob = problems.swe_init_boundary_mesh(96)
+    _, want, _ = ir_eval.run_graph(ir, prob, np.float64, num_threads=8, want_abs_sums=True)
+    outs, written = run_gpu(GraphExtension(ir), ir, prob, np.float64)
+    assert outs == []
+    for k in ("bsx", "bsy"):
+        assert np.array_equal(written[k].reshape(-1), want[k].reshape(-1)), k
+    m = problems.swe_model_inputs(96)
+    cells = 2 * 96 * 96
+    for k in ("bsx", "bsy"):
+        per_cell = np.bincount(prob.indices["bcells"], weights=written[k].reshape(-1), minlength=cells)
+        assert np.abs(per_cell[m["bcells"]] - m[k]).max() <= 1e-15, k
+    assert np.array_equal(np.unique(prob.indices["bcells"]), m["bcells"])
 
 
 def test_more_than_two_to_the_31_nonzeros():
