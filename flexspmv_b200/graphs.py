@@ -456,6 +456,29 @@ def swe_init_boundary_graph() -> GraphIR:
     return _finish("swe_init_boundary", inputs, [], selreg, m, swe_init_boundary_graph.__doc__)
 
 
+def swe_components_graph() -> GraphIR:
+    """The gathering part of the reference's mesh-components collector (``ShallowWaterMeshComponentsCollector.forward``,
+    shallow_water_equation/assemble_shallow_water.py:62-72): for every edge the three vertex ids of its source cell and
+    of its destination cell (two Selector modules on the (nc, 3) ``cells`` tensor), column by column into six
+    per-edge tensors (``getitem`` / ``clone`` / ``copy_``).  Integer map-only graph; the per-cell and per-boundary
+    columns the same module copies (:74-78) are slices of its inputs and need no gather.
+    Operator: merged_spmv_launch(src_p0, src_p1, src_p2, dst_p0, dst_p1, dst_p2, cells, src_idx, dst_idx,
+                                 row_end_offsets(dummy), num_rows, num_cols) -> None"""
+    S1, S3 = (1,), (3,)
+    outs = [f"src_p{i}" for i in range(3)] + [f"dst_p{i}" for i in range(3)]
+    inputs = [placeholder(n, S1) for n in outs] + [placeholder("cells", S3)]
+    inputs += [selector_input("selector_src", "cells", S3), selector_input("selector_dst", "cells", S3)]
+    selreg = [edge_register(n, S1) for n in outs]
+    selreg += [gather_register("selector_src", "cells", S3), gather_register("selector_dst", "cells", S3)]
+    m: List[Dict[str, Any]] = []
+    for i in range(3):
+        for side in ("src", "dst"):
+            m.append(mop(f"{side}_col{i}", "getitem", S1, f"selector_{side}", (None, i)))
+            m.append(mop(f"{side}_clone{i}", "clone", S1, f"{side}_col{i}"))
+            m.append(mop(f"{side}_copy{i}", "copy_", S1, f"{side}_p{i}", f"{side}_clone{i}"))
+    return _finish("swe_components", inputs, [], selreg, m, swe_components_graph.__doc__)
+
+
 def mixed_dims_graph() -> GraphIR:
     """Unit-test graph shaped like the reference's demo model (easier_spmv.py:17-69, generated
     instance include/merged_agent_spmv.cuh:124-149): two selectors on one dim-2 vertex tensor, edge
@@ -537,6 +560,7 @@ ALL_GRAPHS = {
     "rusanov": rusanov_graph,
     "swe_delta": swe_delta_graph,
     "swe_boundary": swe_boundary_graph,
+    "swe_components": swe_components_graph,
     "swe_init_edges": swe_init_edges_graph,
     "swe_init_cells": swe_init_cells_graph,
     "swe_init_boundary": swe_init_boundary_graph,
@@ -553,6 +577,7 @@ GRAPH_DTYPES = {
     "rusanov": ("float64", "float32"),
     "swe_delta": ("float64", "float32"),
     "swe_boundary": ("float64", "float32"),
+    "swe_components": ("int64",),
     "swe_init_edges": ("float64",),
     "swe_init_cells": ("float64",),
     "swe_init_boundary": ("float64",),

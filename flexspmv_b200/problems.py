@@ -289,6 +289,32 @@ def swe_init_boundary_mesh(n: int = 64, dtype=np.float64) -> Problem:
     return Problem("swe_init_boundary", values, indices, None, 0, points.shape[0], {"grid": n})
 
 
+def swe_raw_mesh(n: int = 64) -> Dict[str, np.ndarray]:
+    """The arrays of the reference's MESH file (shallow_water_equation/assemble_shallow_water.py:14-31,85-112) for the
+    triangulated n x n square of ``swe_mesh``: ``points`` (np, 2), ``cells`` (nc, 3), ``src`` / ``dst`` (edges sorted by
+    dst), ``bcells`` and ``bpoints`` (one record per wall face; a corner cell with two wall faces appears twice)."""
+    cm = swe_init_cells_mesh(n)
+    em = swe_mesh(n)
+    bm = swe_init_boundary_mesh(n)
+    cells = np.stack([cm.indices[f"cells_p{i}"].astype(np.int64) for i in range(3)], axis=1)
+    return {"points": cm.values["points"], "cells": cells,
+            "src": em.indices["gather_src"].astype(np.int64), "dst": em.indices["gather_dst"].astype(np.int64),
+            "bcells": bm.indices["bcells"].astype(np.int64),
+            "bpoints": np.stack([bm.indices["bp0"], bm.indices["bp1"]], axis=1).astype(np.int64)}
+
+
+def swe_components_mesh(n: int = 64, dtype=np.int64) -> Problem:
+    """Inputs of the components-collector graph (graphs.swe_components_graph): ``cells`` and the edge lists of
+    ``swe_raw_mesh``; the six per-edge outputs start at zero and are written by the graph."""
+    raw = swe_raw_mesh(n)
+    e = raw["src"].shape[0]
+    values = {f"{side}_p{i}": np.zeros(e, dtype) for side in ("src", "dst") for i in range(3)}
+    values = {k: values[k] for k in [f"src_p{i}" for i in range(3)] + [f"dst_p{i}" for i in range(3)]}
+    values["cells"] = raw["cells"].astype(dtype)
+    indices = {"selector_src": raw["src"].astype(np.int32), "selector_dst": raw["dst"].astype(np.int32)}
+    return Problem("swe_components", values, indices, None, 0, raw["cells"].shape[0], {"grid": n})
+
+
 def swe_model_inputs(n: int = 64, dtype=np.float64) -> Dict[str, np.ndarray]:
     """Every array the reference's ``ShallowWaterEquation`` module loads (shallow_water_equation/
     swe_main.py:19-81) for the triangulated n x n square: interior edges (src, dst sorted by dst, alpha,

@@ -106,3 +106,48 @@ class ShallowWaterStep:
         if self._graph is None:
             raise RuntimeError("capture() first")
         self._graph.replay()
+
+
+def assemble_shallow_water(mesh: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """The reference's mesh assembler (``assemble_shallow_water``, shallow_water_equation/assemble_shallow_water.py:
+    251-291) on the fused operators, with tensors where the reference reads and writes HDF5 data sets.
+
+    ``mesh``: CUDA tensors named as the mesh file's data sets -- points (np, 2) float64, cells (nc, 3), src, dst (ne,),
+    bcells (nbc,), bpoints (nbc, 2), all integer.  Returns what the reference saves: src_p0..2, dst_p0..2, cells_p0..2,
+    bp0..1 (int64) and x, y, area, sx, sy, bsx, bsy, h, alpha (float64).  Four launches: the components collector's
+    gathers (``swe_components``), then the initializer's per-edge, per-cell and boundary parts (``swe_init_edges``,
+    ``swe_init_cells``, ``swe_init_boundary``); the column slices the collector also copies (:74-78) are torch slices.
+    """
+    points = mesh["points"].contiguous()
+    dev = points.device
+    cells = mesh["cells"].to(torch.int64).contiguous()
+    nc, ne, nbc, npnt = int(cells.shape[0]), int(mesh["src"].numel()), int(mesh["bcells"].numel()), int(points.shape[0])
+    i32 = lambda t: t.to(torch.int32).contiguous()
+    dummy = torch.zeros(1, dtype=torch.int32, device=dev)      # row_end_offsets of a graph without a reducer
+    out: Dict[str, torch.Tensor] = {}
+
+    # ShallowWaterMeshComponentsCollector.forward (:62-78)
+    comp = [torch.zeros(ne, dtype=torch.int64, device=dev) for _ in range(6)]
+    load_builtin("swe_components").launch_into(comp + [cells], [i32(mesh["src"]), i32(mesh["dst"])], dummy, [], 0, ne, nc)
+    for i in range(3):
+        out[f"src_p{i}"], out[f"dst_p{i}"] = comp[i], comp[3 + i]
+        out[f"cells_p{i}"] = cells[:, i].clone()
+    bpoints = mesh["bpoints"].to(torch.int64)
+    for i in range(2):
+        out[f"bp{i}"] = bpoints[:, i].clone()
+
+    # ShallowWaterInitializer.forward (:178-248)
+    f64 = lambda n_: torch.zeros(n_, dtype=torch.float64, device=dev)
+    for k in ("sx", "sy", "alpha"):
+        out[k] = f64(ne)
+    load_builtin("swe_init_edges").launch_into([out["sx"], out["sy"], out["alpha"], points],
+                                               [i32(c) for c in comp], dummy, [], 0, ne, npnt)
+    for k in ("area", "x", "y", "h"):
+        out[k] = f64(nc)
+    load_builtin("swe_init_cells").launch_into([out["area"], out["x"], out["y"], out["h"], points],
+                                               [i32(out[f"cells_p{i}"]) for i in range(3)], dummy, [], 0, nc, npnt)
+    centroid = torch.stack([out["x"], out["y"]], dim=1).contiguous()
+    out["bsx"], out["bsy"] = f64(nbc), f64(nbc)
+    load_builtin("swe_init_boundary").launch_into([out["bsx"], out["bsy"], points, centroid],
+                                                  [i32(out["bp0"]), i32(out["bp1"]), i32(mesh["bcells"])], dummy, [], 0, nbc, npnt)
+    return out

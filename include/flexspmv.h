@@ -283,6 +283,7 @@ FLEXSPMV_DECLARE_GRAPH(swe_delta_f64)
 FLEXSPMV_DECLARE_GRAPH(swe_delta_f32)
 FLEXSPMV_DECLARE_GRAPH(swe_boundary_f64)
 FLEXSPMV_DECLARE_GRAPH(swe_boundary_f32)
+FLEXSPMV_DECLARE_GRAPH(swe_components_i64)
 FLEXSPMV_DECLARE_GRAPH(swe_init_edges_f64)
 FLEXSPMV_DECLARE_GRAPH(swe_init_cells_f64)
 FLEXSPMV_DECLARE_GRAPH(swe_init_boundary_f64)

@@ -28,6 +28,7 @@ CASES = [
     ("swe_delta_f64_mesh_12", "swe_delta", np.float64, lambda ir: problems.swe_mesh(12), 6),
     ("swe_delta_f32_cut_rows", "swe_delta", np.float32, lambda ir: problems.random_problem(ir, 200, 200, 4000, 14, np.float32), 5),
     ("swe_boundary_f64_cut_rows", "swe_boundary", np.float64, lambda ir: problems.random_problem(ir, 400, 400, 150, 15, np.float64), 4),
+    ("swe_components_i64_mesh_10", "swe_components", np.int64, lambda ir: problems.swe_components_mesh(10), 4),
     ("swe_init_edges_f64_mesh_10", "swe_init_edges", np.float64, lambda ir: problems.swe_init_mesh(10), 4),
     ("swe_init_cells_f64_mesh_10", "swe_init_cells", np.float64, lambda ir: problems.swe_init_cells_mesh(10), 4),
     ("swe_init_boundary_f64_mesh_10", "swe_init_boundary", np.float64, lambda ir: problems.swe_init_boundary_mesh(10), 4),

@@ -233,6 +233,43 @@ def test_mesh_assembler_boundary_graph_reproduces_the_model_boundary():
     assert np.array_equal(np.unique(prob.indices["bcells"]), m["bcells"])
 
 
+def test_mesh_assembler_end_to_end_feeds_the_model():
+    """The reference's whole ``assemble_shallow_water`` flow (components collector + initializer) as four launches
+    (flexspmv_b200.shallow_water.assemble_shallow_water) from the raw mesh arrays: every saved data set equals the
+    synthetic mesh the model tests use, and three model steps from the assembled mesh match the model oracle."""
+    from flexspmv_b200.shallow_water import ShallowWaterStep, assemble_shallow_water
+    from oracle import swe_model
+    dev = torch.device("cuda:0")
+    n = 48
+    raw = problems.swe_raw_mesh(n)
+    sw = assemble_shallow_water({k: torch.from_numpy(v).to(dev) for k, v in raw.items()})
+    torch.cuda.synchronize()
+    edges, cellsp, bnd = problems.swe_init_mesh(n), problems.swe_init_cells_mesh(n), problems.swe_init_boundary_mesh(n)
+    for k, v in list(edges.indices.items()) + list(cellsp.indices.items()) + [(k, bnd.indices[k]) for k in ("bp0", "bp1")]:
+        assert np.array_equal(sw[k].cpu().numpy(), v.astype(np.int64)), k
+    m = problems.swe_model_inputs(n)
+    for k, tol in (("sx", 1e-15), ("sy", 1e-15), ("area", 1e-15), ("alpha", 1e-12)):   # alpha is a quotient of differences
+        assert np.abs(sw[k].cpu().numpy() - m[k]).max() <= tol, k
+    hs = 1.0 / n
+    assert np.abs(sw["x"].cpu().numpy()[0::2] - (np.arange(n * n) % n + 2.0 / 3.0) * hs).max() <= 1e-15
+    # the model on the assembled mesh: one boundary record per wall face (a corner cell twice), momentum as in the model tests
+    host = {k: v.cpu().numpy() for k, v in sw.items()}
+    mm = {"src": raw["src"].astype(np.int32), "dst": raw["dst"].astype(np.int32), "bcells": raw["bcells"].astype(np.int32),
+          "uh": m["uh"], "vh": m["vh"]}
+    mm.update({k: host[k] for k in ("alpha", "sx", "sy", "bsx", "bsy", "area", "h")})
+    h, uh, vh = mm["h"], mm["uh"], mm["vh"]
+    for _ in range(3):
+        h, uh, vh = swe_model.forward(mm, h, uh, vh, dt=0.005)
+    mesh = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in mm.items()}
+    step = ShallowWaterStep(mesh, dt=0.005)
+    for _ in range(3):
+        step.forward()
+    torch.cuda.synchronize()
+    for name, want in (("h", h), ("uh", uh), ("vh", vh)):
+        got = mesh[name].cpu().numpy()
+        assert float(np.abs(got - want).max()) <= 1e-12 * max(float(np.abs(want).max()), 1e-300), name
+
+
 def test_more_than_two_to_the_31_nonzeros():
     """A 688^3 7-point Laplacian has 2.27e9 non-zeros: edge positions no longer fit 32 bits (the reference's
     OffsetT is int only).  Checked against the stencil applied with torch slicing."""
