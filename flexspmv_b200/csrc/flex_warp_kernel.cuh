@@ -104,26 +104,32 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
   for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
   long long end_row = a.num_rows;      // row the final carry belongs to (num_rows: none)
 
-  // chunk coordinates, two chunks ahead: lanes 0..3 hold (row, edge) of the chunk's begin and end
-  auto load_coords = [&](long long c) -> long long { return (lane < 4) ? (long long)coords[2 * c + lane] : 0; };
+  // A chunk boundary is a (row, edge) pair; every lane reads the same pair (one broadcast transaction, no shuffles).
+  auto load_pair = [&](long long c, OffsetT& x, OffsetT& y) {
+    if constexpr (sizeof(OffsetT) == 4) {
+      const int2 v = __ldg(reinterpret_cast<const int2*>(coords) + c);
+      x = v.x; y = v.y;
+    } else {
+      const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(coords) + c);
+      x = v.x; y = v.y;
+    }
+  };
   // per-edge records of one chunk into registers (lanes on consecutive edges)
-  auto load_edges = [&](long long y0, int ne, typename G::EReg (&er)[IPT]) {
+  auto load_edges = [&](OffsetT y0, int ne, typename G::EReg (&er)[IPT]) {
+    const long long e0 = (long long)y0 + lane;
 #pragma unroll
     for (int i = 0; i < IPT; ++i)
-      if (i * 32 + lane < ne) G::load_edge(p, tile, y0 + (i * 32 + lane), y0 + (i * 32 + lane), er[i]);
+      if (i * 32 + lane < ne) G::load_edge(p, tile, e0 + i * 32, e0 + i * 32, er[i]);
   };
 
-  long long cw = count ? load_coords(c_begin) : 0;
-  long long cw_next = count > 1 ? load_coords(c_begin + 1) : 0;
+  // boundaries of the current chunk (x0, y0) .. (x1, y1) and the two after it
+  OffsetT x0 = 0, y0 = 0, x1 = 0, y1 = 0, x2 = 0, y2 = 0;
+  if (count) { load_pair(c_begin, x0, y0); load_pair(c_begin + 1, x1, y1); }
+  if (count > 1) load_pair(c_begin + 2, x2, y2);
   typename G::EReg er[IPT];
-  {
-    const long long y0 = __shfl_sync(0xffffffffu, cw, 1), y1 = __shfl_sync(0xffffffffu, cw, 3);
-    if (count) load_edges(y0, (int)(y1 - y0), er);
-  }
+  if (count) load_edges(y0, (int)(y1 - y0), er);
 
   for (int k = 0; k < count; ++k) {
-    const long long x0 = __shfl_sync(0xffffffffu, cw, 0), y0 = __shfl_sync(0xffffffffu, cw, 1);
-    const long long x1 = __shfl_sync(0xffffffffu, cw, 2), y1 = __shfl_sync(0xffffffffu, cw, 3);
     const int ne = (int)(y1 - y0), nr = (int)(x1 - x0);
 
     // gathers of this chunk go out first
@@ -132,74 +138,65 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     for (int i = 0; i < IPT; ++i)
       if (i * 32 + lane < ne) G::gather_edge(p, er[i], ge[i]);
 
-    // while they fly: the next chunk's records, the coordinates after that, this chunk's row bounds
+    // while they fly: the next chunk's records, the boundary after that, this chunk's row ends
     typename G::EReg er_next[IPT];
-    cw = cw_next;
-    if (k + 1 < count) {
-      const long long ny0 = __shfl_sync(0xffffffffu, cw, 1), ny1 = __shfl_sync(0xffffffffu, cw, 3);
-      load_edges(ny0, (int)(ny1 - ny0), er_next);
-    }
-    cw_next = (k + 2 < count) ? load_coords(c_begin + k + 2) : 0;
+    if (k + 1 < count) load_edges(y1, (int)(y2 - y1), er_next);
+    OffsetT x3 = 0, y3 = 0;
+    if (k + 3 <= count) load_pair(c_begin + k + 3, x3, y3);
 
-    // markers cleared; bounds of the first 32 rows that end inside the chunk requested before the gathers are waited for
+    // end of row x0 + lane relative to the chunk's first edge (rows past the chunk: unused)
+    const OffsetT* ro0 = ro + x0 + 1;
+    int rel_end = 0;
+    if (lane < nr) rel_end = (int)(ro0[lane] - y0);
     {
       uint32_t* mk32 = reinterpret_cast<uint32_t*>(mk);
 #pragma unroll
       for (int w4 = lane; w4 < CH / 4; w4 += 32) mk32[w4] = 0xffffffffu;
     }
-    auto row_bounds = [&](int r, long long& beg, long long& end) {
-      if (r < nr) {
-        end = (long long)ro[x0 + r + 1];
-        beg = r ? (long long)ro[x0 + r] : y0;          // row x0 may have begun in an earlier chunk
-        if (beg < y0) beg = y0;
-      } else {
-        beg = end = y0;
-      }
-    };
-    long long beg = y0, end = y0;
-    row_bounds(lane, beg, end);
     __syncwarp();
 
     // rows that end inside the chunk, one lane per row: the last edge of a row is marked with the row's number;
     // a row without edges in this chunk is finished here (row x0 then takes the whole carry)
-    bool seed_used = false;
+    const bool seed_used = nr > 0 && __shfl_sync(0xffffffffu, rel_end, 0) == 0;
+    int before = 0;                                      // where the row before this batch's first row ended
     for (int r0 = 0; r0 < nr; r0 += 32) {
       const int r = r0 + lane;
-      const bool have = r < nr;
-      const int len = (int)(end - beg), last = (int)(end - y0) - 1;
-      if (r0 + 32 < nr) row_bounds(r + 32, beg, end);
-      if (have) {
-        if (len > 0) {
-          mk[last] = (unsigned char)r;
+      if (r0) {
+        rel_end = 0;
+        if (r < nr) rel_end = (int)(ro0[r] - y0);
+      }
+      int prev = __shfl_up_sync(0xffffffffu, rel_end, 1);
+      if (lane == 0) prev = before;
+      before = __shfl_sync(0xffffffffu, rel_end, 31);
+      if (r < nr) {
+        if (rel_end > prev) {
+          mk[rel_end - 1] = (unsigned char)r;
         } else {
           static_for<G::kNumReducers>([&](auto R) {
             constexpr int d = G::template red_dim<R.value>();
             constexpr int o = G::template red_off<R.value>();
-            V* dst = G::template red_out<R.value>(p) + (size_t)(x0 + r) * d;
+            V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + r) * d;
 #pragma unroll
             for (int j = 0; j < d; ++j) dst[j] = (r == 0) ? carry[o + j] : V(0);
           });
         }
       }
-      if (r0 == 0) seed_used = __shfl_sync(0xffffffffu, (int)(have && len == 0), 0) != 0;
     }
     if (seed_used) {
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
     }
 
-    // products into this warp's slots (lanes on consecutive edges)
+    // products into this warp's slots (lanes on consecutive edges; slots past the chunk's edges hold zero)
     typename G::GRow gr;
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
-      if (i * 32 + lane < ne) {
-        V prod[kAcc];
+      V prod[kAcc];
 #pragma unroll
-        for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
-        G::map(p, er[i], y0 + (i * 32 + lane), gr, ge[i], prod);
+      for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
+      if (i * 32 + lane < ne) G::map(p, er[i], (long long)y0 + (i * 32 + lane), gr, ge[i], prod);
 #pragma unroll
-        for (int j = 0; j < kAcc; ++j) sp[j * CH + i * 32 + lane] = prod[j];
-      }
+      for (int j = 0; j < kAcc; ++j) sp[j * CH + i * 32 + lane] = prod[j];
     }
     __syncwarp();
 
@@ -210,44 +207,40 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     int first_row = -1;
     {
       V pv[IPT][kAcc];
-      unsigned char pm[IPT];
+      int pm[IPT];
 #pragma unroll
       for (int i = 0; i < IPT; ++i) {
-        const int e = lane * IPT + i;
-        pm[i] = 0xff;
-        if (e < ne) {
-          pm[i] = mk[e];
+        pm[i] = mk[lane * IPT + i];
 #pragma unroll
-          for (int j = 0; j < kAcc; ++j) pv[i][j] = sp[j * CH + e];
-        }
+        for (int j = 0; j < kAcc; ++j) pv[i][j] = sp[j * CH + lane * IPT + i];
       }
 #pragma unroll
       for (int i = 0; i < IPT; ++i) {
-        if (lane * IPT + i < ne) {
 #pragma unroll
-          for (int j = 0; j < kAcc; ++j) run[j] += pv[i][j];
-          if (pm[i] != 0xff) {
-            if (first_row < 0) {                       // may have begun in earlier lanes: finished after the scan
-              first_row = pm[i];
+        for (int j = 0; j < kAcc; ++j) run[j] += pv[i][j];
+        if (pm[i] != 0xff) {
+          if (first_row < 0) {                         // may have begun in earlier lanes: finished after the scan
+            first_row = pm[i];
 #pragma unroll
-              for (int j = 0; j < kAcc; ++j) first[j] = run[j];
-            } else {
-              static_for<G::kNumReducers>([&](auto R) {
-                constexpr int d = G::template red_dim<R.value>();
-                constexpr int o = G::template red_off<R.value>();
-                V* dst = G::template red_out<R.value>(p) + (size_t)(x0 + pm[i]) * d;
+            for (int j = 0; j < kAcc; ++j) first[j] = run[j];
+          } else {
+            static_for<G::kNumReducers>([&](auto R) {
+              constexpr int d = G::template red_dim<R.value>();
+              constexpr int o = G::template red_off<R.value>();
+              V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + pm[i]) * d;
 #pragma unroll
-                for (int j = 0; j < d; ++j) dst[j] = run[o + j];
-              });
-            }
-#pragma unroll
-            for (int j = 0; j < kAcc; ++j) run[j] = V(0);
+              for (int j = 0; j < d; ++j) dst[j] = run[o + j];
+            });
           }
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) run[j] = V(0);
         }
       }
     }
-    // segmented inclusive scan of the open partial sums: a lane that closed a row passes on only what follows it
-    int flag = first_row >= 0 ? 1 : 0;
+    // segmented inclusive scan of the open partial sums: a lane that closed a row passes on only what follows it.
+    // Bit 0 of `flag`: a row was closed at or before this lane; bit 1 is set in lane 0 so that lanes nearer than the
+    // shuffle distance (whose shuffle returns their own value) are complete -- and blocked -- by the time it matters.
+    int flag = (first_row >= 0 ? 1 : 0) | (lane == 0 ? 2 : 0);
     V scan[kAcc];
 #pragma unroll
     for (int j = 0; j < kAcc; ++j) scan[j] = run[j];
@@ -257,12 +250,12 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) {
         const V v_up = shfl_up_any(scan[j], d);
-        if (lane >= d && !flag) scan[j] = v_up + scan[j];
+        if (!flag) scan[j] = v_up + scan[j];
       }
-      if (lane >= d) flag |= f_up;
+      flag |= f_up;
     }
     // what the lanes before this one left open (plus the warp's carry when none of them closed a row)
-    int f_ex = __shfl_up_sync(0xffffffffu, flag, 1);
+    int f_ex = __shfl_up_sync(0xffffffffu, flag, 1) & 1;
     if (lane == 0) f_ex = 0;
     V in[kAcc];
 #pragma unroll
@@ -275,14 +268,14 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
       static_for<G::kNumReducers>([&](auto R) {
         constexpr int d = G::template red_dim<R.value>();
         constexpr int o = G::template red_off<R.value>();
-        V* dst = G::template red_out<R.value>(p) + (size_t)(x0 + first_row) * d;
+        V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + first_row) * d;
 #pragma unroll
         for (int j = 0; j < d; ++j) dst[j] = in[o + j] + first[o + j];
       });
     }
     // the warp's new carry: what is still open behind the last lane
     {
-      const int f31 = __shfl_sync(0xffffffffu, flag, 31);
+      const int f31 = __shfl_sync(0xffffffffu, flag, 31) & 1;
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) {
         const V v31 = __shfl_sync(0xffffffffu, scan[j], 31);
@@ -293,6 +286,7 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     __syncwarp();                                      // the slots are rewritten by the next chunk
 #pragma unroll
     for (int i = 0; i < IPT; ++i) er[i] = er_next[i];
+    x0 = x1; y0 = y1; x1 = x2; y1 = y2; x2 = x3; y2 = y3;
   }
 
   // ---- hand the warp's carry to the last CTA -----------------------------------------------------------
