@@ -217,8 +217,8 @@ struct GraphApi {
                          const WorkspaceHeader& h, cudaStream_t st) {
     if constexpr (G::kHasReducer && kLeanBuilt) {
       auto kernel = flex_warp_kernel<G, OffsetT, CfgLean>;
-      // per warp: one product slot and one marker byte per item of a chunk (the layout of flex_warp_kernel)
-      constexpr int kSmem = CfgLean::kWarps * int(align_up(uint64_t(G::kAccDim) * CfgLean::kChunk * sizeof(V) + CfgLean::kChunk, 16));
+      // per warp: the product slots and marker words of one chunk (WarpSmem, the layout of flex_warp_kernel)
+      constexpr int kSmem = CfgLean::kWarps * WarpSmem<G, CfgLean>::kBytes;
       constexpr int kMaxDevices = 64;
       static std::mutex mu;
       static int resident_of[kMaxDevices] = {};      // 0: not initialised yet

@@ -36,6 +36,12 @@ struct WarpCfg {
   static constexpr int kChunk = 32 * IPT_;        // merge items per warp chunk ("tile" of the plan)
 };
 
+// Shared memory of one warp: a product slot per item and accumulator component, then 8 marker bytes per lane.
+template <class G, class Cfg>
+struct WarpSmem {
+  static constexpr int kBytes = int(align_up(uint64_t(G::kAccDim) * Cfg::kChunk * sizeof(typename G::V) + 256, 16));
+};
+
 constexpr int kMaxWarpCarries = 16384;            // capacity of the per-warp carry arrays in the workspace
 
 // Streaming accessor for the per-edge arrays: plain global pointers read with evict-first loads, so that the
@@ -78,10 +84,12 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   static_assert(CH <= 255, "row numbers inside a chunk are kept in marker bytes");
-  constexpr int kWarpBytes = int(align_up(uint64_t(kAcc) * CH * sizeof(V) + CH, 16));
+  static_assert(IPT <= 8, "a lane's markers are read as one 8-byte word");
+  constexpr int kWarpBytes = WarpSmem<G, Cfg>::kBytes;
   unsigned char* wbase = smem_w + (size_t)warp * kWarpBytes;
   V* sp = reinterpret_cast<V*>(wbase);                                   // this warp's product slots, [kAcc][CH]
-  unsigned char* mk = wbase + (size_t)kAcc * CH * sizeof(V);            // per item: the row (inside the chunk) whose last edge it is, or 0xff
+  // per item: the row (inside the chunk) whose last edge it is, or 0xff; the IPT items of a lane sit in one 8-byte word
+  unsigned char* mk = wbase + (size_t)kAcc * CH * sizeof(V);
   const OffsetT* ro = static_cast<const OffsetT*>(a.row_offsets);
   const OffsetT* coords = static_cast<const OffsetT*>(a.coords);
 
@@ -148,29 +156,26 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     const OffsetT* ro0 = ro + x0 + 1;
     int rel_end = 0;
     if (lane < nr) rel_end = (int)(ro0[lane] - y0);
-    {
-      uint32_t* mk32 = reinterpret_cast<uint32_t*>(mk);
-#pragma unroll
-      for (int w4 = lane; w4 < CH / 4; w4 += 32) mk32[w4] = 0xffffffffu;
-    }
+    reinterpret_cast<uint2*>(mk)[lane] = make_uint2(0xffffffffu, 0xffffffffu);
     __syncwarp();
 
     // rows that end inside the chunk, one lane per row: the last edge of a row is marked with the row's number;
     // a row without edges in this chunk is finished here (row x0 then takes the whole carry)
-    const bool seed_used = nr > 0 && __shfl_sync(0xffffffffu, rel_end, 0) == 0;
+    const bool seed_used = __any_sync(0xffffffffu, lane == 0 && nr > 0 && rel_end == 0);
     int before = 0;                                      // where the row before this batch's first row ended
     for (int r0 = 0; r0 < nr; r0 += 32) {
       const int r = r0 + lane;
       if (r0) {
+        before = __shfl_sync(0xffffffffu, rel_end, 31);
         rel_end = 0;
         if (r < nr) rel_end = (int)(ro0[r] - y0);
       }
       int prev = __shfl_up_sync(0xffffffffu, rel_end, 1);
       if (lane == 0) prev = before;
-      before = __shfl_sync(0xffffffffu, rel_end, 31);
       if (r < nr) {
         if (rel_end > prev) {
-          mk[rel_end - 1] = (unsigned char)r;
+          const int q = rel_end - 1, owner = q / IPT;
+          mk[owner * 8 + (q - owner * IPT)] = (unsigned char)r;
         } else {
           static_for<G::kNumReducers>([&](auto R) {
             constexpr int d = G::template red_dim<R.value>();
@@ -208,9 +213,10 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     {
       V pv[IPT][kAcc];
       int pm[IPT];
+      const uint2 mw = reinterpret_cast<const uint2*>(mk)[lane];
 #pragma unroll
       for (int i = 0; i < IPT; ++i) {
-        pm[i] = mk[lane * IPT + i];
+        pm[i] = (int)(((i < 4 ? mw.x : mw.y) >> (8 * (i & 3))) & 0xffu);
 #pragma unroll
         for (int j = 0; j < kAcc; ++j) pv[i][j] = sp[j * CH + lane * IPT + i];
       }
@@ -238,25 +244,24 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
       }
     }
     // segmented inclusive scan of the open partial sums: a lane that closed a row passes on only what follows it.
-    // Bit 0 of `flag`: a row was closed at or before this lane; bit 1 is set in lane 0 so that lanes nearer than the
-    // shuffle distance (whose shuffle returns their own value) are complete -- and blocked -- by the time it matters.
-    int flag = (first_row >= 0 ? 1 : 0) | (lane == 0 ? 2 : 0);
+    // Which lanes closed a row is one ballot; a lane takes a value from `d` lanes down only while that lane is not
+    // before the nearest closing lane at or below it (lane 0 when there is none).
+    const unsigned closed = __ballot_sync(0xffffffffu, first_row >= 0);
+    const unsigned closed_le = closed & (0xffffffffu >> (31 - lane));
+    const int reach = lane - (closed_le ? 31 - __clz(closed_le) : 0);      // lanes below this one in its segment
     V scan[kAcc];
 #pragma unroll
     for (int j = 0; j < kAcc; ++j) scan[j] = run[j];
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const int f_up = __shfl_up_sync(0xffffffffu, flag, d);
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) {
         const V v_up = shfl_up_any(scan[j], d);
-        if (!flag) scan[j] = v_up + scan[j];
+        if (reach >= d) scan[j] = v_up + scan[j];
       }
-      flag |= f_up;
     }
     // what the lanes before this one left open (plus the warp's carry when none of them closed a row)
-    int f_ex = __shfl_up_sync(0xffffffffu, flag, 1) & 1;
-    if (lane == 0) f_ex = 0;
+    const bool f_ex = (closed_le & ~(1u << lane)) != 0;
     V in[kAcc];
 #pragma unroll
     for (int j = 0; j < kAcc; ++j) {
@@ -275,7 +280,7 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     }
     // the warp's new carry: what is still open behind the last lane
     {
-      const int f31 = __shfl_sync(0xffffffffu, flag, 31) & 1;
+      const bool f31 = closed != 0;
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) {
         const V v31 = __shfl_sync(0xffffffffu, scan[j], 31);
