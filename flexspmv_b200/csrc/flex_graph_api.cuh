@@ -218,7 +218,7 @@ struct GraphApi {
     if constexpr (G::kHasReducer && kLeanBuilt) {
       auto kernel = flex_warp_kernel<G, OffsetT, CfgLean>;
       // per warp: the product slots and marker words of one chunk (WarpSmem, the layout of flex_warp_kernel)
-      constexpr int kSmem = CfgLean::kWarps * WarpSmem<G, CfgLean>::kBytes;
+      constexpr int kSmem = WarpSmem<G, CfgLean>::template cta_bytes<OffsetT>();
       constexpr int kMaxDevices = 64;
       static std::mutex mu;
       static int resident_of[kMaxDevices] = {};      // 0: not initialised yet

@@ -3,19 +3,23 @@
 // On such matrices every gathered record costs its own L1 miss, and what bounds the kernel is how many
 // misses an SM can have in flight: its L1 tag stage accepts one cache line per clock, and every miss
 // in flight holds one line of the L1 / shared-memory array.  Measured on B200 (4-byte gathers from a 64 MB
-// vector): 265 G gathers/s per GPU with at most 32 KB of shared memory per SM, 225 at 132 KB, 183 at 164 KB,
-// 130 at 196 KB, 63 at 228 KB.  So this kernel keeps shared memory small and the miss queue full:
+// vector): 235 - 265 G gathers/s per GPU with at most 32 KB of shared memory per SM, 213 - 225 at 64 - 164 KB,
+// 177 - 183 at 196 KB, 130 at 224 KB.  So this kernel keeps shared memory small and the miss queue full:
 //   * no staging: every warp works alone on merge-path chunks of 32 x IPT items (coordinates planned per
 //     chunk), reads its index / value records with coalesced streaming loads straight into registers --
 //     one chunk ahead of the chunk whose gathers are in flight -- and gathers from registers;
-//   * the only shared memory is one product slot and one marker byte per item (the strided -> blocked
+//   * the only shared memory per item is one product slot and one marker byte (the strided -> blocked
 //     transposition): lanes take consecutive edges for loads and gathers; then every lane takes IPT
 //     consecutive items, sums them left to right and closes the rows whose last edge is marked inside its
 //     span, and a warp-shuffle segmented scan of the lanes' open partial sums supplies what a row received
 //     from the lanes before (every lane is busy whatever the row lengths are);
-//   * a warp owns a contiguous run of chunks, so the carry of a row that spans chunks stays in a register;
-//     one carry per warp reaches global memory and the last CTA to finish folds them, in order.
-// No barriers between warps, no atomics on the output, run-to-run deterministic.
+//   * a CTA owns a contiguous range of chunks and hands it to its warps in runs of consecutive chunks, long runs
+//     first and short ones at the end (each 1/32 of what is left), so the warps finish together although their
+//     speeds differ; inside a run the carry of a row that spans chunks stays in a register.  One carry per run
+//     goes to shared memory and the CTA folds them itself; one carry per CTA reaches global memory and the last
+//     CTA to finish folds those, in order.
+// No barriers between warps while they work, no atomics on the output, run-to-run deterministic (the sequence of
+// runs depends on the range only, not on which warp takes which).
 //
 // Replaces, for those matrices, the same reference code as flex_tile_kernel.cuh (SpmvKernel +
 // AgentFlexSpmv::ConsumeTile / reduce<>, include/merged_spmv_kernels.cuh:110-128,
@@ -40,6 +44,12 @@ struct WarpCfg {
 template <class G, class Cfg>
 struct WarpSmem {
   static constexpr int kBytes = int(align_up(uint64_t(G::kAccDim) * Cfg::kChunk * sizeof(typename G::V) + 256, 16));
+  static constexpr int kMaxRuns = 224;      // runs a CTA hands out to its warps (one carry each, folded by the CTA)
+  // dynamic shared memory of a CTA: the warps' areas, then a row and kAccDim partial sums per run
+  template <typename OffsetT>
+  static constexpr int cta_bytes() {
+    return Cfg::kWarps * kBytes + kMaxRuns * int(sizeof(OffsetT) + G::kAccDim * sizeof(typename G::V));
+  }
 };
 
 constexpr int kMaxWarpCarries = 16384;            // capacity of the per-warp carry arrays in the workspace
@@ -65,8 +75,8 @@ struct WarpKernelArgs {
   const void* row_offsets;  // leading 0 included
   const void* coords;       // (num_chunks + 1) pairs of OffsetT
   WorkspaceHeader* header;
-  long long* carry_row;     // [kMaxWarpCarries]
-  void* carry_val;          // [kMaxWarpCarries][kAcc] of V
+  long long* carry_row;     // one per CTA (capacity kMaxWarpCarries): the row its range left open
+  void* carry_val;          // [..][kAcc] of V: the partial sums of that row
   long long num_rows;
   long long num_edges;
   long long num_chunks;
@@ -82,6 +92,8 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
 
   extern __shared__ __align__(16) unsigned char smem_w[];
   __shared__ int s_last;
+  __shared__ unsigned long long s_next;
+  constexpr int kMaxRuns = WarpSmem<G, Cfg>::kMaxRuns;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   static_assert(CH <= 255, "row numbers inside a chunk are kept in marker bytes");
   static_assert(IPT <= 8, "a lane's markers are read as one 8-byte word");
@@ -99,18 +111,49 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     return;
   }
 
-  // contiguous run of chunks of this warp
-  const long long n_warps = (long long)gridDim.x * Cfg::kWarps;
-  const long long g = (long long)blockIdx.x * Cfg::kWarps + warp;
-  const long long q = a.num_chunks / n_warps, rem = a.num_chunks % n_warps;
-  const long long c_begin = g * q + (g < rem ? g : rem);
-  const int count = (int)(q + (g < rem ? 1 : 0));
+  // The CTA owns a contiguous range of chunks.  Its warps take runs of consecutive chunks from it one after the other
+  // (s_next: next free chunk of the range in the low half, runs handed out so far in the high half).  A run is
+  // 1/kWarps of what is left, at least min_run chunks: long runs first, short ones at the end, so that the warps of
+  // the CTA finish together whatever their speeds were.  The sequence of runs depends only on the range, not on
+  // which warp takes which, so results stay the same from launch to launch.
+  const long long q = a.num_chunks / gridDim.x, rem = a.num_chunks % gridDim.x;
+  const long long cta_begin = (long long)blockIdx.x * q + (blockIdx.x < rem ? blockIdx.x : rem);
+  const unsigned cta_chunks = (unsigned)(q + (blockIdx.x < rem ? 1 : 0));
+  OffsetT* s_run_row = reinterpret_cast<OffsetT*>(smem_w + (size_t)Cfg::kWarps * kWarpBytes);   // [kMaxRuns] row a run left open
+  V* s_run_val = reinterpret_cast<V*>(s_run_row + kMaxRuns);                                     // [kMaxRuns][kAcc] its partial sums
+  const unsigned min_run = cta_chunks >= 16u * Cfg::kWarps ? 4u : 1u;     // a run pays for one pipeline start
+  if (tid == 0) s_next = 0ull;
+  __syncthreads();
 
   StreamTile<G> tile{&p};
+  for (;;) {
+  unsigned run_pos = 0, run_len = 0, run_id = 0;
+  if (lane == 0) {
+    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(&s_next);
+    for (;;) {
+      const unsigned pos = (unsigned)seen, id = (unsigned)(seen >> 32);
+      if (pos >= cta_chunks) break;
+      const unsigned left = cta_chunks - pos;
+      unsigned len = left / Cfg::kWarps;
+      if (len < min_run) len = min_run;
+      if (len > left || id == (unsigned)kMaxRuns - 1) len = left;
+      const unsigned long long want = ((unsigned long long)(id + 1) << 32) | (pos + len);
+      const unsigned long long got = atomicCAS(&s_next, seen, want);
+      if (got == seen) { run_pos = pos; run_len = len; run_id = id; break; }
+      seen = got;
+    }
+  }
+  run_pos = __shfl_sync(0xffffffffu, run_pos, 0);
+  run_len = __shfl_sync(0xffffffffu, run_len, 0);
+  run_id = __shfl_sync(0xffffffffu, run_id, 0);
+  if (run_len == 0) break;
+  const long long c_begin = cta_begin + run_pos;
+  const int count = (int)run_len;
+
   V carry[kAcc];
 #pragma unroll
   for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
-  long long end_row = a.num_rows;      // row the final carry belongs to (num_rows: none)
+  long long end_row = a.num_rows;      // row the run's carry belongs to
 
   // A chunk boundary is a (row, edge) pair; every lane reads the same pair (one broadcast transaction, no shuffles).
   auto load_pair = [&](long long c, OffsetT& x, OffsetT& y) {
@@ -294,12 +337,46 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     x0 = x1; y0 = y1; x1 = x2; y1 = y2; x2 = x3; y2 = y3;
   }
 
-  // ---- hand the warp's carry to the last CTA -----------------------------------------------------------
+  // the run's carry: the row it left open and the partial sums of that row
   if (lane == 0) {
-    V* cv = static_cast<V*>(a.carry_val) + (size_t)g * kAcc;
+    s_run_row[run_id] = (OffsetT)end_row;
 #pragma unroll
-    for (int j = 0; j < kAcc; ++j) cv[j] = carry[j];
-    a.carry_row[g] = count ? end_row : a.num_rows;
+    for (int j = 0; j < kAcc; ++j) s_run_val[run_id * kAcc + j] = carry[j];
+  }
+  }  // runs of this warp
+
+  // ---- the CTA folds the carries of its runs; what its last run left open goes to the last CTA -------------------
+  __syncthreads();
+  {
+    const int n_runs = (int)(s_next >> 32);
+    const long long tail_row = n_runs ? (long long)s_run_row[n_runs - 1] : a.num_rows;
+    for (int c = tid; c < n_runs; c += Cfg::kBlock) {
+      const long long row = (long long)s_run_row[c];
+      if (c > 0 && (long long)s_run_row[c - 1] == row) continue;     // not the first carry of its row
+      V sum[kAcc];
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) sum[i] = s_run_val[c * kAcc + i];
+      for (int c2 = c + 1; c2 < n_runs && (long long)s_run_row[c2] == row; ++c2) {
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) sum[i] += s_run_val[c2 * kAcc + i];
+      }
+      if (row == tail_row) {
+        // still open at the end of the range (or no row at all): another CTA may finish it, so it waits for all of them
+        V* cv = static_cast<V*>(a.carry_val) + (size_t)blockIdx.x * kAcc;
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) cv[i] = sum[i];
+      } else {
+        // finished by a later run of this CTA: every store to it is behind the barrier above
+        static_for<G::kNumReducers>([&](auto R) {
+          constexpr int d = G::template red_dim<R.value>();
+          constexpr int o = G::template red_off<R.value>();
+          V* dst = G::template red_out<R.value>(p) + (size_t)row * d;
+#pragma unroll
+          for (int i = 0; i < d; ++i) dst[i] = dst[i] + sum[o + i];
+        });
+      }
+    }
+    if (tid == 0) a.carry_row[blockIdx.x] = tail_row;
   }
   __threadfence();
   __syncthreads();
@@ -310,7 +387,7 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
   __syncthreads();
   if (s_last) {
     __threadfence();
-    const int n_carry = (int)n_warps;
+    const int n_carry = (int)gridDim.x;
     const V* cvals = static_cast<const V*>(a.carry_val);
     for (int c = tid; c < n_carry; c += Cfg::kBlock) {
       const long long row = __ldcg(a.carry_row + c);
