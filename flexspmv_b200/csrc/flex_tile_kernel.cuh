@@ -560,6 +560,25 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 #pragma unroll
       for (int j = 0; j < kAcc; ++j) sum[j] = (r == 0) ? s_carry[kpar * kAcc + j] : V(0);
       const V* q = sprod + lo;
+      // rows of up to kUnroll edges (the common case) without a loop: every load is issued before the first add,
+      // and threads whose rows differ in length do not diverge
+      constexpr int kUnroll = (kAcc * sizeof(V) <= 8) ? 8 : ((kAcc * sizeof(V) <= 16) ? 4 : 2);
+      if (n <= kUnroll) {
+        V v[kUnroll][kAcc];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) v[u][j] = (u < n) ? q[j * Cfg::kTile + u] : V(0);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          if (u < n) {
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) sum[j] += v[u][j];
+          }
+        }
+        n = 0;
+      }
       for (; n >= 4; n -= 4, q += 4) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
