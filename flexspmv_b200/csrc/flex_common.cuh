@@ -42,7 +42,8 @@ struct WorkspaceHeader {
   uint64_t win_table_offset;   // gather windows (0: not planned): per-tile segment table ...
   uint64_t win_index_offset;   // ... and per-edge 16-bit positions inside the tile's window area
   int32_t win_ready;           // 1 once the window plan has filled them
-  int32_t reserved0;
+  int32_t snapped_grid;        // > 0: the tile boundaries in front of the CTAs of a grid of this size sit on row
+                               // ends (no row spans two CTAs of such a launch: no carries to hand over)
   uint64_t status_mirror;      // device alias of a pinned host int32 that receives a copy of `status` when a
                                // kernel raises an error (0: none); lets the host notice without a sync or a copy
   char pad[256 - 4 * 4 - 3 * 8 - 2 * 4 - 4 * 8 - 8 * 4 - 2 * 8 - 2 * 4 - 8];

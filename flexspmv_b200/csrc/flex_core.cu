@@ -33,6 +33,50 @@ __global__ void partition_kernel(const OffsetT* __restrict__ row_offsets, long l
   coords[2 * t + 1] = y;
 }
 
+// One CTA.  A launch of `grid` CTAs gives CTA c the tiles [c q + min(c, r), ...), q = tiles / grid, r = tiles % grid.
+// The boundary in front of each such run usually cuts a row in two, which costs the launch a carry hand-over
+// between CTAs (fence, ticket, fix-up by the last CTA).  When the part of the cut row in front of the boundary fits
+// into the tile behind it -- which has room for as many extra edges as it holds row ends -- the boundary is moved
+// back to the row's first edge instead.  All boundaries or none: the header records the grid size it was done for.
+template <typename OffsetT>
+__global__ void snap_cta_boundaries_kernel(const OffsetT* __restrict__ row_offsets, long long num_rows, long long num_tiles,
+                                           int grid, OffsetT* __restrict__ coords, WorkspaceHeader* h) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  const long long q = num_tiles / grid, r = num_tiles % grid;
+  for (int c = 1 + threadIdx.x; c < grid; c += blockDim.x) {
+    const long long t = c * q + (c < r ? c : r);
+    const long long x = (long long)coords[2 * t], y = (long long)coords[2 * t + 1];
+    if (x >= num_rows) continue;                                    // behind the last row end: nothing is cut
+    const long long begin = (long long)row_offsets[x];              // first edge of the row the boundary cuts
+    const long long rows_behind = (long long)coords[2 * t + 2] - x; // row ends in the tile behind the boundary
+    const long long y_before = (long long)coords[2 * t - 1];        // where the tile in front of it starts
+    if (y - begin > rows_behind || begin < y_before) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  for (int c = 1 + threadIdx.x; c < grid; c += blockDim.x) {
+    const long long t = c * q + (c < r ? c : r);
+    const long long x = (long long)coords[2 * t];
+    if (x < num_rows) coords[2 * t + 1] = row_offsets[x];
+  }
+  if (threadIdx.x == 0) h->snapped_grid = grid;
+}
+
+int snap_cta_boundaries_launch(const void* d_row_offsets, int offset_bits, long long num_rows, long long num_tiles, int grid,
+                               void* d_coords, void* ws, cudaStream_t stream) {
+  if (grid < 2 || num_tiles < grid) return 0;
+  if (offset_bits == 32)
+    snap_cta_boundaries_kernel<int><<<1, 256, 0, stream>>>(static_cast<const int*>(d_row_offsets), num_rows, num_tiles, grid,
+                                                           static_cast<int*>(d_coords), static_cast<WorkspaceHeader*>(ws));
+  else
+    snap_cta_boundaries_kernel<long long><<<1, 256, 0, stream>>>(static_cast<const long long*>(d_row_offsets), num_rows,
+                                                                 num_tiles, grid, static_cast<long long*>(d_coords),
+                                                                 static_cast<WorkspaceHeader*>(ws));
+  return (int)cudaGetLastError();
+}
+
 int partition_launch(const void* d_row_offsets, int offset_bits, long long num_rows, long long num_edges,
                      int tile_items, void* d_coords, cudaStream_t stream) {
   if (!d_row_offsets || !d_coords || tile_items <= 0 || num_rows < 0 || num_edges < 0) return FLEXSPMV_ERR_BAD_ARG;

@@ -21,6 +21,8 @@ int partition_launch(const void* d_row_offsets, int offset_bits, long long num_r
                      int tile_items, void* d_coords, cudaStream_t stream);
 int device_sm_count();
 int header_init_launch(void* ws, const WorkspaceHeader& h, cudaStream_t stream);
+int snap_cta_boundaries_launch(const void* d_row_offsets, int offset_bits, long long num_rows, long long num_tiles, int grid,
+                               void* d_coords, void* ws, cudaStream_t stream);
 int window_plan_launch(const void* d_coords, int offset_bits, long long num_tiles, const int* d_idx, int rec_bytes,
                        int win_bytes, void* d_table, void* d_local_idx, cudaStream_t st);
 int window_ready_launch(void* ws, cudaStream_t st);
@@ -149,9 +151,53 @@ struct GraphApi {
     if (G::kHasReducer) {
       if (!row_offsets) return FLEXSPMV_ERR_BAD_ARG;
       if (!aligned16(row_offsets)) return FLEXSPMV_ERR_ALIGN;
-      return partition_launch(row_offsets, d->offset_bits, d->num_rows, d->num_edges, tile_items(d),
-                              static_cast<char*>(ws) + h.coords_offset, st);
+      if (int e = partition_launch(row_offsets, d->offset_bits, d->num_rows, d->num_edges, tile_items(d),
+                                   static_cast<char*>(ws) + h.coords_offset, st)) return e;
+      // the tile kernel: boundaries between the CTAs of its grid moved onto row ends where the tiles have room
+      if (!use_lean(d) && h.num_tiles > 1) {
+        int resident = 0;
+        int e = 0;
+        bool win = false;
+        if constexpr (G::kWindowGather && kWindowsBuilt) win = use_win(d);
+        if constexpr (G::kWindowGather && kWindowsBuilt) {
+          if (win) e = d->offset_bits == 64 ? resident_ctas<long long, CfgWin, true>(&resident) : resident_ctas<int, CfgWin, true>(&resident);
+        }
+        if (!win) e = d->offset_bits == 64 ? resident_ctas<long long>(&resident) : resident_ctas<int>(&resident);
+        if (e) return e;
+        long long grid = max_ctas(d, resident);
+        if (grid > h.num_tiles) grid = h.num_tiles;
+        return snap_cta_boundaries_launch(row_offsets, d->offset_bits, d->num_rows, h.num_tiles, (int)grid,
+                                          static_cast<char*>(ws) + h.coords_offset, ws, st);
+      }
+      return 0;
     }
+    return 0;
+  }
+
+  // CTAs of the tile kernel that one SM holds.  The shared-memory opt-in and the occupancy are per device: looked up
+  // once for each device of the process.
+  template <typename OffsetT, class C = Cfg, bool WIN = false>
+  static int resident_ctas(int* out) {
+    using L = TileSmemLayout<G, OffsetT, C, WIN>;
+    static_assert(L::kTotal <= 227 * 1024, "tile kernel needs more shared memory than one sm_100a CTA can have");
+    auto kernel = flex_tile_kernel<G, OffsetT, C, WIN>;
+    constexpr int kThreads = C::kBlock + (G::kDirectLoads ? 0 : 32);
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int resident_of[kMaxDevices] = {};      // 0: not initialised yet
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return FLEXSPMV_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lock(mu);
+    if (resident_of[dev] == 0) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+      int r = 0;
+      if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, kernel, kThreads, L::kTotal);
+      if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
+      resident_of[dev] = r < 1 ? -1 : r;
+    }
+    if (resident_of[dev] < 1) return FLEXSPMV_ERR_TOO_LARGE;
+    *out = resident_of[dev];
     return 0;
   }
 
@@ -159,29 +205,10 @@ struct GraphApi {
   static int launch_tiles(const flexspmv_desc* d, const typename G::Params& p, const void* row_offsets, void* ws,
                           const WorkspaceHeader& h, cudaStream_t st) {
     using L = TileSmemLayout<G, OffsetT, C, WIN>;
-    static_assert(L::kTotal <= 227 * 1024, "tile kernel needs more shared memory than one sm_100a CTA can have");
     auto kernel = flex_tile_kernel<G, OffsetT, C, WIN>;
     constexpr int kThreads = C::kBlock + (G::kDirectLoads ? 0 : 32);   // staged mode adds the producer warp
-    // the shared-memory opt-in and the occupancy are per device: looked up once for each device of the process
-    constexpr int kMaxDevices = 64;
-    static std::mutex mu;
-    static int resident_of[kMaxDevices] = {};      // 0: not initialised yet
-    int dev = 0;
-    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= kMaxDevices) return FLEXSPMV_ERR_BAD_ARG;
     int resident = 0;
-    {
-      std::lock_guard<std::mutex> lock(mu);
-      if (resident_of[dev] == 0) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-        int r = 0;
-        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, kernel, kThreads, L::kTotal);
-        if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
-        resident_of[dev] = r < 1 ? -1 : r;
-      }
-      resident = resident_of[dev];
-    }
-    if (resident < 1) return FLEXSPMV_ERR_TOO_LARGE;
+    if (int e = resident_ctas<OffsetT, C, WIN>(&resident)) return e;
     const long long tiles = h.num_tiles;
     if (tiles == 0) return 0;
     long long grid = max_ctas(d, resident);

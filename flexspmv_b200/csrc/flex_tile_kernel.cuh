@@ -316,6 +316,7 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   }
   if (tid < 2 * kAcc) s_carry[tid] = V(0);
   if (tid < 4) s_nlong[tid] = 0;
+  if (tid == 0) s_flag[1] = (a.header->snapped_grid == (int)gridDim.x) ? 1 : 0;   // no row spans two CTAs of this launch
   __syncthreads();   // the only barrier that includes the producer warp
 
   // ---- producer warp: runs up to S tiles ahead of the consumers, off their critical path -----------
@@ -865,6 +866,8 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   }
 
   // ---- hand the CTA's carry to the last CTA ---------------------------------------------------------
+  // (nothing to hand over when the plan put the boundaries between this launch's CTAs on row ends)
+  if (s_flag[1]) return;
   named_bar_sync(1, BLOCK);
   if (tid < kAcc) {
     V* cv = static_cast<V*>(a.carry_val) + (size_t)blockIdx.x * kAcc;

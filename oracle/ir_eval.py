@@ -95,6 +95,31 @@ def tile_coordinates(row_offsets: np.ndarray, tile_items: int) -> np.ndarray:
     return out
 
 
+def snap_cta_boundaries(coords: np.ndarray, row_offsets: np.ndarray, grid: int):
+    """Restatement of the plan step that moves the tile boundaries in front of the CTAs of a ``grid``-CTA launch
+    onto row ends (this package's own step, no reference counterpart).  CTA c starts at tile
+    ``c q + min(c, r)`` (q, r = divmod(tiles, grid)); a boundary (x, y) that cuts row x moves back to
+    ``(x, row_offsets[x])`` when the cut-off part fits the tile behind it (at most as many edges as that tile
+    holds row ends) and the row starts inside the tile in front.  All boundaries or none.
+    Returns (coords', snapped)."""
+    tiles = coords.shape[0] - 1
+    n = row_offsets.shape[0] - 1
+    if grid < 2 or tiles < grid:
+        return coords, False
+    q, r = divmod(tiles, grid)
+    out = coords.copy()
+    for c in range(1, grid):
+        t = c * q + min(c, r)
+        x, y = int(coords[t, 0]), int(coords[t, 1])
+        if x >= n:
+            continue
+        begin = int(row_offsets[x])
+        if y - begin > int(coords[t + 1, 0]) - x or begin < int(coords[t - 1, 1]):
+            return coords, False
+        out[t, 1] = begin
+    return out, True
+
+
 def gather_window_plan(coords: np.ndarray, idx: np.ndarray, rec_bytes: int, win_bytes: int,
                        max_segs: int = 12, max_buckets: int = 160):
     """Restatement of the gather-window plan (this package's own format, no reference counterpart): per tile

@@ -266,6 +266,14 @@ def test_gather_window_plan_bit_exact():
         tile_items = int(raw[:256].view(np.int32)[10])
         coords = ir_eval.tile_coordinates(ro, tile_items)
         tiles = coords.shape[0] - 1
+        # the plan moves the boundaries between the CTAs of its grid onto row ends where it can (int32 at byte 132: that
+        # grid, 0 when it could not): the coordinates in the workspace against the restatement of that step
+        snapped_grid = int(raw[:256].view(np.int32)[33])
+        if snapped_grid:
+            coords, ok = ir_eval.snap_cta_boundaries(coords, ro, snapped_grid)
+            assert ok
+        got_coords = raw[256:256 + coords.nbytes].view(coords.dtype).reshape(coords.shape)
+        assert np.array_equal(got_coords, coords)
         t_off, i_off = (int(v) for v in raw[112:128].view(np.int64))
         table = raw[t_off:t_off + tiles * 112].view(np.int32).reshape(tiles, 28)[:, :26]
         pos = raw[i_off:i_off + 2 * prob.nnz].view(np.uint16)

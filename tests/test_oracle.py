@@ -157,3 +157,28 @@ def test_tensor_semantics_corner_cases():
     assert np.array_equal(r, [[10.0, 200.0, 30.0, 400.0, 50.0, 600.0]])          # index-modulo broadcast
     evi = ir_eval.IREvaluator(graphs.mixed_dims_graph(), np.int64)
     assert np.array_equal(evi._binary("truediv", np.array([[-7, 7]]), np.array([[2, -2]])), [[-3, -3]])   # C++ truncation
+
+
+def test_snapped_cta_boundaries_keep_every_tile_within_its_capacity():
+    """The restatement of the plan step that moves the boundaries between CTAs onto row ends: afterwards every CTA
+    starts at the first edge of a row, no tile holds more edges than a tile has items, and boundaries stay ordered;
+    a matrix whose rows are longer than a tile is left alone."""
+    from flexspmv_b200 import problems
+    prob = problems.poisson2d(40)
+    ro = prob.row_offsets
+    tile = 256
+    coords = ir_eval.tile_coordinates(ro, tile)
+    tiles = coords.shape[0] - 1
+    for grid in (2, 7, tiles):
+        snapped, ok = ir_eval.snap_cta_boundaries(coords, ro, grid)
+        assert ok
+        q, r = divmod(tiles, grid)
+        for c in range(1, grid):
+            t = c * q + min(c, r)
+            assert snapped[t, 1] == ro[snapped[t, 0]]
+        assert np.all(np.diff(snapped[:, 1]) >= 0) and np.all(np.diff(snapped[:, 1]) <= tile)
+        assert np.array_equal(snapped[:, 0], coords[:, 0])
+    long_rows = np.array([0, 5000, 5001, 9000], dtype=np.int32)
+    c2 = ir_eval.tile_coordinates(long_rows, tile)
+    same, ok = ir_eval.snap_cta_boundaries(c2, long_rows, 4)
+    assert not ok and same is c2
