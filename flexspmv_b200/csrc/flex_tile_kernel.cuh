@@ -202,6 +202,21 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
   pdl_wait();
   pdl_launch_dependents();
 
+  // contiguous run of tiles of this CTA
+  const long long q = a.num_tiles / gridDim.x, rem = a.num_tiles % gridDim.x;
+  const long long t_begin = (long long)blockIdx.x * q + ((long long)blockIdx.x < rem ? blockIdx.x : rem);
+  const int count = (int)(q + ((long long)blockIdx.x < rem ? 1 : 0));
+
+  // The producer warp asks for its first coordinates together with the header (two round trips become one).  The
+  // words lie inside the workspace whether it was planned or not; nothing is done with them before the check below.
+  OffsetT first_coords[4] = {0, 0, 0, 0};
+  if constexpr (!DIRECT) {
+    if (warp == Cfg::kWarps && count) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) first_coords[i] = coords[2 * t_begin + i];
+    }
+  }
+
   // a workspace that was never planned for this problem holds no usable coordinates: every CTA
   // sees the same header, so all of them leave here and the ticket stays untouched
   if (a.header->magic != kMagic || a.header->num_tiles != a.num_tiles || a.header->num_rows != a.num_rows ||
@@ -212,11 +227,6 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
 
   const bool win_ready = WIN && a.header->win_ready == 1;   // until the window plan has run every tile gathers globally
   (void)win_ready;
-
-  // contiguous run of tiles of this CTA
-  const long long q = a.num_tiles / gridDim.x, rem = a.num_tiles % gridDim.x;
-  const long long t_begin = (long long)blockIdx.x * q + ((long long)blockIdx.x < rem ? blockIdx.x : rem);
-  const int count = (int)(q + ((long long)blockIdx.x < rem ? 1 : 0));
 
   // ---- producer ------------------------------------------------------------------------------------------
   // Table entry of a tile's gather windows, one piece per lane: the segment count in every lane, segment j in
@@ -325,8 +335,8 @@ flex_tile_kernel(const typename G::Params p, const TileKernelArgs a) {
       int issued = 0;
       bool pfail = false;
       // coordinates are read one tile ahead, so their load latency overlaps the wait for a free stage
-      long long c_row = count ? (long long)coords[2 * t_begin] : 0, c_nz = count ? (long long)coords[2 * t_begin + 1] : 0;
-      long long n_row = count ? (long long)coords[2 * t_begin + 2] : 0, n_nz = count ? (long long)coords[2 * t_begin + 3] : 0;
+      long long c_row = (long long)first_coords[0], c_nz = (long long)first_coords[1];
+      long long n_row = (long long)first_coords[2], n_nz = (long long)first_coords[3];
       WinEnt c_we = count ? load_win_entry(t_begin) : WinEnt{0, 0, 0};
       // testing aid (flexspmv_debug_withhold_stage): the stage of tile `withhold - 1` and of every later tile is
       // never filled, so that the consumers' bounded wait runs out and the error path can be exercised
