@@ -145,6 +145,9 @@ TUNED_CONFIGS = {
 # 8 x 128 24.3, 16 x 64 23.0 (the same 32 warps per SM every time; the driver sizes the shared-memory carve-out for the
 # largest number of CTAs the kernel could have resident, so few large CTAs leave the most L1); 6 / 7 items per lane 27.6 / 25.5.
 LEAN_CONFIG = (1024, 5, 1)
+# 8-byte values need more than the 64 registers a 1024-thread CTA leaves a thread (the kernel spills: 160 G gathers/s on
+# the power-law matrix in fp64); 768 threads (85 registers) reach 195, 512 threads 172, cuSPARSE 188.
+LEAN_CONFIG_WIDE = (768, 5, 1)
 TUNED_LEAN_CONFIGS = {
 }
 
@@ -605,7 +608,8 @@ def emit_graph(ir: GraphIR, dtype: str, symbol: str | None = None, config=None, 
     else:
         w("using CfgWin = flex::NoWindows;      // built without the gather-window variant of the kernel")
     if lean_eligible(ir, dtype):
-        lb, li, lm = tuple(_override(symbol + "_lean") or TUNED_LEAN_CONFIGS.get(f"{ir.name}_{sfx}") or LEAN_CONFIG)[:3]
+        lean_default = LEAN_CONFIG_WIDE if VBYTES[dtype] == 8 else LEAN_CONFIG
+        lb, li, lm = tuple(_override(symbol + "_lean") or TUNED_LEAN_CONFIGS.get(f"{ir.name}_{sfx}") or lean_default)[:3]
         w(f"using CfgLean = flex::WarpCfg<{lb}, {li}, {lm}>;      // the warp kernel for matrices with random columns")
     else:
         w("using CfgLean = flex::NoLean;")
