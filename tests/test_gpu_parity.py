@@ -333,6 +333,46 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable():
     assert row_error(y.cpu().numpy(), ref[0], sums[0]) <= 1e-12
 
 
+def test_row_aligned_plan_serves_launches_of_any_grid():
+    """The plan moves the boundaries between the CTAs of ITS grid onto row ends (workspace header, int32 at byte 132);
+    a launch of that grid hands no carries over, a launch of another grid (descriptor with another max_ctas) finds
+    boundaries of its own that cut rows and must hand them over as before.  Both give the oracle's rows."""
+    from flexspmv_b200.binding import Desc
+    from parity import row_error
+    lib = load_library()
+    ir = graphs.spmv_graph()
+    prob = problems.poisson2d(150)
+    ref, _, sums = ir_eval.run_graph(ir, prob, np.float64, num_threads=4, want_abs_sums=True)
+    dev = torch.device("cuda:0")
+    vals, x = (torch.from_numpy(prob.values[k]).to(dev) for k in ("vals", "x"))
+    cols = torch.from_numpy(prob.indices["selector"]).to(dev)
+    ro = torch.from_numpy(prob.row_offsets).to(dev)
+    y = torch.empty(prob.num_rows, dtype=torch.float64, device=dev)
+    for name in ("workspace_bytes", "plan", "launch", "device_status"):
+        getattr(lib, f"flexspmv_spmv_f64_{name}").restype = ctypes.c_int
+    desc = Desc(prob.num_rows, prob.nnz, prob.num_cols, 32, 0, 0, 0)
+    nbytes = ctypes.c_size_t()
+    assert lib.flexspmv_spmv_f64_workspace_bytes(ctypes.byref(desc), ctypes.byref(nbytes)) == 0
+    ws = torch.zeros(nbytes.value, dtype=torch.uint8, device=dev)
+    wsp, nb = ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(nbytes.value)
+    assert lib.flexspmv_spmv_f64_plan(ctypes.byref(desc), ctypes.c_void_p(ro.data_ptr()), wsp, nb, None) == 0
+    torch.cuda.synchronize()
+    tiles = (prob.num_rows + prob.nnz + 1279) // 1280
+    assert int(ws[:256].cpu().numpy().view(np.int32)[33]) == tiles        # fewer tiles than CTA slots: one tile per CTA
+    vp = (ctypes.c_void_p * 2)(vals.data_ptr(), x.data_ptr())
+    ip = (ctypes.c_void_p * 1)(cols.data_ptr())
+    op = (ctypes.c_void_p * 1)(y.data_ptr())
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for max_ctas in (0, 7, 1, 50):
+        launch_desc = Desc(prob.num_rows, prob.nnz, prob.num_cols, 32, 0, max_ctas, 0)
+        y.fill_(float("nan"))
+        assert lib.flexspmv_spmv_f64_launch(ctypes.byref(launch_desc), vp, ip, ctypes.c_void_p(ro.data_ptr()), op, wsp, nb, None) == 0
+        assert lib.flexspmv_spmv_f64_device_status(wsp, ctypes.c_void_p(status.data_ptr()), None) == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert row_error(y.cpu().numpy(), ref[0], sums[0]) <= 1e-12, max_ctas
+
+
 def test_failed_launch_reaches_the_host_without_a_status_copy():
     """The operator registers a page-locked int with every workspace it plans; a kernel that gives up stores its
     status there.  `ext.check()` and the next call on that workspace raise; nothing on the launch path
