@@ -179,6 +179,10 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
   if (count > 1) load_pair(c_begin + 2, x2, y2);
   typename G::EReg er[IPT];
   if (count) load_edges(y0, (int)(y1 - y0), er);
+  // the end of row x0 + lane (the first 32 rows that end inside the chunk), requested one chunk ahead like the records:
+  // the row offsets stream from DRAM as the records do
+  OffsetT row_end = 0;
+  if (count && lane < (int)(x1 - x0)) row_end = ro[(long long)x0 + 1 + lane];
 
   for (int k = 0; k < count; ++k) {
     const int ne = (int)(y1 - y0), nr = (int)(x1 - x0);
@@ -195,10 +199,13 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     OffsetT x3 = 0, y3 = 0;
     if (k + 3 <= count) load_pair(c_begin + k + 3, x3, y3);
 
+    OffsetT row_end_next = 0;
+    if (k + 1 < count && lane < (int)(x2 - x1)) row_end_next = ro[(long long)x1 + 1 + lane];
+
     // end of row x0 + lane relative to the chunk's first edge (rows past the chunk: unused)
     const OffsetT* ro0 = ro + x0 + 1;
     int rel_end = 0;
-    if (lane < nr) rel_end = (int)(ro0[lane] - y0);
+    if (lane < nr) rel_end = (int)(row_end - y0);
     reinterpret_cast<uint2*>(mk)[lane] = make_uint2(0xffffffffu, 0xffffffffu);
     __syncwarp();
 
@@ -334,6 +341,7 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
     __syncwarp();                                      // the slots are rewritten by the next chunk
 #pragma unroll
     for (int i = 0; i < IPT; ++i) er[i] = er_next[i];
+    row_end = row_end_next;
     x0 = x1; y0 = y1; x1 = x2; y1 = y2; x2 = x3; y2 = y3;
   }
 
