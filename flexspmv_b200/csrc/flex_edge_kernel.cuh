@@ -90,10 +90,21 @@ __global__ void __launch_bounds__(BLOCK) flex_edge_kernel(const typename G::Para
     }
     __syncthreads();
     if (s_flag) {
+      // the last CTA folds the per-CTA partial sums: every thread takes the CTAs tid, tid + BLOCK, ..., then lanes and
+      // warps are combined in a fixed order (the same sum from launch to launch)
       __threadfence();
+#pragma unroll
+      for (int i = 0; i < kAgg; ++i) {
+        V s = V(0);
+        for (unsigned c = tid; c < gridDim.x; c += BLOCK) s += __ldcg(partials + (size_t)c * kAgg + i);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+        if (lane == 0) s_part[warp * kAgg + i] = s;
+      }
+      __syncthreads();
       if (tid < kAgg) {
         V s = V(0);
-        for (unsigned c = 0; c < gridDim.x; ++c) s += __ldcg(partials + (size_t)c * kAgg + tid);
+        for (int w = 0; w < kWarps; ++w) s += s_part[w * kAgg + tid];
         G::store_aggregate(p, tid, s);
       }
       if (tid == 0) a.header->ticket = 0;

@@ -48,7 +48,10 @@ struct GraphApi {
   static constexpr bool kWindowsBuilt = !std::is_same_v<CfgWin, NoWindows>;
   static constexpr bool kLeanBuilt = !std::is_same_v<CfgLean, NoLean>;
   using V = typename G::V;
-  static constexpr int kEdgeBlock = 256, kEdgeIpt = 4;
+#ifndef FLEX_EDGE_IPT
+#define FLEX_EDGE_IPT 4
+#endif
+  static constexpr int kEdgeBlock = 256, kEdgeIpt = FLEX_EDGE_IPT;
   // Row-mode graphs run one thread per row, the trailing partial row of the tile included: on a mesh with
   // exactly kIpt merge items per row (3 edges + the row end at kIpt = 4) a full tile holds kBlock rows plus
   // that partial row, which would cost a second pass over the rows for one thread's worth of work (measured
