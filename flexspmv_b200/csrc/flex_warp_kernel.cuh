@@ -127,230 +127,230 @@ flex_warp_kernel(const typename G::Params p, const WarpKernelArgs a) {
 
   StreamTile<G> tile{&p};
   for (;;) {
-  unsigned run_pos = 0, run_len = 0, run_id = 0;
-  if (lane == 0) {
-    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(&s_next);
-    for (;;) {
-      const unsigned pos = (unsigned)seen, id = (unsigned)(seen >> 32);
-      if (pos >= cta_chunks) break;
-      const unsigned left = cta_chunks - pos;
-      unsigned len = left / Cfg::kWarps;
-      if (len < min_run) len = min_run;
-      if (len > left || id == (unsigned)kMaxRuns - 1) len = left;
-      const unsigned long long want = ((unsigned long long)(id + 1) << 32) | (pos + len);
-      const unsigned long long got = atomicCAS(&s_next, seen, want);
-      if (got == seen) { run_pos = pos; run_len = len; run_id = id; break; }
-      seen = got;
-    }
-  }
-  run_pos = __shfl_sync(0xffffffffu, run_pos, 0);
-  run_len = __shfl_sync(0xffffffffu, run_len, 0);
-  run_id = __shfl_sync(0xffffffffu, run_id, 0);
-  if (run_len == 0) break;
-  const long long c_begin = cta_begin + run_pos;
-  const int count = (int)run_len;
-
-  V carry[kAcc];
-#pragma unroll
-  for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
-  long long end_row = a.num_rows;      // row the run's carry belongs to
-
-  // A chunk boundary is a (row, edge) pair; every lane reads the same pair (one broadcast transaction, no shuffles).
-  auto load_pair = [&](long long c, OffsetT& x, OffsetT& y) {
-    if constexpr (sizeof(OffsetT) == 4) {
-      const int2 v = __ldg(reinterpret_cast<const int2*>(coords) + c);
-      x = v.x; y = v.y;
-    } else {
-      const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(coords) + c);
-      x = v.x; y = v.y;
-    }
-  };
-  // per-edge records of one chunk into registers (lanes on consecutive edges)
-  auto load_edges = [&](OffsetT y0, int ne, typename G::EReg (&er)[IPT]) {
-    const long long e0 = (long long)y0 + lane;
-#pragma unroll
-    for (int i = 0; i < IPT; ++i)
-      if (i * 32 + lane < ne) G::load_edge(p, tile, e0 + i * 32, e0 + i * 32, er[i]);
-  };
-
-  // boundaries of the current chunk (x0, y0) .. (x1, y1) and the two after it
-  OffsetT x0 = 0, y0 = 0, x1 = 0, y1 = 0, x2 = 0, y2 = 0;
-  if (count) { load_pair(c_begin, x0, y0); load_pair(c_begin + 1, x1, y1); }
-  if (count > 1) load_pair(c_begin + 2, x2, y2);
-  typename G::EReg er[IPT];
-  if (count) load_edges(y0, (int)(y1 - y0), er);
-  // the end of row x0 + lane (the first 32 rows that end inside the chunk), requested one chunk ahead like the records:
-  // the row offsets stream from DRAM as the records do
-  OffsetT row_end = 0;
-  if (count && lane < (int)(x1 - x0)) row_end = ro[(long long)x0 + 1 + lane];
-
-  for (int k = 0; k < count; ++k) {
-    const int ne = (int)(y1 - y0), nr = (int)(x1 - x0);
-
-    // gathers of this chunk go out first
-    typename G::GEdge ge[IPT];
-#pragma unroll
-    for (int i = 0; i < IPT; ++i)
-      if (i * 32 + lane < ne) G::gather_edge(p, er[i], ge[i]);
-
-    // while they fly: the next chunk's records, the boundary after that, this chunk's row ends
-    typename G::EReg er_next[IPT];
-    if (k + 1 < count) load_edges(y1, (int)(y2 - y1), er_next);
-    OffsetT x3 = 0, y3 = 0;
-    if (k + 3 <= count) load_pair(c_begin + k + 3, x3, y3);
-
-    OffsetT row_end_next = 0;
-    if (k + 1 < count && lane < (int)(x2 - x1)) row_end_next = ro[(long long)x1 + 1 + lane];
-
-    // end of row x0 + lane relative to the chunk's first edge (rows past the chunk: unused)
-    const OffsetT* ro0 = ro + x0 + 1;
-    int rel_end = 0;
-    if (lane < nr) rel_end = (int)(row_end - y0);
-    reinterpret_cast<uint2*>(mk)[lane] = make_uint2(0xffffffffu, 0xffffffffu);
-    __syncwarp();
-
-    // rows that end inside the chunk, one lane per row: the last edge of a row is marked with the row's number;
-    // a row without edges in this chunk is finished here (row x0 then takes the whole carry)
-    const bool seed_used = __any_sync(0xffffffffu, lane == 0 && nr > 0 && rel_end == 0);
-    int before = 0;                                      // where the row before this batch's first row ended
-    for (int r0 = 0; r0 < nr; r0 += 32) {
-      const int r = r0 + lane;
-      if (r0) {
-        before = __shfl_sync(0xffffffffu, rel_end, 31);
-        rel_end = 0;
-        if (r < nr) rel_end = (int)(ro0[r] - y0);
+    unsigned run_pos = 0, run_len = 0, run_id = 0;
+    if (lane == 0) {
+      unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(&s_next);
+      for (;;) {
+        const unsigned pos = (unsigned)seen, id = (unsigned)(seen >> 32);
+        if (pos >= cta_chunks) break;
+        const unsigned left = cta_chunks - pos;
+        unsigned len = left / Cfg::kWarps;
+        if (len < min_run) len = min_run;
+        if (len > left || id == (unsigned)kMaxRuns - 1) len = left;
+        const unsigned long long want = ((unsigned long long)(id + 1) << 32) | (pos + len);
+        const unsigned long long got = atomicCAS(&s_next, seen, want);
+        if (got == seen) { run_pos = pos; run_len = len; run_id = id; break; }
+        seen = got;
       }
-      int prev = __shfl_up_sync(0xffffffffu, rel_end, 1);
-      if (lane == 0) prev = before;
-      if (r < nr) {
-        if (rel_end > prev) {
-          const int q = rel_end - 1, owner = q / IPT;
-          mk[owner * 8 + (q - owner * IPT)] = (unsigned char)r;
-        } else {
-          static_for<G::kNumReducers>([&](auto R) {
-            constexpr int d = G::template red_dim<R.value>();
-            constexpr int o = G::template red_off<R.value>();
-            V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + r) * d;
+    }
+    run_pos = __shfl_sync(0xffffffffu, run_pos, 0);
+    run_len = __shfl_sync(0xffffffffu, run_len, 0);
+    run_id = __shfl_sync(0xffffffffu, run_id, 0);
+    if (run_len == 0) break;
+    const long long c_begin = cta_begin + run_pos;
+    const int count = (int)run_len;
+
+    V carry[kAcc];
 #pragma unroll
-            for (int j = 0; j < d; ++j) dst[j] = (r == 0) ? carry[o + j] : V(0);
-          });
+    for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
+    long long end_row = a.num_rows;      // row the run's carry belongs to
+
+    // A chunk boundary is a (row, edge) pair; every lane reads the same pair (one broadcast transaction, no shuffles).
+    auto load_pair = [&](long long c, OffsetT& x, OffsetT& y) {
+      if constexpr (sizeof(OffsetT) == 4) {
+        const int2 v = __ldg(reinterpret_cast<const int2*>(coords) + c);
+        x = v.x; y = v.y;
+      } else {
+        const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(coords) + c);
+        x = v.x; y = v.y;
+      }
+    };
+    // per-edge records of one chunk into registers (lanes on consecutive edges)
+    auto load_edges = [&](OffsetT y0, int ne, typename G::EReg (&er)[IPT]) {
+      const long long e0 = (long long)y0 + lane;
+#pragma unroll
+      for (int i = 0; i < IPT; ++i)
+        if (i * 32 + lane < ne) G::load_edge(p, tile, e0 + i * 32, e0 + i * 32, er[i]);
+    };
+
+    // boundaries of the current chunk (x0, y0) .. (x1, y1) and the two after it
+    OffsetT x0 = 0, y0 = 0, x1 = 0, y1 = 0, x2 = 0, y2 = 0;
+    if (count) { load_pair(c_begin, x0, y0); load_pair(c_begin + 1, x1, y1); }
+    if (count > 1) load_pair(c_begin + 2, x2, y2);
+    typename G::EReg er[IPT];
+    if (count) load_edges(y0, (int)(y1 - y0), er);
+    // the end of row x0 + lane (the first 32 rows that end inside the chunk), requested one chunk ahead like the records:
+    // the row offsets stream from DRAM as the records do
+    OffsetT row_end = 0;
+    if (count && lane < (int)(x1 - x0)) row_end = ro[(long long)x0 + 1 + lane];
+
+    for (int k = 0; k < count; ++k) {
+      const int ne = (int)(y1 - y0), nr = (int)(x1 - x0);
+
+      // gathers of this chunk go out first
+      typename G::GEdge ge[IPT];
+#pragma unroll
+      for (int i = 0; i < IPT; ++i)
+        if (i * 32 + lane < ne) G::gather_edge(p, er[i], ge[i]);
+
+      // while they fly: the next chunk's records, the boundary after that, this chunk's row ends
+      typename G::EReg er_next[IPT];
+      if (k + 1 < count) load_edges(y1, (int)(y2 - y1), er_next);
+      OffsetT x3 = 0, y3 = 0;
+      if (k + 3 <= count) load_pair(c_begin + k + 3, x3, y3);
+
+      OffsetT row_end_next = 0;
+      if (k + 1 < count && lane < (int)(x2 - x1)) row_end_next = ro[(long long)x1 + 1 + lane];
+
+      // end of row x0 + lane relative to the chunk's first edge (rows past the chunk: unused)
+      const OffsetT* ro0 = ro + x0 + 1;
+      int rel_end = 0;
+      if (lane < nr) rel_end = (int)(row_end - y0);
+      reinterpret_cast<uint2*>(mk)[lane] = make_uint2(0xffffffffu, 0xffffffffu);
+      __syncwarp();
+
+      // rows that end inside the chunk, one lane per row: the last edge of a row is marked with the row's number;
+      // a row without edges in this chunk is finished here (row x0 then takes the whole carry)
+      const bool seed_used = __any_sync(0xffffffffu, lane == 0 && nr > 0 && rel_end == 0);
+      int before = 0;                                      // where the row before this batch's first row ended
+      for (int r0 = 0; r0 < nr; r0 += 32) {
+        const int r = r0 + lane;
+        if (r0) {
+          before = __shfl_sync(0xffffffffu, rel_end, 31);
+          rel_end = 0;
+          if (r < nr) rel_end = (int)(ro0[r] - y0);
         }
-      }
-    }
-    if (seed_used) {
-#pragma unroll
-      for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
-    }
-
-    // products into this warp's slots (lanes on consecutive edges; slots past the chunk's edges hold zero)
-    typename G::GRow gr;
-#pragma unroll
-    for (int i = 0; i < IPT; ++i) {
-      V prod[kAcc];
-#pragma unroll
-      for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
-      if (i * 32 + lane < ne) G::map(p, er[i], (long long)y0 + (i * 32 + lane), gr, ge[i], prod);
-#pragma unroll
-      for (int j = 0; j < kAcc; ++j) sp[j * CH + i * 32 + lane] = prod[j];
-    }
-    __syncwarp();
-
-    // blocked pass: every lane sums IPT consecutive items and closes the rows that end inside its span
-    V run[kAcc], first[kAcc];
-#pragma unroll
-    for (int j = 0; j < kAcc; ++j) { run[j] = V(0); first[j] = V(0); }
-    int first_row = -1;
-    {
-      V pv[IPT][kAcc];
-      int pm[IPT];
-      const uint2 mw = reinterpret_cast<const uint2*>(mk)[lane];
-#pragma unroll
-      for (int i = 0; i < IPT; ++i) {
-        pm[i] = (int)(((i < 4 ? mw.x : mw.y) >> (8 * (i & 3))) & 0xffu);
-#pragma unroll
-        for (int j = 0; j < kAcc; ++j) pv[i][j] = sp[j * CH + lane * IPT + i];
-      }
-#pragma unroll
-      for (int i = 0; i < IPT; ++i) {
-#pragma unroll
-        for (int j = 0; j < kAcc; ++j) run[j] += pv[i][j];
-        if (pm[i] != 0xff) {
-          if (first_row < 0) {                         // may have begun in earlier lanes: finished after the scan
-            first_row = pm[i];
-#pragma unroll
-            for (int j = 0; j < kAcc; ++j) first[j] = run[j];
+        int prev = __shfl_up_sync(0xffffffffu, rel_end, 1);
+        if (lane == 0) prev = before;
+        if (r < nr) {
+          if (rel_end > prev) {
+            const int q = rel_end - 1, owner = q / IPT;
+            mk[owner * 8 + (q - owner * IPT)] = (unsigned char)r;
           } else {
             static_for<G::kNumReducers>([&](auto R) {
               constexpr int d = G::template red_dim<R.value>();
               constexpr int o = G::template red_off<R.value>();
-              V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + pm[i]) * d;
+              V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + r) * d;
 #pragma unroll
-              for (int j = 0; j < d; ++j) dst[j] = run[o + j];
+              for (int j = 0; j < d; ++j) dst[j] = (r == 0) ? carry[o + j] : V(0);
             });
           }
-#pragma unroll
-          for (int j = 0; j < kAcc; ++j) run[j] = V(0);
         }
       }
-    }
-    // segmented inclusive scan of the open partial sums: a lane that closed a row passes on only what follows it.
-    // Which lanes closed a row is one ballot; a lane takes a value from `d` lanes down only while that lane is not
-    // before the nearest closing lane at or below it (lane 0 when there is none).
-    const unsigned closed = __ballot_sync(0xffffffffu, first_row >= 0);
-    const unsigned closed_le = closed & (0xffffffffu >> (31 - lane));
-    const int reach = lane - (closed_le ? 31 - __clz(closed_le) : 0);      // lanes below this one in its segment
-    V scan[kAcc];
+      if (seed_used) {
 #pragma unroll
-    for (int j = 0; j < kAcc; ++j) scan[j] = run[j];
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-#pragma unroll
-      for (int j = 0; j < kAcc; ++j) {
-        const V v_up = shfl_up_any(scan[j], d);
-        if (reach >= d) scan[j] = v_up + scan[j];
+        for (int j = 0; j < kAcc; ++j) carry[j] = V(0);
       }
-    }
-    // what the lanes before this one left open (plus the warp's carry when none of them closed a row)
-    const bool f_ex = (closed_le & ~(1u << lane)) != 0;
-    V in[kAcc];
-#pragma unroll
-    for (int j = 0; j < kAcc; ++j) {
-      V v_ex = shfl_up_any(scan[j], 1);
-      if (lane == 0) v_ex = V(0);
-      in[j] = f_ex ? v_ex : carry[j] + v_ex;
-    }
-    if (first_row >= 0) {
-      static_for<G::kNumReducers>([&](auto R) {
-        constexpr int d = G::template red_dim<R.value>();
-        constexpr int o = G::template red_off<R.value>();
-        V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + first_row) * d;
-#pragma unroll
-        for (int j = 0; j < d; ++j) dst[j] = in[o + j] + first[o + j];
-      });
-    }
-    // the warp's new carry: what is still open behind the last lane
-    {
-      const bool f31 = closed != 0;
-#pragma unroll
-      for (int j = 0; j < kAcc; ++j) {
-        const V v31 = __shfl_sync(0xffffffffu, scan[j], 31);
-        carry[j] = f31 ? v31 : carry[j] + v31;
-      }
-    }
-    end_row = x1;
-    __syncwarp();                                      // the slots are rewritten by the next chunk
-#pragma unroll
-    for (int i = 0; i < IPT; ++i) er[i] = er_next[i];
-    row_end = row_end_next;
-    x0 = x1; y0 = y1; x1 = x2; y1 = y2; x2 = x3; y2 = y3;
-  }
 
-  // the run's carry: the row it left open and the partial sums of that row
-  if (lane == 0) {
-    s_run_row[run_id] = (OffsetT)end_row;
+      // products into this warp's slots (lanes on consecutive edges; slots past the chunk's edges hold zero)
+      typename G::GRow gr;
 #pragma unroll
-    for (int j = 0; j < kAcc; ++j) s_run_val[run_id * kAcc + j] = carry[j];
-  }
+      for (int i = 0; i < IPT; ++i) {
+        V prod[kAcc];
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) prod[j] = V(0);
+        if (i * 32 + lane < ne) G::map(p, er[i], (long long)y0 + (i * 32 + lane), gr, ge[i], prod);
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) sp[j * CH + i * 32 + lane] = prod[j];
+      }
+      __syncwarp();
+
+      // blocked pass: every lane sums IPT consecutive items and closes the rows that end inside its span
+      V run[kAcc], first[kAcc];
+#pragma unroll
+      for (int j = 0; j < kAcc; ++j) { run[j] = V(0); first[j] = V(0); }
+      int first_row = -1;
+      {
+        V pv[IPT][kAcc];
+        int pm[IPT];
+        const uint2 mw = reinterpret_cast<const uint2*>(mk)[lane];
+#pragma unroll
+        for (int i = 0; i < IPT; ++i) {
+          pm[i] = (int)(((i < 4 ? mw.x : mw.y) >> (8 * (i & 3))) & 0xffu);
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) pv[i][j] = sp[j * CH + lane * IPT + i];
+        }
+#pragma unroll
+        for (int i = 0; i < IPT; ++i) {
+#pragma unroll
+          for (int j = 0; j < kAcc; ++j) run[j] += pv[i][j];
+          if (pm[i] != 0xff) {
+            if (first_row < 0) {                         // may have begun in earlier lanes: finished after the scan
+              first_row = pm[i];
+#pragma unroll
+              for (int j = 0; j < kAcc; ++j) first[j] = run[j];
+            } else {
+              static_for<G::kNumReducers>([&](auto R) {
+                constexpr int d = G::template red_dim<R.value>();
+                constexpr int o = G::template red_off<R.value>();
+                V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + pm[i]) * d;
+#pragma unroll
+                for (int j = 0; j < d; ++j) dst[j] = run[o + j];
+              });
+            }
+#pragma unroll
+            for (int j = 0; j < kAcc; ++j) run[j] = V(0);
+          }
+        }
+      }
+      // segmented inclusive scan of the open partial sums: a lane that closed a row passes on only what follows it.
+      // Which lanes closed a row is one ballot; a lane takes a value from `d` lanes down only while that lane is not
+      // before the nearest closing lane at or below it (lane 0 when there is none).
+      const unsigned closed = __ballot_sync(0xffffffffu, first_row >= 0);
+      const unsigned closed_le = closed & (0xffffffffu >> (31 - lane));
+      const int reach = lane - (closed_le ? 31 - __clz(closed_le) : 0);      // lanes below this one in its segment
+      V scan[kAcc];
+#pragma unroll
+      for (int j = 0; j < kAcc; ++j) scan[j] = run[j];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) {
+          const V v_up = shfl_up_any(scan[j], d);
+          if (reach >= d) scan[j] = v_up + scan[j];
+        }
+      }
+      // what the lanes before this one left open (plus the warp's carry when none of them closed a row)
+      const bool f_ex = (closed_le & ~(1u << lane)) != 0;
+      V in[kAcc];
+#pragma unroll
+      for (int j = 0; j < kAcc; ++j) {
+        V v_ex = shfl_up_any(scan[j], 1);
+        if (lane == 0) v_ex = V(0);
+        in[j] = f_ex ? v_ex : carry[j] + v_ex;
+      }
+      if (first_row >= 0) {
+        static_for<G::kNumReducers>([&](auto R) {
+          constexpr int d = G::template red_dim<R.value>();
+          constexpr int o = G::template red_off<R.value>();
+          V* dst = G::template red_out<R.value>(p) + (size_t)((long long)x0 + first_row) * d;
+#pragma unroll
+          for (int j = 0; j < d; ++j) dst[j] = in[o + j] + first[o + j];
+        });
+      }
+      // the warp's new carry: what is still open behind the last lane
+      {
+        const bool f31 = closed != 0;
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) {
+          const V v31 = __shfl_sync(0xffffffffu, scan[j], 31);
+          carry[j] = f31 ? v31 : carry[j] + v31;
+        }
+      }
+      end_row = x1;
+      __syncwarp();                                      // the slots are rewritten by the next chunk
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) er[i] = er_next[i];
+      row_end = row_end_next;
+      x0 = x1; y0 = y1; x1 = x2; y1 = y2; x2 = x3; y2 = y3;
+    }
+
+    // the run's carry: the row it left open and the partial sums of that row
+    if (lane == 0) {
+      s_run_row[run_id] = (OffsetT)end_row;
+#pragma unroll
+      for (int j = 0; j < kAcc; ++j) s_run_val[run_id * kAcc + j] = carry[j];
+    }
   }  // runs of this warp
 
   // ---- the CTA folds the carries of its runs; what its last run left open goes to the last CTA -------------------
