@@ -108,3 +108,14 @@ def test_generators_are_valid_csr():
     r = np.repeat(np.arange(5000), np.diff(pl.row_offsets))
     k = r.astype(np.int64) * (1 << 32) + pl.indices["selector"]
     assert (np.diff(k) >= 0).all()                    # columns sorted within each row
+
+
+def test_warp_kernel_configuration_follows_the_value_width():
+    """The emitter gives the random-column kernel 1024-thread CTAs for 4-byte values and 768-thread CTAs for 8-byte
+    values (which need more than the 64 registers a 1024-thread CTA leaves a thread)."""
+    from flexspmv_b200 import graphs
+    from flexspmv_b200.codegen.emit_cuda import emit_graph
+    ir = graphs.spmv_graph()
+    assert "using CfgLean = flex::WarpCfg<1024, 5, 1>;" in emit_graph(ir, "float32", "spmv_f32")
+    for dt, sym in (("float64", "spmv_f64"), ("int64", "spmv_i64")):
+        assert "using CfgLean = flex::WarpCfg<768, 5, 1>;" in emit_graph(ir, dt, sym)
