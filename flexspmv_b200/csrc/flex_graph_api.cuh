@@ -48,10 +48,9 @@ struct GraphApi {
   static constexpr bool kWindowsBuilt = !std::is_same_v<CfgWin, NoWindows>;
   static constexpr bool kLeanBuilt = !std::is_same_v<CfgLean, NoLean>;
   using V = typename G::V;
-#ifndef FLEX_EDGE_IPT
-#define FLEX_EDGE_IPT 4
-#endif
-  static constexpr int kEdgeBlock = 256, kEdgeIpt = FLEX_EDGE_IPT;
+  // edge kernel: 256 threads x 4 edges per thread (measured on B200, 2^27 edges: 2 / 4 / 8 edges per thread give
+  // 91.5 / 90.8 / 62.9 % of the HBM peak for a product + global sum and 76.4 / 94.2 / 77.9 % for a gather written in place)
+  static constexpr int kEdgeBlock = 256, kEdgeIpt = 4;
   // Row-mode graphs run one thread per row, the trailing partial row of the tile included: on a mesh with
   // exactly kIpt merge items per row (3 edges + the row end at kIpt = 4) a full tile holds kBlock rows plus
   // that partial row, which would cost a second pass over the rows for one thread's worth of work (measured
