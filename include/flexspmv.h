@@ -54,7 +54,9 @@ typedef struct flexspmv_desc {
   int64_t num_vertices;  /* rows of the gather sources (informational; used by validation)          */
   int32_t offset_bits;   /* 32 or 64: width of the row-offset entries                               */
   int32_t tile_items;    /* merge items (rows + edges) per tile; 0 = the graph's compiled default   */
-  int32_t max_ctas;      /* cap on persistent CTAs; 0 = SM count x resident CTAs per SM             */
+  int32_t max_ctas;      /* cap on persistent CTAs; 0 = SM count x resident CTAs per SM.  plan() lays the tile
+                            boundaries between the CTAs of THIS grid on row ends where it can; a launch with
+                            another value still works but hands carries between its CTAs            */
   int32_t reserved;      /* flags: 0 or an OR of the FLEXSPMV_FLAG_* below (field name kept from ABI 1) */
 } flexspmv_desc;
 
